@@ -1,0 +1,384 @@
+#!/usr/bin/env python3
+"""Benchmark of the sparse-MLA hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl native|reference]
+
+A step is one pass of the op over one batch of synthetic query tokens.  The default workload is the
+DSV4-Flash absorbed fp8 decode shape (128 tokens x 64 heads, swa 65536 slots / top-k 512 plus a
+compressed extra stream of 16384 slots / top-k 2048, attn_sink); every rank of a multi-GPU run
+processes its own batch against its own cache replica (token sharding, no collective on the data
+path), so scaling is weak.  Prints ONE JSON line (rank 0).
+
+Timing: W warm-up steps, then K steps between CUDA events on the launching stream, bracketed by a
+barrier + synchronize, max over ranks.  The cache is rotated through replicas whose total size
+exceeds the 126 MB L2 so a step never finds its rows cached by the previous one.
+`e2e` repeats the measurement with the step's inputs (q, indices, lens) copied from pinned host
+memory and the output copied back inside the timed region; the paged KV cache stays resident in
+HBM, as it does in serving.  `cpu_baseline` times the fp32 CPU oracle on a bounded token sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "forks-flash-mla-int_b200"))
+sys.path.insert(0, ROOT)
+
+L2_BYTES = 126 * 1024 * 1024
+
+WORKLOADS = {
+    # name: (op kind, builder kwargs, description)
+    "dsv4_fp8_decode_T128_H64": ("decode_fp8", dict(fmt="fp8", T=128, H=64)),
+    "dsv4_int8_decode_T128_H64": ("decode_int8", dict(fmt="int8", T=128, H=64)),
+    "dsv4_int8_decode_T128_H128": ("decode_int8", dict(fmt="int8", T=128, H=128)),
+    "dsv4_int8_decode_T512_H64": ("decode_int8", dict(fmt="int8", T=512, H=64)),
+    "dsv4_int8_decode_T32_H64": ("decode_int8", dict(fmt="int8", T=32, H=64)),
+    "dsv4_int8_decode_T8_H64": ("decode_int8", dict(fmt="int8", T=8, H=64)),
+    "dsv4_int8_decode_T1_H64": ("decode_int8", dict(fmt="int8", T=1, H=64)),
+    "ctx16k_fp8_decode_T1024_H128": ("decode_fp8", dict(fmt="fp8", T=1024, H=128, swa_slots=16384, swa_topk=2048,
+                                                        extra_slots=16384, extra_topk=512, mask_frac=0.0,
+                                                        full_lens=True)),
+    "ctx16k_int8_decode_T1024_H128": ("decode_int8", dict(fmt="int8", T=1024, H=128, swa_slots=16384, swa_topk=2048,
+                                                          extra_slots=16384, extra_topk=512, mask_frac=0.0,
+                                                          full_lens=True)),
+    "int8_prefill_T4096_H64": ("prefill_int8", dict(T=4096, H=64)),
+}
+DEFAULT_WORKLOAD = "dsv4_fp8_decode_T128_H64"
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return None
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in out.splitlines():
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return None
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def build_workload(name, device, seed):
+    from flash_mla import synthetic
+    kind, kw = WORKLOADS[name]
+    if kind == "prefill_int8":
+        args, meta = synthetic.prefill_int8_workload(seed=seed, device=device, **kw)
+    else:
+        args, meta = synthetic.decode_workload(seed=seed, device=device, **kw)
+    return kind, args, meta
+
+
+def op_for(kind):
+    import flash_mla
+    return {"decode_fp8": flash_mla.sparse_mla_decode_fp8, "decode_int8": flash_mla.sparse_mla_decode_int8,
+            "prefill_int8": flash_mla.sparse_mla_prefill_int8}[kind]
+
+
+CACHE_KEYS = ("swa_cache", "swa_scale", "extra_cache", "extra_scale")
+
+
+def cache_replicas(args, meta):
+    """Clones of the cache tensors so that the set cycled through is larger than L2."""
+    import torch
+    per = sum(a.numel() * a.element_size() for a in meta["keep"]) or sum(
+        args[k].numel() * args[k].element_size() for k in CACHE_KEYS if k in args)
+    n = max(1, min(16, -(-int(1.5 * L2_BYTES) // max(per, 1))))
+    reps = [{k: args[k] for k in CACHE_KEYS if k in args}]
+    for _ in range(n - 1):
+        if meta["keep"]:   # inline-528 views: clone the backing buffers and rebuild the views
+            rep = {}
+            for name, buf in zip(("swa", "extra"), meta["keep"]):
+                b = buf.clone()
+                rep[f"{name}_cache"] = b[:, :, :512].view(torch.int8)
+                rep[f"{name}_scale"] = b[:, :, 512:516].view(torch.float32).squeeze(-1)
+            reps.append(rep)
+        else:
+            reps.append({k: args[k].clone() for k in CACHE_KEYS if k in args})
+    return reps, per * n
+
+
+def cpu_oracle_inputs(kind, args):
+    """Dequantised fp32 rows + CPU copies for the oracle (outside any timed region)."""
+    import numpy as np
+    import oracle
+    cpu = {k: (v.detach().cpu() if hasattr(v, "cpu") else v) for k, v in args.items()}
+    if kind == "decode_fp8":
+        swa_K = oracle.dequant_fp8_ds_mla(cpu["swa_cache"].numpy())
+        extra_K = oracle.dequant_fp8_ds_mla(cpu["extra_cache"].numpy()) if "extra_cache" in cpu else None
+    else:
+        swa_K = oracle.dequant_int8_ds_mla(cpu["swa_cache"].contiguous().numpy(), cpu["swa_scale"].contiguous().numpy())
+        extra_K = (oracle.dequant_int8_ds_mla(cpu["extra_cache"].contiguous().numpy(),
+                                              cpu["extra_scale"].contiguous().numpy())
+                   if "extra_cache" in cpu else None)
+    q = cpu["q"].float().numpy()
+    sink = cpu["attn_sink"].numpy() if "attn_sink" in cpu else None
+    return dict(q=q, swa_K=swa_K, swa_idx=cpu["swa_indices"].numpy(), swa_lens=cpu["swa_lens"].numpy(),
+                extra_K=extra_K, extra_idx=cpu["extra_indices"].numpy() if "extra_indices" in cpu else None,
+                extra_lens=cpu["extra_lens"].numpy() if "extra_lens" in cpu else None, sink=sink)
+
+
+def time_cpu_oracle(oin, T, budget_s=12.0):
+    """Times the oracle on the first n tokens, n chosen so the work takes about `budget_s`."""
+    import oracle
+    import torch
+    t0 = time.perf_counter()
+    oracle.sparse_mla_attention(**oin, tokens=[0])
+    per_tok = max(time.perf_counter() - t0, 1e-4)
+    n = int(max(1, min(T, budget_s / per_tok)))
+    t0 = time.perf_counter()
+    out = oracle.sparse_mla_attention(**oin, tokens=list(range(n)))
+    dt = time.perf_counter() - t0
+    return n, dt, out, torch.get_num_threads()
+
+
+def run_reference(args_ns):
+    """Reference arm: the fp32 CPU oracle (a port of the reference's own torch oracle; the Python
+    reference cannot travel to the GPU box) on the host cores, same workload, bounded sample per step."""
+    import torch
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    name = args_ns.workload
+    kind, kw = WORKLOADS[name]
+    if "int8" in kind:   # the int8 caches come from the product quantizer; use its CPU oracle twin here
+        dev = "cuda" if torch.cuda.is_available() else None
+        if dev is None:
+            print(json.dumps({"impl": "reference", "unavailable": "int8 workloads need a GPU to build their caches"}))
+            return
+    else:
+        dev = "cpu"
+    kind, wargs, meta = build_workload(name, dev, 0)
+    oin = cpu_oracle_inputs(kind, wargs)
+    T = meta["T"]
+    import oracle
+    t0 = time.perf_counter()
+    oracle.sparse_mla_attention(**oin, tokens=[0])
+    per_tok = max(time.perf_counter() - t0, 1e-4)
+    n = int(max(1, min(T, 2.0 / per_tok)))          # about 2 s per step
+    toks = list(range(n))
+    for _ in range(args_ns.warmup):
+        oracle.sparse_mla_attention(**oin, tokens=toks[: max(1, n // 8)])
+    t0 = time.perf_counter()
+    for _ in range(args_ns.steps):
+        oracle.sparse_mla_attention(**oin, tokens=toks)
+    dt = time.perf_counter() - t0
+    val = n * args_ns.steps / dt
+    cores = torch.get_num_threads()
+    line = {
+        "impl": "reference", "metric": "sparse MLA decode tokens/s" if "decode" in kind else "sparse MLA prefill tokens/s",
+        "value": val, "unit": "tokens/s", "n_gpus": args_ns.gpus, "steps": args_ns.steps, "warmup": args_ns.warmup,
+        "ms_per_step": dt / args_ns.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": name, "tokens_per_step_sampled": n, "heads": meta["H"]},
+        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port",
+                         "sample": f"first {n} of {T} tokens per step, {args_ns.steps} steps; caches dequantised once outside the timed region"},
+        "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    a = ap.parse_args()
+    a.warmup = max(a.warmup, 3) if a.impl == "native" else a.warmup
+
+    if a.impl == "reference":
+        run_reference(a)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
+    torch.cuda.set_device(local)
+    dev = f"cuda:{local}"
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device(dev))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    kind, wargs, meta = build_workload(a.workload, dev, seed=rank)
+    op = op_for(kind)
+    T, H = meta["T"], meta["H"]
+    reps, rep_bytes = cache_replicas(wargs, meta)
+    base = {k: v for k, v in wargs.items() if k not in CACHE_KEYS}
+
+    def step(i, over=None):
+        kw = dict(base)
+        if over:
+            kw.update(over)
+        kw.update(reps[i % len(reps)])
+        return op(**kw)
+
+    # launches per step (claimed): the attention kernel, plus the combine kernel when split
+    from flash_mla import c_abi
+    import ctypes
+    lib = c_abi.load()
+    width = wargs["swa_indices"].shape[1] + (wargs["extra_indices"].shape[1] if "extra_indices" in wargs else 0)
+    splits = ctypes.c_int(1)
+    if kind.startswith("decode"):
+        lib.smla_decode_plan(T, H, width, ctypes.byref(splits), None)
+    launches_per_step = 1 + (1 if splits.value > 1 else 0)
+
+    for i in range(a.warmup):
+        step(i)
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(a.steps):
+        out = step(i)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if sampler else None
+    if world > 1:
+        tms = torch.tensor([ms], device=dev)
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+        ms = float(tms.item())
+    ms_per_step = ms / a.steps
+    value = world * T * a.steps / (ms / 1e3)
+
+    # ---- end to end: per-step inputs from pinned host memory, result back to host
+    host_keys = [k for k in ("q", "swa_indices", "swa_lens", "extra_indices", "extra_lens") if k in base]
+    host_in = {k: base[k].cpu().pin_memory() for k in host_keys}
+    dev_in = {k: torch.empty_like(base[k]) for k in host_keys}
+    host_out = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+    h2d = sum(v.numel() * v.element_size() for v in host_in.values())
+    d2h = host_out.numel() * host_out.element_size()
+
+    def e2e_step(i):
+        for k in host_keys:
+            dev_in[k].copy_(host_in[k], non_blocking=True)
+        o = step(i, dev_in)
+        host_out.copy_(o, non_blocking=True)
+
+    for i in range(3):
+        e2e_step(i)
+    barrier()
+    e0.record()
+    for i in range(a.steps):
+        e2e_step(i)
+    e1.record()
+    barrier()
+    ms_e2e = e0.elapsed_time(e1)
+    if world > 1:
+        tms = torch.tensor([ms_e2e], device=dev)
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+        ms_e2e = float(tms.item())
+    e2e_value = world * T * a.steps / (ms_e2e / 1e3)
+
+    status = ctypes.c_int(0)
+    lib.smla_read_device_status(ctypes.byref(status))
+
+    if rank == 0:
+        hbm_gbs, bf16_tf, peak_kind = measured_peaks()
+        dur_s = ms_per_step / 1e3            # one attention launch per step (+ a small combine when split)
+        t_hbm = meta["bytes"] / (hbm_gbs * 1e9)
+        t_mma = meta["flops"] / (bf16_tf * 1e12)
+        if t_hbm >= t_mma:
+            roof = {"bound": "hbm", "achieved": meta["bytes"] / dur_s / 1e9, "peak": hbm_gbs, "unit": "GB/s"}
+        else:
+            roof = {"bound": "tensor", "achieved": meta["flops"] / dur_s / 1e12, "peak": bf16_tf, "unit": "TFLOP/s"}
+        roof["frac"] = roof["achieved"] / roof["peak"]
+        roof["traffic"] = None
+        roof["peak_kind"] = peak_kind
+        roof["kernel"] = "sparse_mla_fwd_kernel"
+        roof["algorithmic_bytes_per_launch"] = meta["bytes"]
+        roof["algorithmic_flops_per_launch"] = meta["flops"]
+        roof["other_bound_time_us"] = {"hbm": t_hbm * 1e6, "tensor": t_mma * 1e6}
+        line = {
+            "metric": ("sparse MLA decode tokens/s" if kind.startswith("decode") else "sparse MLA prefill tokens/s"),
+            "value": value, "unit": "tokens/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": a.workload, "tokens_per_gpu_per_step": T, "heads": H,
+                       "rows_in_lens_per_step": meta["rows_in_lens"], "cache_format": meta["fmt"],
+                       "l2": f"cache rotated over {len(reps)} replicas ({rep_bytes / 2**20:.0f} MiB) > 126 MiB L2",
+                       "sharding": "tokens sharded across GPUs, cache replicated, no collective",
+                       "num_splits": splits.value},
+            "roofline": roof,
+            "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": ms_e2e / a.steps,
+                    "note": "q/indices/lens from pinned host memory and output back each step; KV cache resident in HBM"},
+            "gpu_launches": a.steps * launches_per_step,
+            "device_status": status.value,
+        }
+        if clocks:
+            line["clocks"] = clocks
+        if world == 1 and not a.no_cpu_baseline:
+            import numpy as np
+            oin = cpu_oracle_inputs(kind, wargs)
+            n, dt, ref, cores = time_cpu_oracle(oin, T)
+            got = step(0).float().cpu().numpy()[:n]
+            err = np.abs(got - ref[:n])
+            line["cpu_baseline"] = {"value": n / dt, "unit": "tokens/s", "cores": cores, "kind": "port",
+                                    "sample": f"first {n} of {T} tokens of the same step; caches dequantised once outside the timed region"}
+            line["parity"] = {"tokens_checked": n, "max_abs": float(err.max()), "mean_abs": float(err.mean()),
+                              "tolerance": {"max_abs": 2e-2, "mean_abs": 2e-3}}
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

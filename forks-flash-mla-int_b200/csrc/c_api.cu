@@ -1,0 +1,126 @@
+// extern "C" entry points of the sparse-MLA library (declared in include/sparse_mla_b200.h).
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdlib>
+
+#include "smla_internal.h"
+
+namespace {
+
+struct DevInfo {
+    bool known = false;
+    int major = 0, sm_count = 0;
+};
+DevInfo g_dev[64];
+
+int device_info(DevInfo &out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    DevInfo tmp;
+    DevInfo &d = (dev >= 0 && dev < 64) ? g_dev[dev] : tmp;
+    if (!d.known) {
+        e = cudaDeviceGetAttribute(&d.major, cudaDevAttrComputeCapabilityMajor, dev);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        e = cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        d.known = true;
+    }
+    out = d;
+    return SMLA_OK;
+}
+
+int max_width(const smla_attn_params_t &p) { return p.swa.topk + (p.extra.cache ? p.extra.topk : 0); }
+
+}  // namespace
+
+extern "C" {
+
+const char *smla_version(void) { return "sparse_mla_b200 0.1 (sm_100a)"; }
+
+const char *smla_error_string(int code) {
+    switch (code) {
+        case SMLA_OK: return "ok";
+        case SMLA_EINVAL: return "invalid argument (null pointer, bad size or unknown enum)";
+        case SMLA_EALIGN: return "unsupported pointer or stride alignment";
+        case SMLA_EWORKSPACE: return "split-KV workspace missing or too small";
+        case SMLA_EARCH: return "the current device is not compute capability 10.x (B200 / sm_100a)";
+        case SMLA_ETOOBIG: return "request exceeds a fixed capacity of this entry point";
+        default: break;
+    }
+    if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));
+    return "unknown error";
+}
+
+int smla_choose_num_splits(int sm_count, int num_tokens, int num_heads, int max_width_rows) {
+    // One CTA per (token, block of 64 heads) occupies one SM; splits only fill SMs that would
+    // otherwise idle, and a split never gets less than one 128-row tile.
+    int rows_per_split = 128;
+    if (const char *e = getenv("FLASH_MLA_SLOTS_PER_SPLIT")) {
+        const int v = atoi(e);
+        if (v > 0) rows_per_split = ((v + 127) / 128) * 128;
+    }
+    const int head_blocks = (num_heads + 63) / 64;
+    const long long ctas = static_cast<long long>(std::max(num_tokens, 1)) * head_blocks;
+    const int by_sms = static_cast<int>(std::max<long long>(1, sm_count / ctas));
+    const int by_rows = std::max(1, (max_width_rows + rows_per_split - 1) / rows_per_split);
+    return std::max(1, std::min(std::min(by_sms, by_rows), 64));
+}
+
+size_t smla_attn_workspace_bytes(int num_tokens, int num_heads, int num_splits) {
+    if (num_splits <= 1 || num_tokens <= 0 || num_heads <= 0) return 0;
+    return static_cast<size_t>(num_tokens) * num_heads * num_splits * (SMLA_HEAD_DIM + 2) * sizeof(float);
+}
+
+int smla_decode_plan(int num_tokens, int num_heads, int max_width_rows, int *num_splits, size_t *workspace_bytes) {
+    DevInfo d;
+    const int rc = device_info(d);
+    if (rc != SMLA_OK) return rc;
+    if (d.major != 10) return SMLA_EARCH;
+    const int s = smla_choose_num_splits(d.sm_count, num_tokens, num_heads, max_width_rows);
+    if (num_splits) *num_splits = s;
+    if (workspace_bytes) *workspace_bytes = smla_attn_workspace_bytes(num_tokens, num_heads, s);
+    return SMLA_OK;
+}
+
+int smla_sparse_mla_decode(const smla_attn_params_t *p, void *stream) {
+    if (!p) return SMLA_EINVAL;
+    DevInfo d;
+    int rc = device_info(d);
+    if (rc != SMLA_OK) return rc;
+    if (d.major != 10) return SMLA_EARCH;
+    int splits = p->num_splits;
+    if (splits < 0) return SMLA_EINVAL;
+    if (splits == 0) {
+        splits = smla_choose_num_splits(d.sm_count, p->num_tokens, p->num_heads, max_width(*p));
+        // Without scratch the automatic policy degrades to one split instead of failing.
+        if (splits > 1 && (!p->workspace ||
+                           p->workspace_bytes < smla_attn_workspace_bytes(p->num_tokens, p->num_heads, splits)))
+            splits = 1;
+    } else if (splits > 1) {
+        if (!p->workspace || p->workspace_bytes < smla_attn_workspace_bytes(p->num_tokens, p->num_heads, splits))
+            return SMLA_EWORKSPACE;
+    }
+    return smla::launch_sparse_mla_attention(*p, splits, p->workspace, static_cast<cudaStream_t>(stream));
+}
+
+int smla_sparse_mla_prefill(const smla_attn_params_t *p, void *stream) {
+    if (!p) return SMLA_EINVAL;
+    DevInfo d;
+    int rc = device_info(d);
+    if (rc != SMLA_OK) return rc;
+    if (d.major != 10) return SMLA_EARCH;
+    if (max_width(*p) <= 0) return SMLA_EINVAL;   // "prefill requires at least one selected slot"
+    return smla::launch_sparse_mla_attention(*p, 1, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+int smla_quantize_int8_ds_mla_rows(const void *x, int x_dtype, int64_t rows, int64_t x_row_stride, int8_t *q,
+                                   float *scale, void *stream) {
+    return smla::launch_quantize_int8_rows(x, x_dtype, rows, x_row_stride, q, scale,
+                                           static_cast<cudaStream_t>(stream));
+}
+
+int smla_read_device_status(int *status_out) { return smla::read_and_clear_device_status(status_out); }
+
+}  // extern "C"

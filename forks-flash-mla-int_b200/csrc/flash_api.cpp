@@ -1,0 +1,309 @@
+// torch-stable-ABI host binding of the B200 sparse-MLA library.
+//
+// Registers the operator schemas of the reference binding for the sparse path
+// (csrc/flash_api.cpp:810-838 of AppMana/forks-flash-mla-int):
+//   flash_mla::fwd_sparse_decode_mla, fwd_sparse_prefill_mla,
+//   flash_mla::fwd_sparse_int8_decode_mla, fwd_sparse_int8_prefill_mla
+// plus flash_mla::quantize_int8_ds_mla_rows (a torch composite in the reference,
+// flash_mla/int8_sparse_mla.py:15-26; a CUDA kernel here).  Only torch/csrc/stable, the AOTI
+// shim and torch/headeronly are used -- no ATen, c10 or pybind -- and every op validates its
+// arguments, allocates its output (and split-KV scratch) with torch's allocator on q's device,
+// and forwards plain pointers to the C ABI in include/sparse_mla_b200.h on the current stream.
+// Nothing here synchronises, so the ops stay CUDA-graph capturable.
+#include <Python.h>
+#include <torch/csrc/inductor/aoti_torch/c/shim.h>
+#include <torch/csrc/stable/accelerator.h>
+#include <torch/csrc/stable/library.h>
+#include <torch/csrc/stable/ops.h>
+#include <torch/csrc/stable/tensor.h>
+#include <torch/headeronly/util/Exception.h>
+
+#include <cstdint>
+#include <optional>
+#include <string>
+#include <vector>
+
+#include "sparse_mla_b200.h"
+
+using torch::headeronly::ScalarType;
+using torch::stable::Tensor;
+
+namespace {
+
+void *current_stream(int device) {
+    void *s = nullptr;
+    TORCH_ERROR_CODE_CHECK(aoti_torch_get_current_cuda_stream(device, &s));
+    return s;
+}
+
+void check_rc(int rc, const char *what) {
+    STD_TORCH_CHECK(rc == 0, what, " failed: ", smla_error_string(rc), " (code ", rc, ")");
+}
+
+bool aligned16(const Tensor &t) { return (reinterpret_cast<uintptr_t>(t.data_ptr()) & 15u) == 0; }
+
+// q / out style [T, H, 512] bf16 tensor the kernels can read with 16-byte loads.
+Tensor as_kernel_q(const Tensor &q) {
+    if (q.stride(2) == 1 && q.stride(0) % 8 == 0 && q.stride(1) % 8 == 0 && aligned16(q)) return q;
+    return torch::stable::contiguous(q);
+}
+
+Tensor as_index_rows(const Tensor &idx, const char *name) {
+    STD_TORCH_CHECK(idx.dim() == 2, name, " must have shape (num_tokens, topk)");
+    STD_TORCH_CHECK(idx.scalar_type() == ScalarType::Int, name, " must be int32");
+    if (idx.size(1) <= 1 || idx.stride(1) == 1) return idx;
+    return torch::stable::contiguous(idx);
+}
+
+struct StreamTensors {   // keeps the (possibly re-laid-out) tensors alive until the launch returns
+    std::optional<Tensor> indices, lens;
+};
+
+void fill_stream(smla_stream_t &s, StreamTensors &keep, int T, const char *name, const Tensor &cache,
+                 const std::optional<Tensor> &scale, const Tensor &indices, const Tensor &lens, bool int8) {
+    STD_TORCH_CHECK(cache.is_cuda() && indices.is_cuda() && lens.is_cuda(), name, " tensors must be on CUDA");
+    STD_TORCH_CHECK(cache.dim() == 3, name, "_cache must be [num_blocks, block_size, bytes]");
+    keep.indices = as_index_rows(indices, name);
+    STD_TORCH_CHECK(keep.indices->size(0) == T, name, "_indices must have one row per query token");
+    STD_TORCH_CHECK(lens.scalar_type() == ScalarType::Int, name, "_lens must be int32");
+    STD_TORCH_CHECK(lens.dim() == 1 && lens.size(0) == T, name, "_lens must have shape (num_tokens,)");
+    keep.lens = lens.is_contiguous() ? lens : torch::stable::contiguous(lens);
+    s.cache = cache.data_ptr();
+    s.indices = static_cast<const int32_t *>(keep.indices->data_ptr());
+    s.lens = static_cast<const int32_t *>(keep.lens->data_ptr());
+    s.indices_stride = keep.indices->size(0) > 1 ? keep.indices->stride(0) : keep.indices->size(1);
+    s.topk = static_cast<int32_t>(keep.indices->size(1));
+    s.num_blocks = static_cast<int32_t>(cache.size(0));
+    s.block_size = static_cast<int32_t>(cache.size(1));
+    s.block_stride = cache.stride(0) * static_cast<int64_t>(cache.element_size());
+    if (int8) {
+        STD_TORCH_CHECK(cache.scalar_type() == ScalarType::Char, name, "_cache must be int8");
+        STD_TORCH_CHECK(cache.size(2) == 512, "int8 cache payload must be 512 bytes/token");
+        STD_TORCH_CHECK(cache.stride(2) == 1, name, "_cache rows must be contiguous");
+        STD_TORCH_CHECK(scale.has_value(), name, "_scale is required for an int8 cache");
+        const Tensor &sc = scale.value();
+        STD_TORCH_CHECK(sc.is_cuda(), name, "_scale must be on CUDA");
+        STD_TORCH_CHECK(sc.scalar_type() == ScalarType::Float, name, "_scale must be float32");
+        STD_TORCH_CHECK(sc.dim() == 2 && sc.size(0) == cache.size(0) && sc.size(1) == cache.size(1), name,
+                        "_scale must have shape (num_blocks, block_size)");
+        s.scale = static_cast<const float *>(sc.data_ptr());
+        s.pos_stride = cache.stride(1);
+        s.scale_block_stride = sc.stride(0);
+        s.scale_pos_stride = sc.stride(1);
+    } else {
+        STD_TORCH_CHECK(cache.scalar_type() == ScalarType::Byte, name, "_cache must be uint8");
+        STD_TORCH_CHECK(cache.size(2) == 584 && cache.stride(2) == 1 && cache.stride(1) == 584, name,
+                        "_cache must be fp8_ds_mla [num_blocks, block_size, 584] with contiguous blocks");
+        s.scale = nullptr;
+        s.pos_stride = 576;
+    }
+}
+
+Tensor sparse_mla_forward(const char *what, bool int8, bool prefill, const Tensor &q_in, const Tensor &swa_cache,
+                          const std::optional<Tensor> &swa_scale, const Tensor &swa_indices,
+                          const Tensor &swa_lens, double scale, const std::optional<Tensor> &attn_sink,
+                          const std::optional<Tensor> &extra_cache, const std::optional<Tensor> &extra_scale,
+                          const std::optional<Tensor> &extra_indices, const std::optional<Tensor> &extra_lens) {
+    STD_TORCH_CHECK(q_in.is_cuda(), "q must be on CUDA");
+    STD_TORCH_CHECK(q_in.dim() == 3, "q must have shape (num_tokens, num_heads, 512)");
+    STD_TORCH_CHECK(q_in.size(2) == 512, "head_dim must be 512");
+    STD_TORCH_CHECK(q_in.scalar_type() == ScalarType::BFloat16, "q must be bfloat16");
+    const int device = q_in.get_device_index();
+    torch::stable::accelerator::DeviceGuard guard(device);
+
+    const Tensor q = as_kernel_q(q_in);
+    const int64_t T = q.size(0), H = q.size(1);
+    STD_TORCH_CHECK(H >= 1, "q must have at least one head");
+    Tensor out = torch::stable::new_empty(q, {T, H, 512});
+    if (T == 0) return out;
+
+    smla_attn_params_t p = {};
+    p.num_tokens = static_cast<int32_t>(T);
+    p.num_heads = static_cast<int32_t>(H);
+    p.cache_format = int8 ? SMLA_INT8_DS_MLA : SMLA_FP8_DS_MLA;
+    p.softmax_scale = static_cast<float>(scale);
+    p.q = q.data_ptr();
+    p.q_token_stride = q.stride(0);
+    p.q_head_stride = q.stride(1);
+    p.out = out.data_ptr();
+    p.out_token_stride = out.stride(0);
+    p.out_head_stride = out.stride(1);
+    std::optional<Tensor> sink_keep;
+    if (attn_sink.has_value()) {
+        const Tensor &sk = attn_sink.value();
+        STD_TORCH_CHECK(sk.is_cuda(), "attn_sink must be on CUDA");
+        STD_TORCH_CHECK(sk.scalar_type() == ScalarType::Float, "attn_sink must be float32");
+        STD_TORCH_CHECK(sk.dim() == 1 && sk.size(0) == H, "attn_sink must have shape (num_heads,)");
+        sink_keep = sk.is_contiguous() ? sk : torch::stable::contiguous(sk);
+        p.attn_sink = static_cast<const float *>(sink_keep->data_ptr());
+    }
+    StreamTensors swa_keep, extra_keep;
+    fill_stream(p.swa, swa_keep, static_cast<int>(T), "swa", swa_cache, swa_scale, swa_indices, swa_lens, int8);
+    if (extra_cache.has_value()) {
+        STD_TORCH_CHECK(extra_indices.has_value() && extra_lens.has_value() && (!int8 || extra_scale.has_value()),
+                        int8 ? "extra scale/indices/lens required with extra cache"
+                             : "extra indices/lens required with extra cache");
+        fill_stream(p.extra, extra_keep, static_cast<int>(T), "extra", extra_cache.value(), extra_scale,
+                    extra_indices.value(), extra_lens.value(), int8);
+    }
+    const int width = p.swa.topk + (extra_cache.has_value() ? p.extra.topk : 0);
+
+    void *stream = current_stream(device);
+    int rc;
+    std::optional<Tensor> workspace;   // split-KV scratch; freed stream-ordered by torch's allocator
+    if (prefill) {
+        STD_TORCH_CHECK(width > 0, "prefill requires at least one selected slot");
+        rc = smla_sparse_mla_prefill(&p, stream);
+    } else {
+        int splits = 1;
+        size_t ws_bytes = 0;
+        check_rc(smla_decode_plan(p.num_tokens, p.num_heads, width, &splits, &ws_bytes), "sparse-MLA decode plan");
+        if (splits > 1) {
+            workspace = torch::stable::new_empty(q, {static_cast<int64_t>((ws_bytes + 3) / 4)}, ScalarType::Float);
+            p.workspace = workspace->data_ptr();
+            p.workspace_bytes = ws_bytes;
+        }
+        p.num_splits = splits;
+        rc = smla_sparse_mla_decode(&p, stream);
+    }
+    check_rc(rc, what);
+    return out;
+}
+
+Tensor fwd_sparse_decode_mla(Tensor q, Tensor swa_cache, Tensor swa_indices, Tensor swa_lens, double scale,
+                             std::optional<Tensor> attn_sink, std::optional<Tensor> extra_cache,
+                             std::optional<Tensor> extra_indices, std::optional<Tensor> extra_lens) {
+    return sparse_mla_forward("sparse-MLA fp8 decode", false, false, q, swa_cache, std::nullopt, swa_indices,
+                              swa_lens, scale, attn_sink, extra_cache, std::nullopt, extra_indices, extra_lens);
+}
+Tensor fwd_sparse_prefill_mla(Tensor q, Tensor swa_cache, Tensor swa_indices, Tensor swa_lens, double scale,
+                              std::optional<Tensor> attn_sink, std::optional<Tensor> extra_cache,
+                              std::optional<Tensor> extra_indices, std::optional<Tensor> extra_lens) {
+    return sparse_mla_forward("sparse-MLA fp8 prefill", false, true, q, swa_cache, std::nullopt, swa_indices,
+                              swa_lens, scale, attn_sink, extra_cache, std::nullopt, extra_indices, extra_lens);
+}
+Tensor fwd_sparse_int8_decode_mla(Tensor q, Tensor swa_cache, Tensor swa_scale, Tensor swa_indices,
+                                  Tensor swa_lens, double scale, std::optional<Tensor> attn_sink,
+                                  std::optional<Tensor> extra_cache, std::optional<Tensor> extra_scale,
+                                  std::optional<Tensor> extra_indices, std::optional<Tensor> extra_lens) {
+    return sparse_mla_forward("sparse-MLA int8 decode", true, false, q, swa_cache, swa_scale, swa_indices, swa_lens,
+                              scale, attn_sink, extra_cache, extra_scale, extra_indices, extra_lens);
+}
+Tensor fwd_sparse_int8_prefill_mla(Tensor q, Tensor swa_cache, Tensor swa_scale, Tensor swa_indices,
+                                   Tensor swa_lens, double scale, std::optional<Tensor> attn_sink,
+                                   std::optional<Tensor> extra_cache, std::optional<Tensor> extra_scale,
+                                   std::optional<Tensor> extra_indices, std::optional<Tensor> extra_lens) {
+    return sparse_mla_forward("sparse-MLA int8 prefill", true, true, q, swa_cache, swa_scale, swa_indices, swa_lens,
+                              scale, attn_sink, extra_cache, extra_scale, extra_indices, extra_lens);
+}
+
+// k: [..., 512] bf16 / fp16 / fp32 on CUDA -> (int8 [..., 512], fp32 [...]).
+void quantize_int8_ds_mla_rows(const Tensor &k_in, Tensor &q_out, Tensor &scale_out) {
+    STD_TORCH_CHECK(k_in.is_cuda(), "k must be on CUDA");
+    STD_TORCH_CHECK(k_in.dim() >= 1 && k_in.size(k_in.dim() - 1) == 512, "expected last dim 512");
+    int dtype = -1;
+    switch (k_in.scalar_type()) {
+        case ScalarType::BFloat16: dtype = 0; break;
+        case ScalarType::Half: dtype = 1; break;
+        case ScalarType::Float: dtype = 2; break;
+        default: STD_TORCH_CHECK(false, "k must be bfloat16, float16 or float32");
+    }
+    const int device = k_in.get_device_index();
+    torch::stable::accelerator::DeviceGuard guard(device);
+    const Tensor k = (k_in.is_contiguous() && aligned16(k_in)) ? k_in : torch::stable::contiguous(k_in);
+    const int64_t rows = k.numel() / 512;
+    std::vector<int64_t> qs, ss;
+    for (int64_t i = 0; i < k.dim(); ++i) qs.push_back(k.size(i));
+    for (int64_t i = 0; i + 1 < k.dim(); ++i) ss.push_back(k.size(i));
+    q_out = torch::stable::new_empty(k, torch::headeronly::IntHeaderOnlyArrayRef(qs.data(), qs.size()),
+                                     ScalarType::Char);
+    scale_out = torch::stable::new_empty(k, torch::headeronly::IntHeaderOnlyArrayRef(ss.data(), ss.size()),
+                                         ScalarType::Float);
+    check_rc(smla_quantize_int8_ds_mla_rows(k.data_ptr(), dtype, rows, 512, static_cast<int8_t *>(q_out.data_ptr()),
+                                            static_cast<float *>(scale_out.data_ptr()), current_stream(device)),
+             "int8_ds_mla row quantizer");
+}
+
+// ------------------------------------------------------------------ boxed shims
+using torch::stable::detail::from;
+using torch::stable::detail::to;
+
+template <bool PREFILL>
+void boxed_fp8(StableIValue *stack, uint64_t, uint64_t) {
+    auto q = to<Tensor>(stack[0]);
+    auto swa_cache = to<Tensor>(stack[1]);
+    auto swa_indices = to<Tensor>(stack[2]);
+    auto swa_lens = to<Tensor>(stack[3]);
+    auto scale = to<double>(stack[4]);
+    auto attn_sink = to<std::optional<Tensor>>(stack[5]);
+    auto extra_cache = to<std::optional<Tensor>>(stack[6]);
+    auto extra_indices = to<std::optional<Tensor>>(stack[7]);
+    auto extra_lens = to<std::optional<Tensor>>(stack[8]);
+    Tensor res = PREFILL ? fwd_sparse_prefill_mla(q, swa_cache, swa_indices, swa_lens, scale, attn_sink, extra_cache,
+                                                  extra_indices, extra_lens)
+                         : fwd_sparse_decode_mla(q, swa_cache, swa_indices, swa_lens, scale, attn_sink, extra_cache,
+                                                 extra_indices, extra_lens);
+    stack[0] = from(res);
+}
+
+template <bool PREFILL>
+void boxed_int8(StableIValue *stack, uint64_t, uint64_t) {
+    auto q = to<Tensor>(stack[0]);
+    auto swa_cache = to<Tensor>(stack[1]);
+    auto swa_scale = to<Tensor>(stack[2]);
+    auto swa_indices = to<Tensor>(stack[3]);
+    auto swa_lens = to<Tensor>(stack[4]);
+    auto scale = to<double>(stack[5]);
+    auto attn_sink = to<std::optional<Tensor>>(stack[6]);
+    auto extra_cache = to<std::optional<Tensor>>(stack[7]);
+    auto extra_scale = to<std::optional<Tensor>>(stack[8]);
+    auto extra_indices = to<std::optional<Tensor>>(stack[9]);
+    auto extra_lens = to<std::optional<Tensor>>(stack[10]);
+    Tensor res = PREFILL ? fwd_sparse_int8_prefill_mla(q, swa_cache, swa_scale, swa_indices, swa_lens, scale,
+                                                       attn_sink, extra_cache, extra_scale, extra_indices, extra_lens)
+                         : fwd_sparse_int8_decode_mla(q, swa_cache, swa_scale, swa_indices, swa_lens, scale,
+                                                      attn_sink, extra_cache, extra_scale, extra_indices, extra_lens);
+    stack[0] = from(res);
+}
+
+void boxed_quantize(StableIValue *stack, uint64_t, uint64_t) {
+    auto k = to<Tensor>(stack[0]);
+    Tensor q, s;
+    quantize_int8_ds_mla_rows(k, q, s);
+    stack[0] = from(q);
+    stack[1] = from(s);
+}
+
+}  // namespace
+
+STABLE_TORCH_LIBRARY(flash_mla, m) {
+    m.def("fwd_sparse_decode_mla(Tensor q, Tensor swa_cache, Tensor swa_indices, Tensor swa_lens, "
+          "float scale, Tensor? attn_sink, Tensor? extra_cache, Tensor? extra_indices, "
+          "Tensor? extra_lens) -> Tensor");
+    m.def("fwd_sparse_prefill_mla(Tensor q, Tensor swa_cache, Tensor swa_indices, Tensor swa_lens, "
+          "float scale, Tensor? attn_sink, Tensor? extra_cache, Tensor? extra_indices, "
+          "Tensor? extra_lens) -> Tensor");
+    m.def("fwd_sparse_int8_prefill_mla(Tensor q, Tensor swa_cache, Tensor swa_scale, "
+          "Tensor swa_indices, Tensor swa_lens, float scale, Tensor? attn_sink, "
+          "Tensor? extra_cache, Tensor? extra_scale, Tensor? extra_indices, Tensor? extra_lens) -> Tensor");
+    m.def("fwd_sparse_int8_decode_mla(Tensor q, Tensor swa_cache, Tensor swa_scale, "
+          "Tensor swa_indices, Tensor swa_lens, float scale, Tensor? attn_sink, "
+          "Tensor? extra_cache, Tensor? extra_scale, Tensor? extra_indices, Tensor? extra_lens) -> Tensor");
+    m.def("quantize_int8_ds_mla_rows(Tensor k) -> (Tensor, Tensor)");
+}
+
+STABLE_TORCH_LIBRARY_IMPL(flash_mla, CUDA, m) {
+    m.impl("fwd_sparse_decode_mla", &boxed_fp8<false>);
+    m.impl("fwd_sparse_prefill_mla", &boxed_fp8<true>);
+    m.impl("fwd_sparse_int8_prefill_mla", &boxed_int8<true>);
+    m.impl("fwd_sparse_int8_decode_mla", &boxed_int8<false>);
+    m.impl("quantize_int8_ds_mla_rows", &boxed_quantize);
+}
+
+// `import flash_mla_cuda` only has to load this library so the static registrars above run.
+extern "C" {
+__attribute__((visibility("default"))) PyObject *PyInit_flash_mla_cuda(void) {
+    static struct PyModuleDef module_def = {PyModuleDef_HEAD_INIT, "flash_mla_cuda", nullptr, -1, nullptr};
+    return PyModule_Create(&module_def);
+}
+}

@@ -1,0 +1,29 @@
+"""flash_mla for B200 (sm_100a): the sparse-MLA path of AppMana/forks-flash-mla-int.
+
+Same names and argument contract as the reference package (flash_mla/__init__.py:3-15) for
+the sparse ops and the int8 row quantizer.  The dense-MLA entry points and the Triton decoder
+(``get_mla_metadata``, ``flash_mla_with_kvcache``, ``flash_mla_with_kvcache_int8``,
+``sparse_mla_decode_int8_triton``) are not part of this library.
+
+Importing the package loads the compiled extension; there is no CPU or eager fallback -- a
+missing library raises ImportError.
+"""
+__version__ = "2.0.0+b200"
+
+from .flash_mla_interface import (  # noqa: F401
+    sparse_mla_decode_fp8,
+    sparse_mla_prefill,
+)
+from .int8_sparse_mla import (  # noqa: F401
+    quantize_int8_ds_mla_rows,
+    sparse_mla_decode_int8,
+    sparse_mla_prefill_int8,
+)
+
+__all__ = [
+    "sparse_mla_decode_fp8",
+    "sparse_mla_prefill",
+    "sparse_mla_decode_int8",
+    "sparse_mla_prefill_int8",
+    "quantize_int8_ds_mla_rows",
+]

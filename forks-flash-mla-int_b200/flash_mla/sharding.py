@@ -1,0 +1,50 @@
+"""Token sharding for multi-GPU runs: every query token is independent (no cross-token reduction),
+so a batch splits into contiguous token ranges, one per rank, with the caches replicated (or
+batch-partitioned by the caller) and NO collective on the data path.  Outputs stay on the rank
+that owns the tokens; ``gather_outputs`` is a convenience for harnesses that want one tensor."""
+from __future__ import annotations
+
+from typing import Dict, Tuple
+
+import torch
+
+TOKEN_KEYS = ("q", "swa_indices", "swa_lens", "extra_indices", "extra_lens")
+
+
+def token_range(num_tokens: int, world_size: int, rank: int) -> Tuple[int, int]:
+    """Contiguous [start, stop) of rank `rank`; the first ``num_tokens % world_size`` ranks get one more."""
+    if world_size < 1 or not 0 <= rank < world_size:
+        raise ValueError(f"bad rank {rank} / world size {world_size}")
+    base, rem = divmod(num_tokens, world_size)
+    start = rank * base + min(rank, rem)
+    return start, start + base + (1 if rank < rem else 0)
+
+
+def shard_tokens(kwargs: Dict[str, object], world_size: int, rank: int) -> Dict[str, object]:
+    """Slice the per-token arguments of a sparse-MLA call to this rank's token range; cache, scale
+    and attn_sink arguments are passed through untouched (replicated)."""
+    T = kwargs["q"].shape[0]
+    a, b = token_range(T, world_size, rank)
+    out = dict(kwargs)
+    for k in TOKEN_KEYS:
+        v = kwargs.get(k)
+        if v is not None:
+            if v.shape[0] != T:
+                raise ValueError(f"{k} has {v.shape[0]} rows, expected {T}")
+            out[k] = v[a:b]
+    return out
+
+
+def gather_outputs(local_out: torch.Tensor, num_tokens: int, group=None) -> torch.Tensor:
+    """all_gather of ragged token shards into [num_tokens, H, 512] (outside any timed region)."""
+    import torch.distributed as dist
+    world = dist.get_world_size(group)
+    shards = []
+    for r in range(world):
+        a, b = token_range(num_tokens, world, r)
+        shards.append(torch.empty((b - a,) + tuple(local_out.shape[1:]), dtype=local_out.dtype,
+                                  device=local_out.device))
+    dist.all_gather(shards, local_out.contiguous(), group=group) if len({s.shape for s in shards}) == 1 else \
+        [dist.broadcast(s if r != dist.get_rank(group) else s.copy_(local_out), src=dist.get_global_rank(group, r) if group else r, group=group)
+         for r, s in enumerate(shards)]
+    return torch.cat(shards, dim=0)

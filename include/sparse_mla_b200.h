@@ -1,0 +1,127 @@
+/* sparse_mla_b200.h -- C ABI of the B200 (sm_100a) sparse-MLA library.
+ *
+ * Plain pointers and sizes only: every pointer is a DEVICE pointer on the device that is
+ * current when the function is called, `stream` is a cudaStream_t passed as void*.  All
+ * functions are asynchronous on `stream`, never synchronise, never allocate, and return 0 on
+ * success, a negative SMLA_E* code for a rejected argument, or a positive cudaError_t when a
+ * launch failed.  Inputs are borrowed and never written.
+ *
+ * Each entry point names the reference interface (AppMana/forks-flash-mla-int, path within
+ * that project) it replaces.
+ */
+#ifndef SPARSE_MLA_B200_H_
+#define SPARSE_MLA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SMLA_HEAD_DIM 512
+
+#if defined(__GNUC__)
+#define SMLA_API __attribute__((visibility("default")))
+#else
+#define SMLA_API
+#endif
+
+enum smla_cache_format {
+    SMLA_FP8_DS_MLA = 0,  /* uint8 [nb, bs, 584]: per block [bs x 576 data][bs x 8 scale] */
+    SMLA_INT8_DS_MLA = 1  /* int8 [nb, bs, 512] + fp32 scale [nb, bs], runtime strides     */
+};
+
+enum smla_error {
+    SMLA_OK = 0,
+    SMLA_EINVAL = -1,     /* null pointer / non-positive size / unknown enum            */
+    SMLA_EALIGN = -2,     /* pointer or stride alignment the kernels cannot gather from */
+    SMLA_EWORKSPACE = -3, /* workspace missing or too small for the requested splits    */
+    SMLA_EARCH = -4,      /* current device is not compute capability 10.x              */
+    SMLA_ETOOBIG = -5     /* request exceeds a fixed capacity of the entry point         */
+};
+
+/* One index stream of the selection (the sliding-window "swa" cache or the optional
+ * compressed "extra" cache).  Mirrors the per-stream fields of Sparse_mla_decode_params /
+ * Sparse_mla_prefill_params (csrc/flash_mla.h:73-115, 127-152). */
+typedef struct smla_stream {
+    const void *cache;          /* NULL = stream absent (extra only)                         */
+    const float *scale;         /* int8_ds_mla: fp32 [nb, bs]; NULL for fp8_ds_mla            */
+    const int32_t *indices;     /* int32 [T, topk] slot ids; <0 or >= nb*bs = zero row         */
+    const int32_t *lens;        /* int32 [T], rows of `indices` that take part (<= topk)      */
+    int64_t indices_stride;     /* elements between consecutive tokens' index rows           */
+    int32_t topk;
+    int32_t num_blocks;
+    int32_t block_size;
+    int64_t block_stride;       /* bytes between paged blocks                                 */
+    int64_t pos_stride;         /* int8: bytes between tokens of a block (512, 528, ...)       */
+    int64_t scale_block_stride; /* int8: elements                                             */
+    int64_t scale_pos_stride;   /* int8: elements                                             */
+} smla_stream_t;
+
+/* Launch contract of the attention kernels.  Replaces Sparse_mla_decode_params and
+ * Sparse_mla_prefill_params (csrc/flash_mla.h:73-115, 127-152); the reference's dense
+ * selection scratch (sel_kv_ptr) and whole-cache dequant buffer (kv_ptr) have no
+ * counterpart because rows are gathered and dequantised inside the attention kernel. */
+typedef struct smla_attn_params {
+    int32_t num_tokens;         /* T */
+    int32_t num_heads;          /* H */
+    int32_t cache_format;       /* enum smla_cache_format, both streams                       */
+    float softmax_scale;        /* natural-log units (the library multiplies by log2 e)        */
+    const void *q;              /* bf16 [T, H, 512], innermost stride 1, 16-byte aligned rows  */
+    int64_t q_token_stride, q_head_stride;     /* elements */
+    void *out;                  /* bf16 [T, H, 512] */
+    int64_t out_token_stride, out_head_stride; /* elements */
+    const float *attn_sink;     /* fp32 [H] natural-log logits, or NULL                        */
+    smla_stream_t swa;
+    smla_stream_t extra;        /* extra.cache == NULL when absent                            */
+    int32_t num_splits;         /* split-KV count; 0 = let the library choose                  */
+    void *workspace;            /* >= smla_attn_workspace_bytes(...) when splits > 1, else NULL */
+    size_t workspace_bytes;
+} smla_attn_params_t;
+
+/* Library version string. */
+SMLA_API const char *smla_version(void);
+
+/* Human-readable text for a return code of this library (negative) or of CUDA (positive). */
+SMLA_API const char *smla_error_string(int code);
+
+/* Split-KV policy: how many splits smla_sparse_mla_decode would use for this problem on a
+ * device with `sm_count` SMs.  Counterpart of sparse_mla_num_splits (csrc/flash_api.cpp:75-102);
+ * the environment variable FLASH_MLA_SLOTS_PER_SPLIT is honoured the same way (read per call). */
+SMLA_API int smla_choose_num_splits(int sm_count, int num_tokens, int num_heads, int max_width);
+
+/* Bytes of split-KV scratch (fp32 partial outputs + {max, denominator} pairs) for `num_splits`
+ * splits; 0 when num_splits <= 1.  Counterpart of the oaccum/mlse tensors allocated at
+ * csrc/flash_api.cpp:388-400. */
+SMLA_API size_t smla_attn_workspace_bytes(int num_tokens, int num_heads, int num_splits);
+
+/* Split count smla_sparse_mla_decode would pick on the CURRENT device (queries its SM count) and
+ * the scratch bytes that count needs; what the reference binding computes inline at
+ * csrc/flash_api.cpp:381-405 before it allocates oaccum / mlse. */
+SMLA_API int smla_decode_plan(int num_tokens, int num_heads, int max_width, int *num_splits, size_t *workspace_bytes);
+
+/* Sparse MLA decode.  Replaces run_sparse_mla_decode (csrc/flash_mla.h:125,
+ * csrc/flash_sparse_mla_decode_sm80.cu:1198-1275) for both cache formats. */
+SMLA_API int smla_sparse_mla_decode(const smla_attn_params_t *params, void *stream);
+
+/* Sparse MLA prefill (many query tokens, never split).  Replaces run_sparse_mla_prefill
+ * (csrc/flash_mla.h:159-160, csrc/flash_sparse_mla_prefill_fused_sm80.cu:468-506). */
+SMLA_API int smla_sparse_mla_prefill(const smla_attn_params_t *params, void *stream);
+
+/* int8_ds_mla row quantizer, bit-exact with quantize_int8_ds_mla_rows
+ * (flash_mla/int8_sparse_mla.py:15-26): scale = max(amax|x|, 1e-12) / 127 and
+ * q = clamp(rint(x / scale), -127, 127) in IEEE fp32.
+ *   x: [rows, 512] of `x_dtype` (0 = bf16, 1 = fp16, 2 = fp32), `x_row_stride` elements apart;
+ *   q: int8 [rows, 512] contiguous; scale: fp32 [rows]. */
+SMLA_API int smla_quantize_int8_ds_mla_rows(const void *x, int x_dtype, int64_t rows, int64_t x_row_stride,
+                                   int8_t *q, float *scale, void *stream);
+
+/* Reads and clears the per-device error word the kernels set when a bounded wait ran out
+ * (0 = none).  Synchronises the device; meant for tests and debugging, not for hot paths. */
+SMLA_API int smla_read_device_status(int *status_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SPARSE_MLA_B200_H_ */

@@ -1,0 +1,369 @@
+"""GPU parity tests: the sm_100a kernels, called through the reference-shaped Python API (which
+forwards to the C ABI), against the golden fixtures and against the CPU oracle on the same
+seeded inputs.  The cases mirror the reference's own sparse tests:
+tests/test_sparse_mla_decode_sm86.py, tests/test_sparse_mla_prefill_adversarial.py,
+tests/test_sparse_mla_decode_int8_adversarial.py, tests/test_sparse_mla_prefill_int8_adversarial.py.
+"""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import (assert_attention_close, bf16_from_bits, device_status, fp8_cache_from_latent,
+                     int8_cache_from_latent, oracle_out, to_dev)
+import oracle
+
+pytestmark = pytest.mark.gpu
+SCALE = 1.0 / math.sqrt(512)
+
+
+@pytest.fixture(scope="module")
+def fm():
+    import flash_mla
+    return flash_mla
+
+
+@pytest.fixture(autouse=True)
+def _status_clean():
+    yield
+    assert device_status() == 0, "a kernel wait ran out (device status word set)"
+
+
+# ----------------------------------------------------------------------------- golden fixtures
+def test_quantizer_golden(fm, golden):
+    g = golden("quantizer_kat.npz")
+    x = bf16_from_bits(g["x_bf16"])
+    q, s = fm.quantize_int8_ds_mla_rows(x)
+    assert q.dtype == torch.int8 and s.dtype == torch.float32
+    assert np.array_equal(q.cpu().numpy(), g["q"])
+    assert np.array_equal(s.cpu().numpy().view(np.uint32), g["scale"].view(np.uint32))
+    q3, s3 = fm.quantize_int8_ds_mla_rows(x.view(4, 24, 512))
+    assert q3.shape == (4, 24, 512) and s3.shape == (4, 24)
+    assert torch.equal(q3.view(96, 512), q) and torch.equal(s3.view(96), s)
+    for dt in (torch.float32, torch.float16):
+        xq = x.to(dt)
+        qo, so = oracle.quantize_int8_rows(xq.float().cpu().numpy())
+        qg, sg = fm.quantize_int8_ds_mla_rows(xq)
+        assert np.array_equal(qg.cpu().numpy(), qo) and np.array_equal(sg.cpu().numpy(), so)
+
+
+def test_fp8_single_stream_golden(fm, golden):
+    g = golden("fp8_decode_single.npz")
+    q, cache = bf16_from_bits(g["q"]), to_dev(g["cache"])
+    idx, lens, sink = to_dev(g["idx"]), to_dev(g["lens"]), to_dev(g["sink"])
+    for op in (fm.sparse_mla_decode_fp8, fm.sparse_mla_prefill):
+        out = op(q, cache, idx, lens, scale=float(g["scale"]), attn_sink=sink)
+        assert out.dtype == torch.bfloat16 and out.shape == q.shape
+        assert_attention_close(out, g["out"], f"{op.__name__} sink")
+        out = op(q, cache, idx, lens, scale=float(g["scale"]))
+        assert_attention_close(out, g["out_nosink"], f"{op.__name__} no sink")
+
+
+def test_fp8_two_stream_golden(fm, golden):
+    g = golden("fp8_two_stream.npz")
+    q, sink = bf16_from_bits(g["q"]), to_dev(g["sink"])
+    kw = dict(swa_cache=to_dev(g["swa_cache"]), swa_indices=to_dev(g["swa_idx"]), swa_lens=to_dev(g["swa_lens"]),
+              scale=float(g["scale"]), attn_sink=sink, extra_cache=to_dev(g["extra_cache"]),
+              extra_indices=to_dev(g["extra_idx"]), extra_lens=to_dev(g["extra_lens"]))
+    for op in (fm.sparse_mla_decode_fp8, fm.sparse_mla_prefill):
+        out = op(q, **kw)
+        assert_attention_close(out, g["out"], op.__name__)
+        assert torch.all(out[0] == 0)    # token with no selected rows
+
+
+@pytest.mark.parametrize("layout", ["inline528", "separate"])
+def test_int8_two_stream_golden(fm, golden, layout):
+    g = golden(f"int8_two_stream_{layout}.npz")
+    q, sink = bf16_from_bits(g["q"]), to_dev(g["sink"])
+    if layout == "inline528":   # rebuild the production 528-byte container and its strided views
+        def views(qi, sc, bs):
+            buf = to_dev(oracle.pack_int8_inline528(qi.reshape(-1, 512), sc.reshape(-1), bs))
+            return buf[:, :, :512].view(torch.int8), buf[:, :, 512:516].view(torch.float32).squeeze(-1), buf
+        sq, ss, _k1 = views(g["swa_q"], g["swa_scale"], g["swa_q"].shape[1])
+        eq, es, _k2 = views(g["extra_q"], g["extra_scale"], g["extra_q"].shape[1])
+        assert sq.stride(1) == 528 and ss.stride(1) == 132
+    else:
+        sq, ss, eq, es = to_dev(g["swa_q"]), to_dev(g["swa_scale"]), to_dev(g["extra_q"]), to_dev(g["extra_scale"])
+    for op in (fm.sparse_mla_decode_int8, fm.sparse_mla_prefill_int8):
+        out = op(q, sq, ss, to_dev(g["swa_idx"]), to_dev(g["swa_lens"]), scale=float(g["scale"]), attn_sink=sink,
+                 extra_cache=eq, extra_scale=es, extra_indices=to_dev(g["extra_idx"]),
+                 extra_lens=to_dev(g["extra_lens"]))
+        assert_attention_close(out, g["out"], f"{op.__name__} {layout}")
+
+
+def test_config1_golden(fm, golden):
+    """BASELINE config 1 (T=4, H=16, 4096 slots, top-k 128, ~3 % invalid ids, scale=None, no sink)."""
+    g = golden("config1_cpu_oracle.npz")
+    q, cache, idx, lens = bf16_from_bits(g["q"]), to_dev(g["cache"]), to_dev(g["idx"]), to_dev(g["lens"])
+    for op in (fm.sparse_mla_decode_fp8, fm.sparse_mla_prefill):
+        assert_attention_close(op(q, cache, idx, lens), g["out"], op.__name__)
+
+
+# ----------------------------------------------------------------------------- oracle parity, fp8
+def _rand_latent(rng, n, mult=1.0):
+    return (rng.standard_normal((n, 512)) * mult).astype(np.float32)
+
+
+@pytest.mark.parametrize("H", [16, 32, 48, 64, 128])
+@pytest.mark.parametrize("topk", [256, 512])
+def test_decode_fp8_parity(fm, H, topk):
+    """tests/test_sparse_mla_decode_sm86.py:75-107 (T=2, lens topk and topk-7), widened over H."""
+    rng = np.random.default_rng(H * 1000 + topk)
+    torch.manual_seed(0)
+    slots, bs = topk + 64, 32
+    cache, K = fp8_cache_from_latent(_rand_latent(rng, slots), bs)
+    q = torch.randn(2, H, 512, device="cuda").to(torch.bfloat16)
+    lens = torch.tensor([topk, topk - 7], dtype=torch.int32, device="cuda")
+    idx = torch.stack([torch.randperm(slots, device="cuda")[:topk].int() for _ in range(2)])
+    sink = torch.randn(H, device="cuda") * 0.1
+    ref = oracle_out(q, K, idx, lens, scale=SCALE, sink=sink)
+    out = fm.sparse_mla_decode_fp8(q=q, swa_cache=cache, swa_indices=idx, swa_lens=lens, scale=SCALE, attn_sink=sink)
+    assert_attention_close(out, ref, f"H={H} topk={topk}")
+
+
+@pytest.mark.parametrize("T,swa_bs,extra_bs", [(1, 256, 64), (2, 256, 2), (4, 256, 64), (6, 32, 16), (3, 33, 7)])
+def test_decode_fp8_two_stream_serving_shapes(fm, T, swa_bs, extra_bs):
+    """tests/test_sparse_mla_decode_sm86.py:119-161,247-301: two streams with different block sizes
+    (incl. odd sizes whose rows are only 8-byte aligned), [T,1,topk] indices, sink."""
+    rng = np.random.default_rng(T * 7 + swa_bs)
+    torch.manual_seed(T)
+    H, st, et = 64, 128, 384
+    swa_cache, swa_K = fp8_cache_from_latent(_rand_latent(rng, 600), swa_bs)
+    extra_cache, extra_K = fp8_cache_from_latent(_rand_latent(rng, 700), extra_bs)
+    q = torch.randn(T, H, 512, device="cuda").to(torch.bfloat16)
+    si = torch.randint(0, 600, (T, 1, st), device="cuda", dtype=torch.int32)
+    ei = torch.randint(0, 700, (T, 1, et), device="cuda", dtype=torch.int32)
+    sl = torch.randint(1, st + 1, (T,), device="cuda", dtype=torch.int32)
+    el = torch.randint(0, et + 1, (T,), device="cuda", dtype=torch.int32)
+    sink = torch.randn(H, device="cuda")
+    ref = oracle_out(q, swa_K, si[:, 0], sl, extra_K, ei[:, 0], el, scale=SCALE, sink=sink)
+    out = fm.sparse_mla_decode_fp8(q, swa_cache, si, sl, scale=SCALE, attn_sink=sink, extra_cache=extra_cache,
+                                   extra_indices=ei, extra_lens=el)
+    assert_attention_close(out, ref, f"T={T}")
+
+
+@pytest.mark.parametrize("swa_topk,extra_topk", [(256, 256), (512, 512)])
+def test_prefill_fp8_adversarial(fm, swa_topk, extra_topk):
+    """tests/test_sparse_mla_prefill_adversarial.py:56-95: T=67, ragged lens incl. 0 and tile
+    boundaries, invalid ids inside lens."""
+    rng = np.random.default_rng(7)
+    torch.manual_seed(7)
+    T, H = 67, 64
+    swa_cache, swa_K = fp8_cache_from_latent(_rand_latent(rng, swa_topk + 40), 32)
+    extra_cache, extra_K = fp8_cache_from_latent(_rand_latent(rng, extra_topk + 40), 16)
+    q = torch.randn(T, H, 512, device="cuda").to(torch.bfloat16)
+    specials = [0, 1, 15, 16, 17, 31, 32, 33, 63, 64, 65, 127, 128, 129, swa_topk]
+    sl = torch.randint(0, swa_topk + 1, (T,), dtype=torch.int32, device="cuda")
+    el = torch.randint(0, extra_topk + 1, (T,), dtype=torch.int32, device="cuda")
+    for i, v in enumerate(specials):
+        sl[i] = min(v, swa_topk)
+        el[-1 - i] = min(v, extra_topk)
+    si = torch.randint(0, swa_K.shape[0], (T, swa_topk), dtype=torch.int32, device="cuda")
+    ei = torch.randint(0, extra_K.shape[0], (T, extra_topk), dtype=torch.int32, device="cuda")
+    si[3, 2] = -1
+    si[4, 0] = swa_K.shape[0] + 5
+    ei[5, 1] = -1
+    sink = torch.randn(H, device="cuda") * 0.1
+    ref = oracle_out(q, swa_K, si, sl, extra_K, ei, el, scale=SCALE, sink=sink)
+    out = fm.sparse_mla_prefill(q=q, swa_cache=swa_cache, swa_indices=si, swa_lens=sl, scale=SCALE, attn_sink=sink,
+                                extra_cache=extra_cache, extra_indices=ei, extra_lens=el)
+    assert_attention_close(out, ref, "prefill adversarial")
+    torch.testing.assert_close(out.float().cpu(), torch.from_numpy(ref), rtol=2e-2, atol=2e-2)
+
+
+def test_prefill_fp8_swa_only(fm):
+    """tests/test_sparse_mla_prefill_adversarial.py:98-121."""
+    rng = np.random.default_rng(11)
+    torch.manual_seed(11)
+    T, H, topk = 33, 64, 512
+    cache, K = fp8_cache_from_latent(_rand_latent(rng, topk + 32), 64)
+    q = torch.randn(T, H, 512, device="cuda").to(torch.bfloat16)
+    lens = torch.randint(0, topk + 1, (T,), dtype=torch.int32, device="cuda")
+    lens[0], lens[1] = 0, topk
+    idx = torch.randint(0, K.shape[0], (T, topk), dtype=torch.int32, device="cuda")
+    sink = torch.randn(H, device="cuda") * 0.1
+    ref = oracle_out(q, K, idx, lens, scale=SCALE, sink=sink)
+    out = fm.sparse_mla_prefill(q=q, swa_cache=cache, swa_indices=idx, swa_lens=lens, scale=SCALE, attn_sink=sink)
+    assert_attention_close(out, ref, "swa-only prefill")
+    assert torch.all(out[0] == 0)
+
+
+# ----------------------------------------------------------------------------- oracle parity, int8
+@pytest.mark.parametrize("layout", ["inline528", "separate"])
+@pytest.mark.parametrize("topk", [(128, 384), (128, 896)])
+@pytest.mark.parametrize("T", [1, 4])
+def test_decode_int8_adversarial(fm, layout, topk, T):
+    """tests/test_sparse_mla_decode_int8_adversarial.py:30-103: both layouts, lens 0, invalid ids."""
+    rng = np.random.default_rng(31 + T)
+    torch.manual_seed(31)
+    H, (st, et) = 64, topk
+    sq, ss, swa_K, _b1 = int8_cache_from_latent(_rand_latent(rng, st + 40, 2.0), 64, layout)
+    eq, es, extra_K, _b2 = int8_cache_from_latent(_rand_latent(rng, et + 40, 2.0), 16, layout)
+    q = torch.randn(T, H, 512, device="cuda").to(torch.bfloat16)
+    si = torch.randint(0, swa_K.shape[0], (T, st), dtype=torch.int32, device="cuda")
+    ei = torch.randint(0, extra_K.shape[0], (T, et), dtype=torch.int32, device="cuda")
+    sl = torch.randint(0, st + 1, (T,), dtype=torch.int32, device="cuda")
+    el = torch.randint(0, et + 1, (T,), dtype=torch.int32, device="cuda")
+    sl[0] = st
+    el[0] = et
+    if T > 1:
+        sl[1] = 0
+        el[2] = 0
+    si[0, 1] = -1
+    ei[0, 3] = extra_K.shape[0] + 9
+    sink = torch.randn(H, device="cuda") * 0.1
+    ref = oracle_out(q, swa_K, si, sl, extra_K, ei, el, scale=SCALE, sink=sink)
+    out = fm.sparse_mla_decode_int8(q, sq, ss, si, sl, scale=SCALE, attn_sink=sink, extra_cache=eq, extra_scale=es,
+                                    extra_indices=ei, extra_lens=el)
+    assert_attention_close(out, ref, f"{layout} {topk} T={T}")
+
+
+def test_decode_int8_swa_only_and_index_head_dim(fm):
+    """...int8_adversarial.py:106-127,154-176: swa-only with lens [0, topk]; [T,1,topk] indices."""
+    rng = np.random.default_rng(33)
+    torch.manual_seed(33)
+    T, H, topk = 2, 64, 640
+    sq, ss, K, _ = int8_cache_from_latent(_rand_latent(rng, topk + 24, 2.0), 64, "inline528")
+    q = torch.randn(T, H, 512, device="cuda").to(torch.bfloat16)
+    idx = torch.randint(0, K.shape[0], (T, 1, topk), dtype=torch.int32, device="cuda")
+    lens = torch.tensor([0, topk], dtype=torch.int32, device="cuda")
+    ref = oracle_out(q, K, idx[:, 0], lens, scale=SCALE)
+    out = fm.sparse_mla_decode_int8(q, sq, ss, idx, lens, scale=SCALE)
+    assert_attention_close(out, ref, "swa-only int8")
+    assert torch.all(out[0] == 0)
+
+
+def test_decode_int8_split_stability(fm, monkeypatch):
+    """...int8_adversarial.py:298-354: split-KV must not change the result beyond fp32-partial noise
+    (RMSE < 5e-4, max <= 2^-8) -- compare the automatic split count with one split."""
+    from flash_mla import c_abi
+    rng = np.random.default_rng(43)
+    torch.manual_seed(43)
+    T, H, st, et = 1, 64, 128, 4096
+    sq, ss, swa_K, _b1 = int8_cache_from_latent(_rand_latent(rng, 512, 2.0), 128, "inline528")
+    eq, es, extra_K, _b2 = int8_cache_from_latent(_rand_latent(rng, 4096, 2.0), 64, "inline528")
+    q = torch.randn(T, H, 512, device="cuda").to(torch.bfloat16)
+    si = torch.randint(0, 512, (T, st), dtype=torch.int32, device="cuda")
+    ei = torch.stack([torch.randperm(4096, device="cuda")[:et].int() for _ in range(T)])
+    sl = torch.full((T,), st, dtype=torch.int32, device="cuda")
+    el = torch.full((T,), et, dtype=torch.int32, device="cuda")
+    sink = torch.randn(H, device="cuda") * 0.1
+    lib = c_abi.load()
+    outs = {}
+    for splits in (1, 7, 33):
+        out = torch.empty_like(q)
+        ws = torch.empty(lib.smla_attn_workspace_bytes(T, H, splits) // 4 + 1, dtype=torch.float32, device="cuda")
+        p = c_abi.attn_params(q, out, c_abi.SMLA_INT8_DS_MLA, SCALE, c_abi.stream_from_tensors(sq, ss, si, sl),
+                              c_abi.stream_from_tensors(eq, es, ei, el), sink, num_splits=splits, workspace=ws)
+        c_abi.check(lib.smla_sparse_mla_decode(p, torch.cuda.current_stream().cuda_stream))
+        torch.cuda.synchronize()
+        outs[splits] = out.float()
+    auto = fm.sparse_mla_decode_int8(q, sq, ss, si, sl, scale=SCALE, attn_sink=sink, extra_cache=eq, extra_scale=es,
+                                     extra_indices=ei, extra_lens=el).float()
+    ref = oracle_out(q, swa_K, si, sl, extra_K, ei, el, scale=SCALE, sink=sink)
+    for k, o in list(outs.items()) + [("auto", auto)]:
+        assert_attention_close(o, ref, f"splits={k}")
+        d = o - outs[1]
+        assert d.pow(2).mean().sqrt().item() < 5e-4, k
+        assert d.abs().max().item() <= 3.90625e-3, k
+    monkeypatch.setenv("FLASH_MLA_SLOTS_PER_SPLIT", "96")
+    again = fm.sparse_mla_decode_int8(q, sq, ss, si, sl, scale=SCALE, attn_sink=sink, extra_cache=eq, extra_scale=es,
+                                      extra_indices=ei, extra_lens=el).float()
+    assert torch.equal(again, auto)     # 96 rounds up to one 128-row tile: same schedule, same bits
+
+
+def test_decode_int8_many_tokens_single_split(fm):
+    """...int8_adversarial.py:130-151: T=64 fills the SMs, one split."""
+    rng = np.random.default_rng(41)
+    torch.manual_seed(41)
+    T, H, topk = 192, 64, 384
+    sq, ss, K, _ = int8_cache_from_latent(_rand_latent(rng, 1024, 2.0), 64, "separate")
+    q = torch.randn(T, H, 512, device="cuda").to(torch.bfloat16)
+    idx = torch.randint(0, 1024, (T, topk), dtype=torch.int32, device="cuda")
+    lens = torch.randint(1, topk + 1, (T,), dtype=torch.int32, device="cuda")
+    ref = oracle_out(q, K, idx, lens, scale=SCALE)
+    out = fm.sparse_mla_decode_int8(q, sq, ss, idx, lens, scale=SCALE)
+    assert_attention_close(out, ref, "T=192")
+
+
+@pytest.mark.parametrize("layout", ["inline528", "separate"])
+@pytest.mark.parametrize("H", [32, 64])
+def test_prefill_int8_adversarial(fm, layout, H):
+    """tests/test_sparse_mla_prefill_int8_adversarial.py:77-126,156-225 (H=32 is the TP2 shape)."""
+    rng = np.random.default_rng(21)
+    torch.manual_seed(21)
+    T, st, et = 67, 256, 256
+    sq, ss, swa_K, _b1 = int8_cache_from_latent(_rand_latent(rng, st + 40, 2.0), 64, layout)
+    eq, es, extra_K, _b2 = int8_cache_from_latent(_rand_latent(rng, et + 40, 2.0), 16, layout)
+    q = torch.randn(T, H, 512, device="cuda").to(torch.bfloat16)
+    specials = [0, 1, 15, 16, 17, 31, 32, 33, 63, 64, 65, st]
+    sl = torch.randint(0, st + 1, (T,), dtype=torch.int32, device="cuda")
+    el = torch.randint(0, et + 1, (T,), dtype=torch.int32, device="cuda")
+    for i, v in enumerate(specials):
+        sl[i] = min(v, st)
+        el[-1 - i] = min(v, et)
+    si = torch.randint(0, swa_K.shape[0], (T, st), dtype=torch.int32, device="cuda")
+    ei = torch.randint(0, extra_K.shape[0], (T, et), dtype=torch.int32, device="cuda")
+    si[3, 2] = -1
+    si[4, 0] = swa_K.shape[0] + 5
+    ei[5, 1] = -1
+    sink = torch.randn(H, device="cuda") * 0.1
+    ref = oracle_out(q, swa_K, si, sl, extra_K, ei, el, scale=SCALE, sink=sink)
+    out = fm.sparse_mla_prefill_int8(q, sq, ss, si, sl, scale=SCALE, attn_sink=sink, extra_cache=eq, extra_scale=es,
+                                     extra_indices=ei, extra_lens=el)
+    assert_attention_close(out, ref, f"int8 prefill {layout} H={H}")
+    torch.testing.assert_close(out.float().cpu(), torch.from_numpy(ref), rtol=2e-2, atol=2e-2)
+
+
+def test_outlier_rows_and_large_scores(fm):
+    """Rows scaled x50 (BASELINE config 3) make one score dominate: exercises the lazy running-max
+    rescale of the accumulator across tiles."""
+    rng = np.random.default_rng(5)
+    torch.manual_seed(5)
+    T, H, topk = 3, 64, 1024
+    lat = _rand_latent(rng, 2048)
+    lat[rng.random(2048) < 0.05] *= 50.0
+    order = np.argsort(np.abs(lat).max(axis=1))          # weakest rows first: the max keeps growing
+    sq, ss, K, _ = int8_cache_from_latent(lat, 64, "inline528")
+    q = torch.randn(T, H, 512, device="cuda").to(torch.bfloat16)
+    idx = torch.from_numpy(np.stack([order[:topk], order[-topk:], order[::2][:topk]]).astype(np.int32)).cuda()
+    lens = torch.full((T,), topk, dtype=torch.int32, device="cuda")
+    ref = oracle_out(q, K, idx, lens, scale=SCALE)
+    out = fm.sparse_mla_decode_int8(q, sq, ss, idx, lens, scale=SCALE)
+    assert_attention_close(out, ref, "outliers")
+
+
+# ----------------------------------------------------------------------------- argument errors
+def test_argument_errors(fm):
+    q = torch.randn(2, 64, 512, device="cuda").to(torch.bfloat16)
+    cache = torch.zeros(4, 32, 584, dtype=torch.uint8, device="cuda")
+    idx = torch.zeros(2, 64, dtype=torch.int32, device="cuda")
+    lens = torch.full((2,), 64, dtype=torch.int32, device="cuda")
+    with pytest.raises(RuntimeError, match="bfloat16"):
+        fm.sparse_mla_decode_fp8(q.float(), cache, idx, lens)
+    with pytest.raises(RuntimeError, match="head_dim"):
+        fm.sparse_mla_decode_fp8(q[:, :, :256].contiguous(), cache, idx, lens)
+    with pytest.raises(RuntimeError, match="int32"):
+        fm.sparse_mla_decode_fp8(q, cache, idx.long(), lens)
+    with pytest.raises(RuntimeError, match="uint8"):
+        fm.sparse_mla_prefill(q, cache.view(torch.int8), idx, lens)
+    with pytest.raises(ValueError):
+        fm.sparse_mla_decode_fp8(q, cache, idx.view(2, 2, 32), lens)
+    with pytest.raises(RuntimeError, match="extra"):
+        fm.sparse_mla_decode_fp8(q, cache, idx, lens, extra_cache=cache)
+    i8 = torch.zeros(4, 32, 512, dtype=torch.int8, device="cuda")
+    sc = torch.ones(4, 32, device="cuda")
+    with pytest.raises(ValueError):
+        fm.sparse_mla_decode_int8(q[:, :, :128], i8, sc, idx, lens)
+    with pytest.raises(ValueError):
+        fm.sparse_mla_decode_int8(q, i8, sc, idx.view(2, 2, 32), lens)
+    with pytest.raises(RuntimeError, match="int8"):
+        fm.sparse_mla_decode_int8(q, i8.view(torch.uint8), sc, idx, lens)
+    with pytest.raises(RuntimeError, match="float32"):
+        fm.sparse_mla_prefill_int8(q, i8, sc.half(), idx, lens)
+    with pytest.raises(ValueError):
+        fm.quantize_int8_ds_mla_rows(torch.zeros(3, 256, device="cuda"))
+    # everything above was rejected before any launch; a valid call still works afterwards
+    out = fm.sparse_mla_decode_fp8(q, cache, idx, lens)
+    assert torch.all(out == 0)     # zero cache -> zero rows -> zeros
