@@ -39,6 +39,16 @@ namespace smla {
 
 __device__ int g_device_status = 0;
 
+#ifdef SMLA_TRACE   // developer timing trace of CTA 0 (never defined in the product build)
+__device__ unsigned long long g_trace[32 * 16];
+#define SMLA_MARK(tile, k)                                                              \
+    do {                                                                                \
+        if (blockIdx.x == 0 && blockIdx.y == 0 && (tile) < 32) g_trace[(tile) * 16 + (k)] = clock64(); \
+    } while (0)
+#else
+#define SMLA_MARK(tile, k) do {} while (0)
+#endif
+
 namespace {
 
 constexpr int kD = 512;
@@ -333,14 +343,17 @@ __device__ __forceinline__ void gather_role(const KernelArgs &a, uint8_t *smem, 
                     return;
                 }
             }
+            if (gwarp == 0 && lane == 0 && c == 0) SMLA_MARK(it, 7);
 #pragma unroll
             for (int j = 0; j < J; ++j) {
                 const bool mine = (j < 8) ? ((j >> 1) == c) : (c == 3);
                 if (mine) convert_step<FMT>(raw[j], j, quarter, cur.sc0, cur.sc1, k_row_addr);
             }
+            if (gwarp == 0 && lane == 0) SMLA_MARK(it, 8 + c);
             fence_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(bars + c * 8);
+            if (gwarp == 0 && lane == 0 && c == 3) SMLA_MARK(it, 12);
             if (has_next) {
 #pragma unroll
                 for (int j = 0; j < J; ++j) {
@@ -427,7 +440,11 @@ __device__ __forceinline__ void softmax_role(const KernelArgs &a, uint8_t *smem,
 
     bool ok = true;
     for (int it = 0; it < ntl && ok; ++it) {
-        if (tid == 0) ok = issue_qk<NPAD>(smem, tmem_base, it);
+        if (tid == 0) {
+            SMLA_MARK(it, 0);
+            ok = issue_qk<NPAD>(smem, tmem_base, it);
+            SMLA_MARK(it, 1);
+        }
         __syncwarp();
         if (!mbar_wait(bars + 8 * 8, it & 1, abort_flag)) {
             give_up(abort_flag, kStatusSoftmaxWait);
@@ -441,6 +458,7 @@ __device__ __forceinline__ void softmax_role(const KernelArgs &a, uint8_t *smem,
         }
         tc_fence_after_sync();
 
+        if (tid == 0) SMLA_MARK(it, 2);
         uint32_t sraw[NPAD];
         TmemIO<NPAD>::ld(tmem_lane, sraw);
         float s[NPAD];
@@ -459,11 +477,15 @@ __device__ __forceinline__ void softmax_role(const KernelArgs &a, uint8_t *smem,
             const float tm = fmaxf(fmaxf(red[tid], red[NPAD + tid]), fmaxf(red[2 * NPAD + tid], red[3 * NPAD + tid]));
             const float m_old = m_s[tid];
             need = tm > m_old + kRescaleThreshold;
-            const float m_new = need ? tm : m_old;
+            // The reference point is kept INTEGER-valued (log2 units): then 2^(s - m) has the same
+            // mantissa whatever m is, so P rounds to bf16 identically in every split and the split
+            // count only changes fp32 summation order, not the rounding of the weights.
+            const float m_new = need ? ceilf(tm) : m_old;
             alpha_s[tid] = need ? fast_exp2(m_old - m_new) : 1.0f;
             m_s[tid] = m_new;
         }
         const bool rescale = named_bar_or(kSoftmaxBar, kSoftmaxThreads, need);
+        if (tid == 0) SMLA_MARK(it, 3);
 
         if (rescale) {
 #pragma unroll
@@ -492,12 +514,15 @@ __device__ __forceinline__ void softmax_role(const KernelArgs &a, uint8_t *smem,
             }
             tmem_st_wait();
         }
+        if (tid == 0) SMLA_MARK(it, 4);
         fence_async_smem();
         tc_fence_before_sync();
         named_bar_sync(kSoftmaxBar, kSoftmaxThreads);
         if (tid == 0) {
             tc_fence_after_sync();
+            SMLA_MARK(it, 5);
             issue_pv<NPAD>(smem, tmem_base, it, it + 1 == ntl);
+            SMLA_MARK(it, 6);
         }
         __syncwarp();
     }
@@ -595,7 +620,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const __gri
     }
     if (tid < NPAD) {
         float m0 = -INFINITY;
-        if (a.num_splits == 1 && a.sink != nullptr && tid < hvalid) m0 = a.sink[h0 + tid] * kLog2e;
+        if (a.num_splits == 1 && a.sink != nullptr && tid < hvalid) m0 = ceilf(a.sink[h0 + tid] * kLog2e);
         reinterpret_cast<float *>(smem + L::kM)[tid] = m0;
     }
     {
@@ -781,6 +806,13 @@ int launch_sparse_mla_attention(const smla_attn_params_t &p, int num_splits, voi
     }
     return rc;
 }
+
+#ifdef SMLA_TRACE
+extern "C" __attribute__((visibility("default"))) int smla_debug_read_trace(unsigned long long *host_out) {
+    cudaDeviceSynchronize();
+    return static_cast<int>(cudaMemcpyFromSymbol(host_out, g_trace, sizeof(unsigned long long) * 32 * 16));
+}
+#endif
 
 int read_and_clear_device_status(int *status_out) {
     int v = 0;

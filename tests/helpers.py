@@ -1,9 +1,14 @@
 """Shared helpers for the GPU parity tests: cache builders (oracle packers -> device tensors),
 the oracle call on device inputs, and the tolerance checks.
 
-Tolerances (stated once): attention outputs must satisfy max-abs <= 2e-2 and mean-abs <= 2e-3
-against the fp32 oracle, plus the reference's own gate cos_diff < 8e-5
-(tests/test_sparse_mla_prefill_adversarial.py:92-95).
+Tolerances (stated once).  Outputs are bf16, so an output of magnitude x cannot be closer than
+half a bf16 ulp (x * 2^-9) to an fp32 reference: the golden fixtures built with the reference's
+deterministic packer reach |x| = 20, where rounding alone is 6e-2.  The bounds are therefore
+    |out - ref| <= 2e-2 + 2^-8 |ref|   elementwise   (max-abs 2e-2 on top of one bf16 quantum)
+    mean|out - ref| <= 2e-3 + 2^-9 mean|ref|
+    cos_diff < 8e-5   (the reference's own gate, tests/test_sparse_mla_prefill_adversarial.py:92-95)
+and, for the N(0,1)-scale workloads of the benchmark configurations (``strict_abs=True``), the plain
+max-abs <= 2e-2 and mean-abs <= 2e-3.
 """
 from __future__ import annotations
 
@@ -59,16 +64,21 @@ def oracle_out(q, swa_K, swa_idx, swa_lens, extra_K=None, extra_idx=None, extra_
                                        scale=scale, sink=n(sink), tokens=tokens)
 
 
-def assert_attention_close(out: torch.Tensor, ref: np.ndarray, what="", tokens=None):
+def assert_attention_close(out: torch.Tensor, ref: np.ndarray, what="", tokens=None, strict_abs=False):
     got = out.detach().float().cpu().numpy()
     if tokens is not None:
         got, ref = got[tokens], ref[tokens]
     assert not np.isnan(got).any(), f"{what}: NaN in output"
     d = np.abs(got - ref)
     cd = oracle.cos_diff(got, ref)
-    assert d.max() <= MAX_ABS, f"{what}: max-abs {d.max():.3e} > {MAX_ABS}"
-    assert d.mean() <= MEAN_ABS, f"{what}: mean-abs {d.mean():.3e} > {MEAN_ABS}"
+    excess = (d - (MAX_ABS + 2.0 ** -8 * np.abs(ref))).max()
+    assert excess <= 0, f"{what}: error exceeds 2e-2 + one bf16 quantum by {excess:.3e} (max-abs {d.max():.3e})"
+    mean_bound = MEAN_ABS + 2.0 ** -9 * np.abs(ref).mean()
+    assert d.mean() <= mean_bound, f"{what}: mean-abs {d.mean():.3e} > {mean_bound:.3e}"
     assert cd < COS_DIFF, f"{what}: cos_diff {cd:.3e} >= {COS_DIFF}"
+    if strict_abs:
+        assert d.max() <= MAX_ABS, f"{what}: max-abs {d.max():.3e} > {MAX_ABS}"
+        assert d.mean() <= MEAN_ABS, f"{what}: mean-abs {d.mean():.3e} > {MEAN_ABS}"
 
 
 def device_status() -> int:

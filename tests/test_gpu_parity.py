@@ -367,3 +367,75 @@ def test_argument_errors(fm):
     # everything above was rejected before any launch; a valid call still works afterwards
     out = fm.sparse_mla_decode_fp8(q, cache, idx, lens)
     assert torch.all(out == 0)     # zero cache -> zero rows -> zeros
+
+
+# ----------------------------------------------------------------------------- benchmark-shaped workloads
+@pytest.mark.parametrize("fmt,T,H", [("fp8", 16, 64), ("int8", 8, 128), ("int8", 1, 64), ("fp8", 3, 16)])
+def test_decode_dsv4_shape_vs_oracle(fm, fmt, T, H):
+    """BASELINE configs 2/3 at reduced token count: 65536-slot swa (block 256, top-k 512) + 16384-slot
+    extra (block 64, top-k 2048), ~2 % masked ids, lens in [topk/2, topk], sink; N(0,1) data, so the
+    plain max-abs 2e-2 / mean-abs 2e-3 bounds apply."""
+    from flash_mla import synthetic
+    kw, meta = synthetic.decode_workload(fmt=fmt, T=T, H=H, seed=3)
+    op = fm.sparse_mla_decode_fp8 if fmt == "fp8" else fm.sparse_mla_decode_int8
+    out = op(**kw)
+    if fmt == "fp8":
+        swa_K = oracle.dequant_fp8_ds_mla(kw["swa_cache"].cpu().numpy())
+        extra_K = oracle.dequant_fp8_ds_mla(kw["extra_cache"].cpu().numpy())
+    else:
+        swa_K = oracle.dequant_int8_ds_mla(kw["swa_cache"].contiguous().cpu().numpy(), kw["swa_scale"].contiguous().cpu().numpy())
+        extra_K = oracle.dequant_int8_ds_mla(kw["extra_cache"].contiguous().cpu().numpy(),
+                                             kw["extra_scale"].contiguous().cpu().numpy())
+    ref = oracle_out(kw["q"], swa_K, kw["swa_indices"], kw["swa_lens"], extra_K, kw["extra_indices"], kw["extra_lens"],
+                     sink=kw["attn_sink"])
+    assert_attention_close(out, ref, f"{fmt} T={T} H={H}", strict_abs=True)
+
+
+def test_full_size_properties_config2(fm):
+    """BASELINE config 2 at full size (T=128, H=64, 2560-wide selection): size-independent properties.
+    (a) the order of a token's selected rows does not matter (softmax-weighted sum is permutation
+    invariant); (b) a token whose rows are all the same slot returns that row when there is no sink;
+    (c) sampled tokens agree with the oracle."""
+    from flash_mla import synthetic
+    kw, meta = synthetic.decode_workload(fmt="fp8", T=128, H=64, seed=0)
+    out = fm.sparse_mla_decode_fp8(**kw)
+    # (a) reverse each token's valid prefix in both streams
+    kw2 = dict(kw)
+    for name in ("swa", "extra"):
+        idx, lens = kw[f"{name}_indices"], kw[f"{name}_lens"]
+        pos = torch.arange(idx.shape[1], device=idx.device)[None, :]
+        src = torch.where(pos < lens[:, None], lens[:, None] - 1 - pos, pos)
+        kw2[f"{name}_indices"] = torch.gather(idx, 1, src.long()).contiguous()
+    out2 = fm.sparse_mla_decode_fp8(**kw2)
+    d = (out.float() - out2.float()).abs()
+    assert d.max().item() <= 4e-3 and d.mean().item() <= 2e-4
+    # (b) constant selection, no sink
+    kw3 = {k: v for k, v in kw.items() if k != "attn_sink"}
+    kw3["swa_indices"] = torch.full_like(kw["swa_indices"], 4242)
+    kw3["extra_indices"] = torch.full_like(kw["extra_indices"], 777)
+    kw3["extra_lens"] = torch.zeros_like(kw["extra_lens"])
+    out3 = fm.sparse_mla_decode_fp8(**kw3)
+    row = torch.from_numpy(oracle.dequant_fp8_ds_mla(kw["swa_cache"][4242 // 256:4242 // 256 + 1].cpu().numpy())[4242 % 256])
+    assert torch.allclose(out3.float().cpu(), row.expand(128, 64, 512), rtol=2 ** -7, atol=1e-3)
+    # (c) a token sample against the oracle
+    toks = [0, 17, 63, 127]
+    swa_K = oracle.dequant_fp8_ds_mla(kw["swa_cache"].cpu().numpy())
+    extra_K = oracle.dequant_fp8_ds_mla(kw["extra_cache"].cpu().numpy())
+    ref = oracle_out(kw["q"], swa_K, kw["swa_indices"], kw["swa_lens"], extra_K, kw["extra_indices"],
+                     kw["extra_lens"], sink=kw["attn_sink"], tokens=toks)
+    assert_attention_close(out, ref, "config 2 sample", tokens=toks, strict_abs=True)
+
+
+def test_prefill_int8_causal_config4_reduced(fm):
+    """BASELINE config 4 geometry at T=512 (causal top-k with -1 padding, extra stream on p // 4)."""
+    from flash_mla import synthetic
+    kw, meta = synthetic.prefill_int8_workload(T=512, H=64, swa_slots=2048, swa_topk=1024, extra_slots=512,
+                                               extra_topk=256, seed=4)
+    out = fm.sparse_mla_prefill_int8(**kw)
+    swa_K = oracle.dequant_int8_ds_mla(kw["swa_cache"].contiguous().cpu().numpy(), kw["swa_scale"].contiguous().cpu().numpy())
+    extra_K = oracle.dequant_int8_ds_mla(kw["extra_cache"].contiguous().cpu().numpy(),
+                                         kw["extra_scale"].contiguous().cpu().numpy())
+    toks = [0, 1, 2, 3, 5, 127, 128, 129, 300, 511]
+    ref = oracle_out(kw["q"], swa_K, kw["swa_indices"], kw["swa_lens"], extra_K, kw["extra_indices"], kw["extra_lens"],
+                     sink=kw["attn_sink"], tokens=toks)
+    assert_attention_close(out, ref, "config 4 reduced", tokens=toks)
