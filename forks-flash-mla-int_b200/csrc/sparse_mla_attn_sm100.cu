@@ -16,10 +16,14 @@
 // serves both products: it is stored as 8x16-byte core matrices (8 rows x 8 dims) which a
 // no-swizzle descriptor can walk row-group-first (K-major) or dim-group-first (MN-major).
 //
-// Roles (640 threads): warps 0-3 softmax/epilogue (thread 0 also issues every MMA); warps 4-19
-// gather: each owns 8 rows of the tile, loads the raw bytes of its rows for the NEXT tile into
-// registers (16-byte loads), and converts them chunk by chunk (128 dims) into the single K
-// buffer as soon as the previous tile's PV releases that chunk.
+// Roles (544 threads, no register rebalancing: setmaxnreg.inc can block without any time limit).
+// Warps 0-15 are workers that alternate between two jobs: (1) convert -- warp w owns rows 8w..8w+7
+// of the tile, keeps their raw bytes for the NEXT tile in registers (16-byte loads issued a tile
+// ahead) and writes them as bf16 into the single K buffer chunk by chunk (128 dims), each chunk as
+// soon as the previous tile's PV has released it; (2) softmax -- warp w owns TMEM lanes
+// 32*(w%4).. and head columns (N/4)*(w/4)..: S^T -> P^T with a lazily moved, integer-valued
+// reference max, running denominators, and the epilogue.  Warp 16 allocates TMEM and its lane 0
+// issues every tcgen05.mma.
 //
 // Every spin is time-bounded; a wait that runs out sets a bit in the device status word and the
 // CTA leaves through the normal teardown.
@@ -53,27 +57,30 @@ namespace {
 
 constexpr int kD = 512;
 constexpr int kTileRows = 128;
-constexpr int kSoftmaxThreads = 128;
-constexpr int kGatherWarps = 16;
-constexpr int kThreads = kSoftmaxThreads + kGatherWarps * 32;  // 640
+constexpr int kWorkerWarps = 16;                 // gather/dequant + softmax + epilogue
+constexpr int kWorkerThreads = kWorkerWarps * 32;
+constexpr int kMmaWarp = kWorkerWarps;           // one more warp: TMEM allocation and every tcgen05.mma
+constexpr int kThreads = kWorkerThreads + 128;   // 640: the MMA warp plus three idle warps (register
+                                                 // files are handed out per group of four warps)
+// No register rebalancing between the roles: setmaxnreg.inc blocks with no time limit until the
+// registers it asks for have been released inside the same CTA, a hang this kernel has no way to
+// bound.  Every thread gets the 96 registers __launch_bounds__(640, 1) allows.
 constexpr int kNumWarps = kThreads / 32;
-constexpr int kCoreBytes = 128;             // one 8x16B core matrix
+constexpr int kCoreBytes = 128;                  // one 8x16B core matrix
 constexpr int kRowGroupBytes = 64 * kCoreBytes;  // 8 rows x 512 dims of bf16
 constexpr int kKBytes = 16 * kRowGroupBytes;     // 128 rows
 constexpr int kTmemCols = 512;
-constexpr int kTmemOCol = 64;               // O^T chunks start here; S^T at column 0
+constexpr int kTmemOCol = 64;                    // O^T chunks start here; S^T at column 0
 constexpr float kLog2e = 1.4426950408889634f;
-constexpr float kRescaleThreshold = 8.0f;   // log2 units: the running max may lag by up to 2^8
-constexpr int kSoftmaxBar = 1;
-// Register rebalancing.  setmaxnreg.inc blocks (without any time limit) until the registers it asks
-// for have been released INSIDE THE SAME CTA, so the two role budgets must fit the pool the CTA was
-// launched with: 640 threads x 96 registers (the cap __launch_bounds__(640, 1) gives ptxas).
-constexpr int kLaunchRegs = 96;
-constexpr int kSoftmaxRegs = 224;
-constexpr int kGatherRegs = 64;
-static_assert(kSoftmaxThreads * kSoftmaxRegs + kGatherWarps * 32 * kGatherRegs <= kThreads * kLaunchRegs,
-              "role register budgets exceed the CTA's launch-time register pool: setmaxnreg.inc would never return");
-static_assert(kThreads * kLaunchRegs <= 65536 && kLaunchRegs == ((65536 / kThreads) / 8) * 8, "launch register cap");
+constexpr float kRescaleThreshold = 8.0f;        // log2 units: the reference max may lag by up to 2^8
+constexpr int kAllWorkersBar = 5;                // named barriers 1..4: the four column-slice groups
+// mbarrier slots
+constexpr int kBarReady = 0;   // [4] K chunk c holds this tile (16 arrivals: one per worker warp)
+constexpr int kBarFree = 4;    // [4] PV of the previous tile has finished reading K chunk c
+constexpr int kBarS = 8;       //     S^T of this tile is complete in TMEM
+constexpr int kBarP = 9;       //     P^T of this tile is in shared memory (16 arrivals)
+constexpr int kBarO = 10;      //     the last PV has completed
+static_assert(kBarO + 1 <= 12, "mbarrier slots reserved in Smem");
 
 struct StreamDev {
     const uint8_t *cache;
@@ -105,8 +112,8 @@ struct Smem {
     static constexpr int kRed = kP + NPAD * 256;         // [4][NPAD] floats
     static constexpr int kM = kRed + 4 * NPAD * 4;       // running reference max per head
     static constexpr int kAlpha = kM + NPAD * 4;         // rescale factor / final 1/l per head
-    static constexpr int kBars = kAlpha + NPAD * 4;      // ready[4], free[4], s, o
-    static constexpr int kTmemPtr = kBars + 10 * 8;
+    static constexpr int kBars = kAlpha + NPAD * 4;      // kNumBars mbarriers
+    static constexpr int kTmemPtr = kBars + 12 * 8;
     static constexpr int kAbort = kTmemPtr + 4;
     static constexpr int kTotal = kAbort + 4 + 8;
 };
@@ -195,29 +202,26 @@ struct ColReduce {
         }
     }
 };
-template <int NPAD>
-__device__ __forceinline__ void store_col_partials(float *red_row, const float *r, int lane) {
-    if constexpr (NPAD == 64) {
-        *reinterpret_cast<float2 *>(red_row + 2 * lane) = make_float2(r[0], r[1]);
-    } else if constexpr (NPAD == 32) {
-        red_row[lane] = r[0];
-    } else {
-        if ((lane & 1) == 0) red_row[lane >> 1] = r[0];
-    }
+// After ColReduce<W, 16, .> the value of column c (0 <= c < W <= 16) sits in every lane with
+// lane >> kShift == c; the lane whose low kShift bits are zero writes it.
+template <int W>
+__device__ __forceinline__ void store_col_partial(float *dst_cols, float v, int lane) {
+    constexpr int kShift = (W == 16) ? 1 : (W == 8) ? 2 : 3;
+    if ((lane & ((1 << kShift) - 1)) == 0) dst_cols[lane >> kShift] = v;
 }
 
 template <int N> struct TmemIO;
+template <> struct TmemIO<4> {
+    static __device__ __forceinline__ void ld(uint32_t a, uint32_t (&r)[4]) { tmem_ld_x4(a, r); }
+    static __device__ __forceinline__ void st(uint32_t a, const uint32_t (&r)[4]) { tmem_st_x4(a, r); }
+};
+template <> struct TmemIO<8> {
+    static __device__ __forceinline__ void ld(uint32_t a, uint32_t (&r)[8]) { tmem_ld_x8(a, r); }
+    static __device__ __forceinline__ void st(uint32_t a, const uint32_t (&r)[8]) { tmem_st_x8(a, r); }
+};
 template <> struct TmemIO<16> {
     static __device__ __forceinline__ void ld(uint32_t a, uint32_t (&r)[16]) { tmem_ld_x16(a, r); }
     static __device__ __forceinline__ void st(uint32_t a, const uint32_t (&r)[16]) { tmem_st_x16(a, r); }
-};
-template <> struct TmemIO<32> {
-    static __device__ __forceinline__ void ld(uint32_t a, uint32_t (&r)[32]) { tmem_ld_x32(a, r); }
-    static __device__ __forceinline__ void st(uint32_t a, const uint32_t (&r)[32]) { tmem_st_x32(a, r); }
-};
-template <> struct TmemIO<64> {
-    static __device__ __forceinline__ void ld(uint32_t a, uint32_t (&r)[64]) { tmem_ld_x64(a, r); }
-    static __device__ __forceinline__ void st(uint32_t a, const uint32_t (&r)[64]) { tmem_st_x64(a, r); }
 };
 
 __device__ __forceinline__ void give_up(volatile int *abort_flag, int bit) {
@@ -225,7 +229,7 @@ __device__ __forceinline__ void give_up(volatile int *abort_flag, int bit) {
     atomicOr(&g_device_status, bit);
 }
 
-// ------------------------------------------------------------------ gather role (warps 4..19)
+// ------------------------------------------------------------------ row gather / dequant helpers
 template <int FMT>
 struct RowRef {
     const uint8_t *ptr;   // first data byte of the row (unused when !ok)
@@ -310,18 +314,119 @@ __device__ __forceinline__ void convert_step(const uint4 &raw, int j, int quarte
     }
 }
 
-template <int FMT, int NPAD>
-__device__ __forceinline__ void gather_role(const KernelArgs &a, uint8_t *smem, int t, int ns, int n, int tile0,
-                                            int ntl, int gwarp, int lane) {
+// Warp-level wait: lane 0 polls, the result is broadcast.  A wait that runs out (or finds the CTA
+// already aborted) records `bit` and returns false; callers carry on with garbage instead of leaving,
+// so that every named barrier below still sees all of its threads.
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int lane, int bit) {
+    int ok = 1;
+    if (lane == 0) {
+        ok = mbar_wait(bar, parity, abort_flag) ? 1 : 0;
+        if (!ok) give_up(abort_flag, bit);
+    }
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+
+// ------------------------------------------------------------------ MMA issue (lane 0 of the MMA warp)
+template <int NPAD>
+__device__ __forceinline__ void mma_role(uint8_t *smem, uint32_t tmem_base, int ntl) {
     using L = Smem<NPAD>;
-    constexpr int J = Steps<FMT>::kCount;
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::kAbort);
     const uint32_t bars = smem_u32(smem + L::kBars);
-    const int quarter = lane >> 3;
-    const int r_in_tile = gwarp * 8 + (lane & 7);
-    const uint32_t k_row_addr = smem_u32(smem + L::kK) + gwarp * kRowGroupBytes + (lane & 7) * 16;
+    constexpr uint32_t idesc_qk = umma_idesc_bf16(128, NPAD, 0, 0);
+    constexpr uint32_t idesc_pv = umma_idesc_bf16(128, NPAD, 1, 1);
+    // QK^T: K-major A (rows x dims) and B (heads x dims): M/N step = one row group (8192 B), K step =
+    // one core matrix (128 B).  PV: MN-major A = K^T chunk (dims x rows): M step = next dim group
+    // (128 B), K step = next row group (8192 B); MN-major B = P^T: N step = next head group (2048 B),
+    // K step = next row group (128 B).  Only the 14-bit start-address field changes between MMAs, so
+    // stepping a descriptor is one 32-bit add: the thread must sustain one MMA per ~50 cycles.
+    const uint64_t qa = umma_desc(smem_u32(smem + L::kK), kCoreBytes, kRowGroupBytes);
+    const uint64_t qb = umma_desc(smem_u32(smem + L::kQ), kCoreBytes, kRowGroupBytes);
+    const uint64_t pa = umma_desc(smem_u32(smem + L::kK), kRowGroupBytes, kCoreBytes);
+    const uint64_t pb = umma_desc(smem_u32(smem + L::kP), kCoreBytes, 2048);
+    const uint32_t qa_lo = static_cast<uint32_t>(qa), qa_hi = static_cast<uint32_t>(qa >> 32);
+    const uint32_t qb_lo = static_cast<uint32_t>(qb), qb_hi = static_cast<uint32_t>(qb >> 32);
+    const uint32_t pa_lo = static_cast<uint32_t>(pa), pa_hi = static_cast<uint32_t>(pa >> 32);
+    const uint32_t pb_lo = static_cast<uint32_t>(pb), pb_hi = static_cast<uint32_t>(pb >> 32);
 
-    int g = tile0 * kTileRows + r_in_tile;
+    for (int it = 0; it < ntl; ++it) {
+        SMLA_MARK(it, 0);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            if (!mbar_wait(bars + (kBarReady + c) * 8, it & 1, abort_flag)) {
+                give_up(abort_flag, kStatusMmaWait);
+                return;
+            }
+            tc_fence_after_sync();
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const uint32_t off = static_cast<uint32_t>(((16 * c + 2 * k) * kCoreBytes) >> 4);
+                umma_bf16_ss_lohi(tmem_base, qa_lo + off, qa_hi, qb_lo + off, qb_hi, idesc_qk, (c | k) != 0 ? 1u : 0u);
+            }
+        }
+        umma_commit(bars + kBarS * 8);
+        SMLA_MARK(it, 1);
+        if (!mbar_wait(bars + kBarP * 8, it & 1, abort_flag)) {
+            give_up(abort_flag, kStatusMmaWait);
+            return;
+        }
+        tc_fence_after_sync();
+        SMLA_MARK(it, 5);
+        const uint32_t acc0 = it > 0 ? 1u : 0u;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const uint32_t aoff = static_cast<uint32_t>((c * 16 * kCoreBytes + 2 * k * kRowGroupBytes) >> 4);
+                const uint32_t boff = static_cast<uint32_t>((2 * k * kCoreBytes) >> 4);
+                umma_bf16_ss_lohi(tmem_base + kTmemOCol + c * NPAD, pa_lo + aoff, pa_hi, pb_lo + boff, pb_hi, idesc_pv,
+                                  k > 0 ? 1u : acc0);
+            }
+            umma_commit(bars + (kBarFree + c) * 8);   // chunk c of the K buffer may be refilled
+        }
+        if (it + 1 == ntl) umma_commit(bars + kBarO * 8);
+        SMLA_MARK(it, 6);
+    }
+}
+
+// ------------------------------------------------------------------ worker warps (0..15)
+// Each worker warp alternates between two jobs that never overlap in time for one tile:
+//   convert: it owns rows 8w..8w+7 of the tile; raw bytes (already in registers) -> bf16 K chunks;
+//   softmax: it owns TMEM lanes 32*(w%4).. (rows of S^T / dims of O^T) and head columns
+//            (NPAD/4)*(w/4)..: scores -> P^T, running denominators, rare accumulator rescale.
+template <int FMT, int NPAD>
+__device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, uint32_t tmem_base, int t, int h0,
+                                            int hvalid, int sp, int ns, int n, int tile0, int ntl, int warp,
+                                            int lane) {
+    using L = Smem<NPAD>;
+    constexpr int J = Steps<FMT>::kCount;
+    constexpr int CW = NPAD / 4;   // head columns per warp in the softmax job
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::kAbort);
+    const uint32_t bars = smem_u32(smem + L::kBars);
+    float *red = reinterpret_cast<float *>(smem + L::kRed);
+    float *m_s = reinterpret_cast<float *>(smem + L::kM);
+    float *alpha_s = reinterpret_cast<float *>(smem + L::kAlpha);
+    const int tid = warp * 32 + lane;
+    const bool direct = a.num_splits == 1;
+    const bool tracer = (warp == 0 && lane == 0);
+    (void)tracer;
+
+    // convert job
+    const int quarter = lane >> 3;
+    const uint32_t k_row_addr = smem_u32(smem + L::kK) + warp * kRowGroupBytes + (lane & 7) * 16;
+    // softmax job
+    const int q = warp & 3, cs = warp >> 2;
+    const int row = q * 32 + lane;
+    const int col0 = cs * CW;
+    const uint32_t tmem_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+    const uint32_t p_addr = smem_u32(smem + L::kP) + (col0 >> 3) * 2048 + (row >> 3) * kCoreBytes + (row & 7) * 16 +
+                            (col0 & 7) * 2;
+    const int group_bar = 1 + cs;
+
+    float lsum[CW];
+#pragma unroll
+    for (int j = 0; j < CW; ++j) lsum[j] = 0.0f;
+
+    int g = tile0 * kTileRows + warp * 8 + (lane & 7);
     RowRef<FMT> cur = make_row_ref<FMT>(a, ns, n, g, load_slot_id(a, t, ns, n, g));
     uint4 raw[J];
 #pragma unroll
@@ -332,213 +437,117 @@ __device__ __forceinline__ void gather_role(const KernelArgs &a, uint8_t *smem, 
         const bool has_next = it + 1 < ntl;
         RowRef<FMT> nxt = make_row_ref<FMT>(a, ns, n, has_next ? g + kTileRows : n, id_next);
         if (it + 2 < ntl) id_next = load_slot_id(a, t, ns, n, g + 2 * kTileRows);
+
+        // ---- convert: raw registers -> K chunks, each as soon as the previous tile's PV released it
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-            if (it > 0) {
-                int ok = 1;
-                if (lane == 0) ok = mbar_wait(bars + (4 + c) * 8, (it - 1) & 1, abort_flag) ? 1 : 0;
-                ok = __shfl_sync(0xffffffffu, ok, 0);
-                if (!ok) {
-                    if (lane == 0) give_up(abort_flag, kStatusGatherWait);
-                    return;
-                }
-            }
-            if (gwarp == 0 && lane == 0 && c == 0) SMLA_MARK(it, 7);
+            if (it > 0) warp_wait(bars + (kBarFree + c) * 8, (it - 1) & 1, abort_flag, lane, kStatusGatherWait);
+            if (tracer && c == 0) SMLA_MARK(it, 7);
 #pragma unroll
             for (int j = 0; j < J; ++j) {
                 const bool mine = (j < 8) ? ((j >> 1) == c) : (c == 3);
                 if (mine) convert_step<FMT>(raw[j], j, quarter, cur.sc0, cur.sc1, k_row_addr);
             }
-            if (gwarp == 0 && lane == 0) SMLA_MARK(it, 8 + c);
+            if (tracer) SMLA_MARK(it, 8 + c);
             fence_async_smem();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bars + c * 8);
-            if (gwarp == 0 && lane == 0 && c == 3) SMLA_MARK(it, 12);
-            if (has_next) {
+            if (lane == 0) mbar_arrive(bars + (kBarReady + c) * 8);
+        }
+        if (tracer) SMLA_MARK(it, 12);
+        // Raw bytes of the next tile.  Issued only now, after this tile's last conversion fence: a
+        // proxy fence also waits for the thread's global loads in flight, so loads issued between
+        // the chunks would put a memory latency on every hand-over.  They land while QK^T runs.
+        if (has_next) {
 #pragma unroll
-                for (int j = 0; j < J; ++j) {
-                    const bool mine = (j < 8) ? ((j >> 1) == c) : (c == 3);
-                    if (mine) load_step<FMT>(nxt, j, quarter, raw[j]);
-                }
-            }
+            for (int j = 0; j < J; ++j) load_step<FMT>(nxt, j, quarter, raw[j]);
         }
         cur = nxt;
         g += kTileRows;
-    }
-}
 
-// ------------------------------------------------------------------ MMA issue (thread 0)
-template <int NPAD>
-__device__ __forceinline__ bool issue_qk(uint8_t *smem, uint32_t tmem_base, int it) {
-    using L = Smem<NPAD>;
-    volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::kAbort);
-    const uint32_t bars = smem_u32(smem + L::kBars);
-    constexpr uint32_t idesc = umma_idesc_bf16(128, NPAD, 0, 0);
-    // K-major A (rows x dims) and B (heads x dims): step along M/N = 8 rows = one row group
-    // (8192 B), step along K = 8 dims = one core matrix (128 B).
-    const uint64_t a0 = umma_desc(smem_u32(smem + L::kK), kCoreBytes, kRowGroupBytes);
-    const uint64_t b0 = umma_desc(smem_u32(smem + L::kQ), kCoreBytes, kRowGroupBytes);
-#pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
-        if (!mbar_wait(bars + c * 8, it & 1, abort_flag)) {
-            give_up(abort_flag, kStatusMmaWait);
-            return false;
-        }
+        // ---- softmax of this tile
+        warp_wait(bars + kBarS * 8, it & 1, abort_flag, lane, kStatusSoftmaxWait);
         tc_fence_after_sync();
+        if (tracer) SMLA_MARK(it, 2);
+        float s[CW];
+        {
+            uint32_t sraw[CW];
+            TmemIO<CW>::ld(tmem_lane + col0, sraw);
+            const bool row_valid = (tile0 + it) * kTileRows + row < n;
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            const uint64_t off = static_cast<uint64_t>(((16 * c + 2 * k) * kCoreBytes) >> 4);
-            umma_bf16_ss(tmem_base, a0 + off, b0 + off, idesc, (c | k) != 0 ? 1u : 0u);
+            for (int j = 0; j < CW; ++j) s[j] = row_valid ? __uint_as_float(sraw[j]) * a.scale_log2 : -INFINITY;
         }
-    }
-    umma_commit(bars + 8 * 8);
-    return true;
-}
-
-template <int NPAD>
-__device__ __forceinline__ void issue_pv(uint8_t *smem, uint32_t tmem_base, int it, bool last) {
-    using L = Smem<NPAD>;
-    const uint32_t bars = smem_u32(smem + L::kBars);
-    constexpr uint32_t idesc = umma_idesc_bf16(128, NPAD, 1, 1);
-    // MN-major A = K^T chunk (128 dims x 16 rows): M step = next dim group (128 B), K step = next
-    // row group (8192 B).  MN-major B = P^T (N heads x 16 rows): N step = next head group
-    // (2048 B), K step = next row group (128 B).
-    const uint64_t a0 = umma_desc(smem_u32(smem + L::kK), kRowGroupBytes, kCoreBytes);
-    const uint64_t b0 = umma_desc(smem_u32(smem + L::kP), kCoreBytes, 2048);
-#pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            const uint64_t aoff = static_cast<uint64_t>((c * 16 * kCoreBytes + 2 * k * kRowGroupBytes) >> 4);
-            const uint64_t boff = static_cast<uint64_t>((2 * k * kCoreBytes) >> 4);
-            umma_bf16_ss(tmem_base + kTmemOCol + c * NPAD, a0 + aoff, b0 + boff, idesc, (it > 0 || k > 0) ? 1u : 0u);
-        }
-        umma_commit(bars + (4 + c) * 8);   // chunk c of the K buffer may be refilled
-    }
-    if (last) umma_commit(bars + 9 * 8);
-}
-
-// ------------------------------------------------------------------ softmax / epilogue role (warps 0..3)
-template <int FMT, int NPAD>
-__device__ __forceinline__ void softmax_role(const KernelArgs &a, uint8_t *smem, uint32_t tmem_base, int t, int h0,
-                                             int hvalid, int sp, int n, int tile0, int ntl, int tid) {
-    using L = Smem<NPAD>;
-    volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::kAbort);
-    const uint32_t bars = smem_u32(smem + L::kBars);
-    float *red = reinterpret_cast<float *>(smem + L::kRed);
-    float *m_s = reinterpret_cast<float *>(smem + L::kM);
-    float *alpha_s = reinterpret_cast<float *>(smem + L::kAlpha);
-    const int lane = tid & 31, wq = tid >> 5;
-    const int row = tid;                                     // TMEM lane = row of the tile / dim of an O chunk
-    const uint32_t tmem_lane = tmem_base + (static_cast<uint32_t>(wq * 32) << 16);
-    const uint32_t p_row_addr = smem_u32(smem + L::kP) + (row >> 3) * kCoreBytes + (row & 7) * 16;
-    const bool direct = a.num_splits == 1;
-
-    float lsum[NPAD];
-#pragma unroll
-    for (int h = 0; h < NPAD; ++h) lsum[h] = 0.0f;
-
-    bool ok = true;
-    for (int it = 0; it < ntl && ok; ++it) {
-        if (tid == 0) {
-            SMLA_MARK(it, 0);
-            ok = issue_qk<NPAD>(smem, tmem_base, it);
-            SMLA_MARK(it, 1);
-        }
-        __syncwarp();
-        if (!mbar_wait(bars + 8 * 8, it & 1, abort_flag)) {
-            give_up(abort_flag, kStatusSoftmaxWait);
-            ok = false;
-        }
-        __syncwarp();
-        // Leave together: every softmax thread must see the same decision before the named barriers.
-        if (named_bar_or(kSoftmaxBar, kSoftmaxThreads, !ok)) {
-            ok = false;
-            break;
-        }
-        tc_fence_after_sync();
-
-        if (tid == 0) SMLA_MARK(it, 2);
-        uint32_t sraw[NPAD];
-        TmemIO<NPAD>::ld(tmem_lane, sraw);
-        float s[NPAD];
-        const bool row_valid = (tile0 + it) * kTileRows + row < n;
-#pragma unroll
-        for (int h = 0; h < NPAD; ++h) s[h] = row_valid ? __uint_as_float(sraw[h]) * a.scale_log2 : -INFINITY;
-
-        {   // per-head max over the 128 rows of the tile
-            float r[2];
-            ColReduce<NPAD, 16, true>::run(s, lane, r);
-            store_col_partials<NPAD>(red + wq * NPAD, r, lane);
-        }
-        named_bar_sync(kSoftmaxBar, kSoftmaxThreads);
+        // The reference max m is only moved when some score exceeds it by more than the threshold
+        // (always on the first tile).  The vote spans the four warps that share these columns.
         bool need = false;
-        if (tid < NPAD) {
-            const float tm = fmaxf(fmaxf(red[tid], red[NPAD + tid]), fmaxf(red[2 * NPAD + tid], red[3 * NPAD + tid]));
-            const float m_old = m_s[tid];
-            need = tm > m_old + kRescaleThreshold;
-            // The reference point is kept INTEGER-valued (log2 units): then 2^(s - m) has the same
-            // mantissa whatever m is, so P rounds to bf16 identically in every split and the split
-            // count only changes fp32 summation order, not the rounding of the weights.
-            const float m_new = need ? ceilf(tm) : m_old;
-            alpha_s[tid] = need ? fast_exp2(m_old - m_new) : 1.0f;
-            m_s[tid] = m_new;
-        }
-        const bool rescale = named_bar_or(kSoftmaxBar, kSoftmaxThreads, need);
-        if (tid == 0) SMLA_MARK(it, 3);
-
-        if (rescale) {
 #pragma unroll
-            for (int h = 0; h < NPAD; ++h) lsum[h] *= alpha_s[h];
-        }
-        // P^T = exp2(S^T - m), rounded to bf16, into the MN-major B-operand layout.
-#pragma unroll
-        for (int hg = 0; hg < NPAD / 8; ++hg) {
-            float p[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                p[i] = fast_exp2(s[hg * 8 + i] - m_s[hg * 8 + i]);
-                lsum[hg * 8 + i] += p[i];
+        for (int j = 0; j < CW; ++j) need |= s[j] > m_s[col0 + j] + kRescaleThreshold;
+        if (named_bar_or(group_bar, 128, need)) {
+            float r[1];
+            ColReduce<CW, 16, true>::run(s, lane, r);
+            store_col_partial<CW>(red + q * NPAD + col0, r[0], lane);
+            named_bar_sync(group_bar, 128);
+            if (q == 0 && lane < CW) {
+                const int col = col0 + lane;
+                const float tm = fmaxf(fmaxf(red[col], red[NPAD + col]), fmaxf(red[2 * NPAD + col], red[3 * NPAD + col]));
+                const float m_old = m_s[col];
+                const bool up = tm > m_old + kRescaleThreshold;
+                // m stays INTEGER-valued (log2 units): 2^(s - m) then has the same mantissa whatever m
+                // is, so P rounds to bf16 identically in every split-KV schedule.
+                const float m_new = up ? ceilf(tm) : m_old;
+                alpha_s[col] = up ? fast_exp2(m_old - m_new) : 1.0f;
+                m_s[col] = m_new;
             }
-            st_shared_v4(p_row_addr + hg * 2048, pack_bf16x2(p[0], p[1]), pack_bf16x2(p[2], p[3]),
-                         pack_bf16x2(p[4], p[5]), pack_bf16x2(p[6], p[7]));
-        }
-        if (rescale && it > 0) {   // O^T[:, h] *= alpha[h]; the previous PV has completed (it precedes this QK)
+            named_bar_sync(group_bar, 128);
+#pragma unroll
+            for (int j = 0; j < CW; ++j) lsum[j] *= alpha_s[col0 + j];
+            if (it > 0) {   // O^T[:, h] *= alpha[h]; the previous PV completed before this tile's S^T did
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                uint32_t o[NPAD];
-                TmemIO<NPAD>::ld(tmem_lane + kTmemOCol + c * NPAD, o);
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t o[CW];
+                    TmemIO<CW>::ld(tmem_lane + kTmemOCol + c * NPAD + col0, o);
 #pragma unroll
-                for (int h = 0; h < NPAD; ++h) o[h] = __float_as_uint(__uint_as_float(o[h]) * alpha_s[h]);
-                TmemIO<NPAD>::st(tmem_lane + kTmemOCol + c * NPAD, o);
+                    for (int j = 0; j < CW; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha_s[col0 + j]);
+                    TmemIO<CW>::st(tmem_lane + kTmemOCol + c * NPAD + col0, o);
+                }
+                tmem_st_wait();
             }
-            tmem_st_wait();
         }
-        if (tid == 0) SMLA_MARK(it, 4);
+        if (tracer) SMLA_MARK(it, 3);
+        {   // P^T = 2^(S^T - m) rounded to bf16, MN-major B-operand layout (8 heads = 16 bytes per row)
+            uint32_t pk[CW / 2];
+#pragma unroll
+            for (int j = 0; j < CW; j += 2) {
+                const float p0 = fast_exp2(s[j] - m_s[col0 + j]);
+                const float p1 = fast_exp2(s[j + 1] - m_s[col0 + j + 1]);
+                lsum[j] += p0;
+                lsum[j + 1] += p1;
+                pk[j / 2] = pack_bf16x2(p0, p1);
+            }
+            if constexpr (CW == 16) {
+                st_shared_v4(p_addr, pk[0], pk[1], pk[2], pk[3]);
+                st_shared_v4(p_addr + 2048, pk[4], pk[5], pk[6], pk[7]);
+            } else if constexpr (CW == 8) {
+                st_shared_v4(p_addr, pk[0], pk[1], pk[2], pk[3]);
+            } else {
+                asm volatile("st.shared.v2.b32 [%0], {%1,%2};" ::"r"(p_addr), "r"(pk[0]), "r"(pk[1]) : "memory");
+            }
+        }
+        if (tracer) SMLA_MARK(it, 4);
         fence_async_smem();
         tc_fence_before_sync();
-        named_bar_sync(kSoftmaxBar, kSoftmaxThreads);
-        if (tid == 0) {
-            tc_fence_after_sync();
-            SMLA_MARK(it, 5);
-            issue_pv<NPAD>(smem, tmem_base, it, it + 1 == ntl);
-            SMLA_MARK(it, 6);
-        }
         __syncwarp();
+        if (lane == 0) mbar_arrive(bars + kBarP * 8);
     }
-    if (!ok) return;
 
     // ---- epilogue: O^T / l
-    if (!mbar_wait(bars + 9 * 8, 0, abort_flag)) give_up(abort_flag, kStatusEpilogueWait), ok = false;
-    __syncwarp();
-    if (named_bar_or(kSoftmaxBar, kSoftmaxThreads, !ok)) return;
+    warp_wait(bars + kBarO * 8, 0, abort_flag, lane, kStatusEpilogueWait);
     tc_fence_after_sync();
     {
-        float r[2];
-        ColReduce<NPAD, 16, false>::run(lsum, lane, r);
-        store_col_partials<NPAD>(red + wq * NPAD, r, lane);
+        float r[1];
+        ColReduce<CW, 16, false>::run(lsum, lane, r);
+        store_col_partial<CW>(red + q * NPAD + col0, r[0], lane);
     }
-    named_bar_sync(kSoftmaxBar, kSoftmaxThreads);
+    named_bar_sync(kAllWorkersBar, kWorkerThreads);
     if (tid < NPAD) {
         float l = (red[tid] + red[NPAD + tid]) + (red[2 * NPAD + tid] + red[3 * NPAD + tid]);
         if (direct) {
@@ -550,22 +559,22 @@ __device__ __forceinline__ void softmax_role(const KernelArgs &a, uint8_t *smem,
             ml[1] = l;
         }
     }
-    named_bar_sync(kSoftmaxBar, kSoftmaxThreads);
+    named_bar_sync(kAllWorkersBar, kWorkerThreads);
 #pragma unroll 1
     for (int c = 0; c < 4; ++c) {
-        uint32_t o[NPAD];
-        TmemIO<NPAD>::ld(tmem_lane + kTmemOCol + c * NPAD, o);
+        uint32_t o[CW];
+        TmemIO<CW>::ld(tmem_lane + kTmemOCol + c * NPAD + col0, o);
         const int d = c * 128 + row;
         if (direct) {
-            __nv_bfloat16 *dst = a.out + static_cast<long long>(t) * a.o_ts + static_cast<long long>(h0) * a.o_hs + d;
+            __nv_bfloat16 *dst = a.out + static_cast<long long>(t) * a.o_ts + static_cast<long long>(h0 + col0) * a.o_hs + d;
 #pragma unroll
-            for (int h = 0; h < NPAD; ++h)
-                if (h < hvalid) dst[h * a.o_hs] = __float2bfloat16_rn(__uint_as_float(o[h]) * alpha_s[h]);
+            for (int j = 0; j < CW; ++j)
+                if (col0 + j < hvalid) dst[j * a.o_hs] = __float2bfloat16_rn(__uint_as_float(o[j]) * alpha_s[col0 + j]);
         } else {
-            float *dst = a.part_o + ((static_cast<long long>(t) * a.H + h0) * a.num_splits + sp) * kD + d;
+            float *dst = a.part_o + ((static_cast<long long>(t) * a.H + h0 + col0) * a.num_splits + sp) * kD + d;
 #pragma unroll
-            for (int h = 0; h < NPAD; ++h)
-                if (h < hvalid) dst[static_cast<long long>(h) * a.num_splits * kD] = __uint_as_float(o[h]);
+            for (int j = 0; j < CW; ++j)
+                if (col0 + j < hvalid) dst[static_cast<long long>(j) * a.num_splits * kD] = __uint_as_float(o[j]);
         }
     }
     tc_fence_before_sync();
@@ -607,14 +616,15 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const __gri
     // ---- set-up: barriers, TMEM, reference max, Q tile
     if (tid == 0) {
         const uint32_t bars = smem_u32(smem + L::kBars);
-        for (int c = 0; c < 4; ++c) mbar_init(bars + c * 8, kGatherWarps);   // K chunk filled
-        for (int c = 0; c < 4; ++c) mbar_init(bars + (4 + c) * 8, 1);        // K chunk released by PV
-        mbar_init(bars + 8 * 8, 1);                                           // S^T ready
-        mbar_init(bars + 9 * 8, 1);                                           // last PV done
+        for (int c = 0; c < 4; ++c) mbar_init(bars + (kBarReady + c) * 8, kWorkerWarps);
+        for (int c = 0; c < 4; ++c) mbar_init(bars + (kBarFree + c) * 8, 1);
+        mbar_init(bars + kBarS * 8, 1);
+        mbar_init(bars + kBarP * 8, kWorkerWarps);
+        mbar_init(bars + kBarO * 8, 1);
         *reinterpret_cast<volatile int *>(smem + L::kAbort) = 0;
         mbar_init_fence();
     }
-    if (warp == 0) {
+    if (warp == kMmaWarp) {
         tmem_alloc(smem_u32(smem + L::kTmemPtr), kTmemCols);
         tmem_relinquish();
     }
@@ -639,16 +649,15 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const __gri
     tc_fence_after_sync();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(smem + L::kTmemPtr);
 
-    if (warp < 4) {
-        setmaxnreg_inc<kSoftmaxRegs>();
-        softmax_role<FMT, NPAD>(a, smem, tmem_base, t, h0, hvalid, sp, n, tile0, ntl, tid);
+    if (warp < kWorkerWarps) {
+        worker_role<FMT, NPAD>(a, smem, tmem_base, t, h0, hvalid, sp, ns, n, tile0, ntl, warp, lane);
     } else {
-        setmaxnreg_dec<kGatherRegs>();
-        gather_role<FMT, NPAD>(a, smem, t, ns, n, tile0, ntl, warp - 4, lane);
+        if (warp == kMmaWarp && lane == 0) mma_role<NPAD>(smem, tmem_base, ntl);
+        __syncwarp();
     }
 
     __syncthreads();
-    if (warp == 0) {
+    if (warp == kMmaWarp) {
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, kTmemCols);
     }
