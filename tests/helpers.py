@@ -1,14 +1,17 @@
 """Shared helpers for the GPU parity tests: cache builders (oracle packers -> device tensors),
 the oracle call on device inputs, and the tolerance checks.
 
-Tolerances (stated once).  Outputs are bf16, so an output of magnitude x cannot be closer than
-half a bf16 ulp (x * 2^-9) to an fp32 reference: the golden fixtures built with the reference's
-deterministic packer reach |x| = 20, where rounding alone is 6e-2.  The bounds are therefore
-    |out - ref| <= 2e-2 + 2^-7 |ref|   elementwise   (max-abs 2e-2 on top of one bf16 ulp)
-    mean|out - ref| <= 2e-3 + 2^-9 mean|ref|
-    cos_diff < 8e-5   (the reference's own gate, tests/test_sparse_mla_prefill_adversarial.py:92-95)
-and, for the N(0,1)-scale workloads of the benchmark configurations (``strict_abs=True``), the plain
-max-abs <= 2e-2 and mean-abs <= 2e-3.
+Tolerances (stated once).  Outputs are bf16 and P is rounded to bf16 before PV (as in the
+reference kernels), so an output of magnitude x carries an error of up to about x * 2^-7 whatever
+the implementation: the golden fixtures built with the reference's deterministic packer reach
+|x| = 20 and the x50 outlier rows of BASELINE config 3 reach |x| = 160, where a CPU emulation of the
+algorithm (bf16 P, fp32 accumulation, bf16 output) is already 1.0 away from the fp32 oracle.  Bounds:
+    |out - ref| <= 2e-2 + 2e-2 |ref|   elementwise: the reference's own gate, assert_close(rtol=2e-2,
+                                       atol=2e-2), tests/test_sparse_mla_prefill_adversarial.py:92-95
+    mean|out - ref| <= 2e-3 + 2^-8 mean|ref|
+    cos_diff < 8e-5                    (the reference's gate, same file)
+and, for N(0,1)-scale workloads without outlier rows (``strict_abs=True``), the plain north-star
+bounds max-abs <= 2e-2 and mean-abs <= 2e-3.
 """
 from __future__ import annotations
 
@@ -71,9 +74,9 @@ def assert_attention_close(out: torch.Tensor, ref: np.ndarray, what="", tokens=N
     assert not np.isnan(got).any(), f"{what}: NaN in output"
     d = np.abs(got - ref)
     cd = oracle.cos_diff(got, ref)
-    excess = (d - (MAX_ABS + 2.0 ** -7 * np.abs(ref))).max()
-    assert excess <= 0, f"{what}: error exceeds 2e-2 + one bf16 ulp by {excess:.3e} (max-abs {d.max():.3e})"
-    mean_bound = MEAN_ABS + 2.0 ** -9 * np.abs(ref).mean()
+    excess = (d - (MAX_ABS + 2e-2 * np.abs(ref))).max()
+    assert excess <= 0, f"{what}: error exceeds atol 2e-2 + rtol 2e-2 by {excess:.3e} (max-abs {d.max():.3e})"
+    mean_bound = MEAN_ABS + 2.0 ** -8 * np.abs(ref).mean()
     assert d.mean() <= mean_bound, f"{what}: mean-abs {d.mean():.3e} > {mean_bound:.3e}"
     assert cd < COS_DIFF, f"{what}: cos_diff {cd:.3e} >= {COS_DIFF}"
     if strict_abs:

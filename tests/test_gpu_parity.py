@@ -374,7 +374,8 @@ def test_argument_errors(fm):
 def test_decode_dsv4_shape_vs_oracle(fm, fmt, T, H):
     """BASELINE configs 2/3 at reduced token count: 65536-slot swa (block 256, top-k 512) + 16384-slot
     extra (block 64, top-k 2048), ~2 % masked ids, lens in [topk/2, topk], sink; N(0,1) data, so the
-    plain max-abs 2e-2 / mean-abs 2e-3 bounds apply."""
+    plain max-abs 2e-2 / mean-abs 2e-3 bounds apply to fp8; the int8 variant has 5 % of its rows scaled
+    x50 (config 3), whose outputs reach |x| ~ 100 and are held to the relative gate."""
     from flash_mla import synthetic
     kw, meta = synthetic.decode_workload(fmt=fmt, T=T, H=H, seed=3)
     op = fm.sparse_mla_decode_fp8 if fmt == "fp8" else fm.sparse_mla_decode_int8
@@ -388,7 +389,7 @@ def test_decode_dsv4_shape_vs_oracle(fm, fmt, T, H):
                                              kw["extra_scale"].contiguous().cpu().numpy())
     ref = oracle_out(kw["q"], swa_K, kw["swa_indices"], kw["swa_lens"], extra_K, kw["extra_indices"], kw["extra_lens"],
                      sink=kw["attn_sink"])
-    assert_attention_close(out, ref, f"{fmt} T={T} H={H}", strict_abs=True)
+    assert_attention_close(out, ref, f"{fmt} T={T} H={H}", strict_abs=(fmt == "fp8"))  # int8: x50 outlier rows
 
 
 def test_full_size_properties_config2(fm):
