@@ -468,20 +468,23 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
         warp_wait(bars + kBarS * 8, it & 1, abort_flag, lane, kStatusSoftmaxWait);
         tc_fence_after_sync();
         if (tracer) SMLA_MARK(it, 2);
-        float s[CW];
-        {
-            uint32_t sraw[CW];
-            TmemIO<CW>::ld(tmem_lane + col0, sraw);
-            const bool row_valid = (tile0 + it) * kTileRows + row < n;
+        // sm = S^T * scale - m, with m read once per tile as float4s (the same for all rows).
+        const bool row_valid = (tile0 + it) * kTileRows + row < n;
+        float sm[CW];
+        uint32_t sraw[CW];
+        TmemIO<CW>::ld(tmem_lane + col0, sraw);
 #pragma unroll
-            for (int j = 0; j < CW; ++j) s[j] = row_valid ? __uint_as_float(sraw[j]) * a.scale_log2 : -INFINITY;
-        }
+        for (int j = 0; j < CW; ++j)
+            sm[j] = row_valid ? fmaf(__uint_as_float(sraw[j]), a.scale_log2, -m_s[col0 + j]) : -INFINITY;
         // The reference max m is only moved when some score exceeds it by more than the threshold
         // (always on the first tile).  The vote spans the four warps that share these columns.
         bool need = false;
 #pragma unroll
-        for (int j = 0; j < CW; ++j) need |= s[j] > m_s[col0 + j] + kRescaleThreshold;
+        for (int j = 0; j < CW; ++j) need |= sm[j] > kRescaleThreshold;
         if (named_bar_or(group_bar, 128, need)) {
+            float s[CW];
+#pragma unroll
+            for (int j = 0; j < CW; ++j) s[j] = row_valid ? __uint_as_float(sraw[j]) * a.scale_log2 : -INFINITY;
             float r[1];
             ColReduce<CW, 16, true>::run(s, lane, r);
             store_col_partial<CW>(red + q * NPAD + col0, r[0], lane);
@@ -499,7 +502,10 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
             }
             named_bar_sync(group_bar, 128);
 #pragma unroll
-            for (int j = 0; j < CW; ++j) lsum[j] *= alpha_s[col0 + j];
+            for (int j = 0; j < CW; ++j) {
+                lsum[j] *= alpha_s[col0 + j];
+                sm[j] = s[j] - m_s[col0 + j];
+            }
             if (it > 0) {   // O^T[:, h] *= alpha[h]; the previous PV completed before this tile's S^T did
 #pragma unroll 1
                 for (int c = 0; c < 4; ++c) {
@@ -517,8 +523,8 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
             uint32_t pk[CW / 2];
 #pragma unroll
             for (int j = 0; j < CW; j += 2) {
-                const float p0 = fast_exp2(s[j] - m_s[col0 + j]);
-                const float p1 = fast_exp2(s[j + 1] - m_s[col0 + j + 1]);
+                const float p0 = fast_exp2(sm[j]);
+                const float p1 = fast_exp2(sm[j + 1]);
                 lsum[j] += p0;
                 lsum[j + 1] += p1;
                 pk[j / 2] = pack_bf16x2(p0, p1);
@@ -665,6 +671,8 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const __gri
 
 // ------------------------------------------------------------------ split-KV combine
 // One warp per (token, head): out = sum_s 2^(m_s - M) O_s / (sum_s 2^(m_s - M) l_s + 2^(sink - M)).
+// Lane s first turns {m_s, l_s} into a weight (S <= 64: two per lane); the partial rows are then
+// streamed four splits at a time so that 16 independent 16-byte loads are in flight per lane.
 __global__ void __launch_bounds__(128) sparse_mla_combine_kernel(const float *__restrict__ part_o,
                                                                  const float *__restrict__ part_ml,
                                                                  const float *__restrict__ sink,
@@ -674,30 +682,50 @@ __global__ void __launch_bounds__(128) sparse_mla_combine_kernel(const float *__
     const long long th = static_cast<long long>(blockIdx.x) * 4 + (threadIdx.x >> 5);
     if (th >= static_cast<long long>(T) * H) return;
     const int t = static_cast<int>(th / H), h = static_cast<int>(th - static_cast<long long>(t) * H);
-    const float *ml = part_ml + th * S * 2;
+    const float2 *ml = reinterpret_cast<const float2 *>(part_ml + th * S * 2);
     const float sink_l2 = sink ? sink[h] * kLog2e : -INFINITY;
+    float2 e0 = make_float2(-INFINITY, 0.0f), e1 = make_float2(-INFINITY, 0.0f);
+    if (lane < S) e0 = ml[lane];
+    if (lane + 32 < S) e1 = ml[lane + 32];
     float M = sink_l2;
-    for (int s = 0; s < S; ++s)
-        if (ml[2 * s + 1] > 0.0f) M = fmaxf(M, ml[2 * s]);
+    if (e0.y > 0.0f) M = fmaxf(M, e0.x);
+    if (e1.y > 0.0f) M = fmaxf(M, e1.x);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    // empty splits (l == 0) get weight 0 and their (unwritten) partial rows are never multiplied in
+    const float w0 = (e0.y > 0.0f && M > -INFINITY) ? fast_exp2(e0.x - M) : 0.0f;
+    const float w1 = (e1.y > 0.0f && M > -INFINITY) ? fast_exp2(e1.x - M) : 0.0f;
+    float denom = w0 * e0.y + w1 * e1.y;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) denom += __shfl_xor_sync(0xffffffffu, denom, o);
+    if (M > -INFINITY) denom += fast_exp2(sink_l2 - M);
+
     float acc[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) acc[i] = 0.0f;
-    float denom = 0.0f;
-    if (M > -INFINITY) {
-        denom = fast_exp2(sink_l2 - M);
-        for (int s = 0; s < S; ++s) {
-            const float l = ml[2 * s + 1];
-            if (!(l > 0.0f)) continue;
-            const float w = fast_exp2(ml[2 * s] - M);
-            denom += w * l;
-            const float4 *src = reinterpret_cast<const float4 *>(part_o + (th * S + s) * kD);
+    const float4 *base = reinterpret_cast<const float4 *>(part_o + th * S * kD);
+    for (int s0 = 0; s0 < S; s0 += 4) {
+        float4 x[4][4];
+        float w[4];
 #pragma unroll
-            for (int v = 0; v < 4; ++v) {
-                const float4 x = __ldg(src + v * 32 + lane);
-                acc[4 * v] += w * x.x;
-                acc[4 * v + 1] += w * x.y;
-                acc[4 * v + 2] += w * x.z;
-                acc[4 * v + 3] += w * x.w;
+        for (int u = 0; u < 4; ++u) {
+            const int s = s0 + u;
+            const float ws = __shfl_sync(0xffffffffu, (s < 32) ? w0 : w1, s & 31);
+            w[u] = (s < S) ? ws : 0.0f;
+            const float4 *src = base + static_cast<long long>(min(s, S - 1)) * (kD / 4);
+#pragma unroll
+            for (int v = 0; v < 4; ++v) x[u][v] = __ldg(src + v * 32 + lane);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (w[u] != 0.0f) {
+#pragma unroll
+                for (int v = 0; v < 4; ++v) {
+                    acc[4 * v] += w[u] * x[u][v].x;
+                    acc[4 * v + 1] += w[u] * x[u][v].y;
+                    acc[4 * v + 2] += w[u] * x[u][v].z;
+                    acc[4 * v + 3] += w[u] * x[u][v].w;
+                }
             }
         }
     }
@@ -802,7 +830,7 @@ int launch_sparse_mla_attention(const smla_attn_params_t &p, int num_splits, voi
         a.part_ml = a.part_o + static_cast<size_t>(p.num_tokens) * p.num_heads * a.num_splits * kD;
     }
     const long long gx = static_cast<long long>(p.num_tokens) * a.head_blocks;
-    if (gx > 0x7FFFFFFFLL || a.num_splits > 65535) return SMLA_ETOOBIG;
+    if (gx > 0x7FFFFFFFLL || a.num_splits > 64) return SMLA_ETOOBIG;   // the combine kernel keeps two weights per lane
     const dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(a.num_splits));
     rc = (p.cache_format == SMLA_FP8_DS_MLA) ? launch_fwd_npad<SMLA_FP8_DS_MLA>(npad, a, grid, stream)
                                              : launch_fwd_npad<SMLA_INT8_DS_MLA>(npad, a, grid, stream);
