@@ -13,10 +13,12 @@ from ._loader import CORE_LIB
 
 SMLA_FP8_DS_MLA = 0
 SMLA_INT8_DS_MLA = 1
+SMLA_STATIC_SCRATCH_BYTES = 32 << 20
+SMLA_ETOOBIG = -5
 
 EXPORTS = (
     "smla_version", "smla_error_string", "smla_choose_num_splits", "smla_attn_workspace_bytes",
-    "smla_decode_plan", "smla_sparse_mla_decode", "smla_sparse_mla_prefill",
+    "smla_decode_plan", "smla_sparse_mla_decode", "smla_sparse_mla_decode_static_scratch", "smla_sparse_mla_prefill",
     "smla_quantize_int8_ds_mla_rows", "smla_read_device_status",
 )
 
@@ -79,6 +81,7 @@ def load() -> C.CDLL:
     lib.smla_decode_plan.argtypes = [C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_size_t)]
     lib.smla_sparse_mla_decode.argtypes = [C.POINTER(SmlaAttnParams), C.c_void_p]
     lib.smla_sparse_mla_prefill.argtypes = [C.POINTER(SmlaAttnParams), C.c_void_p]
+    lib.smla_sparse_mla_decode_static_scratch.argtypes = [C.POINTER(SmlaAttnParams), C.c_void_p]
     lib.smla_quantize_int8_ds_mla_rows.argtypes = [C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_void_p,
                                                    C.c_void_p, C.c_void_p]
     lib.smla_read_device_status.argtypes = [C.POINTER(C.c_int)]

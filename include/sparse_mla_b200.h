@@ -105,6 +105,23 @@ SMLA_API int smla_decode_plan(int num_tokens, int num_heads, int max_width, int 
  * csrc/flash_sparse_mla_decode_sm80.cu:1198-1275) for both cache formats. */
 SMLA_API int smla_sparse_mla_decode(const smla_attn_params_t *params, void *stream);
 
+/* Split-KV decode that brings its own scratch: same contract and results as smla_sparse_mla_decode,
+ * but `workspace` / `workspace_bytes` are ignored and the partials go to an array of
+ * SMLA_STATIC_SCRATCH_BYTES that is part of the library image (each GPU that loads the library holds
+ * it until exit).  No counterpart in the reference, whose binding always allocates its partial
+ * buffers through torch (csrc/flash_api.cpp:388-405).  It exists for hosts that cannot allocate
+ * device memory when a decode step runs: every byte of HBM already belongs to the engine's KV-cache
+ * pool, cudaMalloc would synchronise the device inside the latency-critical loop, and it is not
+ * allowed during stream capture.  This function calls no allocator of any kind.
+ *   - Requests whose scratch (smla_attn_workspace_bytes for the chosen split count) exceeds
+ *     SMLA_STATIC_SCRATCH_BYTES are rejected with SMLA_ETOOBIG; nothing is launched.
+ *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress, that
+ *     device current); make that first call before any stream capture.
+ *   - All calls on a device share the array, which keeps the previous call's contents (nothing in it
+ *     needs clearing); calls whose kernels overlap on the GPU race on it. */
+#define SMLA_STATIC_SCRATCH_BYTES (32u << 20)
+SMLA_API int smla_sparse_mla_decode_static_scratch(const smla_attn_params_t *params, void *stream);
+
 /* Sparse MLA prefill (many query tokens, never split).  Replaces run_sparse_mla_prefill
  * (csrc/flash_mla.h:159-160, csrc/flash_sparse_mla_prefill_fused_sm80.cu:468-506). */
 SMLA_API int smla_sparse_mla_prefill(const smla_attn_params_t *params, void *stream);

@@ -1,0 +1,87 @@
+"""The decode entry point that allocates nothing (`smla_sparse_mla_decode_static_scratch`).
+
+Why it exists: a host that has given all of HBM to its own KV-cache pool, or that is inside the
+latency-critical decode loop (cudaMalloc synchronises the device) or a stream capture, cannot
+allocate the split-KV scratch when the step runs.  This entry point keeps that scratch in an array
+that ships inside the library.  The test calls it through the C ABI twice in a row -- the second
+call with different queries, so leftovers of the first call in the shared array would show -- and
+compares each result with the regular entry point fed a torch-allocated workspace.
+
+Collected last (file name), so a run that stops at the first failure has already run everything
+else; it passes alone in a fresh process as well as after the other tests.
+"""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+SCALE = 1.0 / math.sqrt(512)
+
+
+def _case(seed, T=3, H=64, st=128, et=1024):
+    from helpers import int8_cache_from_latent
+    rng = np.random.default_rng(seed)
+    torch.manual_seed(seed)
+    sq, ss, swa_K, b1 = int8_cache_from_latent((rng.standard_normal((512, 512)) * 2).astype(np.float32), 64, "inline528")
+    eq, es, extra_K, b2 = int8_cache_from_latent((rng.standard_normal((2048, 512)) * 2).astype(np.float32), 64, "inline528")
+    q = torch.randn(T, H, 512, device="cuda").to(torch.bfloat16)
+    si = torch.randint(0, 512, (T, st), dtype=torch.int32, device="cuda")
+    ei = torch.randint(-3, 2048 + 3, (T, et), dtype=torch.int32, device="cuda")      # a few invalid ids
+    sl = torch.randint(1, st + 1, (T,), dtype=torch.int32, device="cuda")
+    el = torch.randint(et // 2, et + 1, (T,), dtype=torch.int32, device="cuda")
+    sink = torch.randn(H, device="cuda") * 0.1
+    return dict(q=q, sq=sq, ss=ss, eq=eq, es=es, si=si, ei=ei, sl=sl, el=el, sink=sink, swa_K=swa_K, extra_K=extra_K,
+                keep=(b1, b2))
+
+
+def _params(c_abi, c, out, splits, workspace=None):
+    return c_abi.attn_params(c["q"], out, c_abi.SMLA_INT8_DS_MLA, SCALE,
+                             c_abi.stream_from_tensors(c["sq"], c["ss"], c["si"], c["sl"]),
+                             c_abi.stream_from_tensors(c["eq"], c["es"], c["ei"], c["el"]), c["sink"],
+                             num_splits=splits, workspace=workspace)
+
+
+def test_static_scratch_decode_matches_regular_decode_twice():
+    from flash_mla import c_abi
+    from helpers import assert_attention_close, device_status, oracle_out
+    lib = c_abi.load()
+    stream = torch.cuda.current_stream().cuda_stream
+    splits = 5                                            # 1152 rows -> 9 tiles -> 2 tiles per split
+    for seed in (101, 202):                               # two calls in a row on the shared array
+        c = _case(seed)
+        T, H = c["q"].shape[:2]
+        ws = torch.empty(lib.smla_attn_workspace_bytes(T, H, splits) // 4, dtype=torch.float32, device="cuda")
+        want = torch.empty_like(c["q"])
+        c_abi.check(lib.smla_sparse_mla_decode(_params(c_abi, c, want, splits, ws), stream), "regular decode")
+        got = torch.full_like(c["q"], float("nan"))
+        c_abi.check(lib.smla_sparse_mla_decode_static_scratch(_params(c_abi, c, got, splits), stream),
+                    "static-scratch decode")
+        torch.cuda.synchronize()
+        assert_attention_close(got, want.float().cpu().numpy(), f"static scratch vs regular, seed {seed}")
+        assert torch.equal(got, want)                     # same kernels, same schedule: same bits
+        ref = oracle_out(c["q"], c["swa_K"], c["si"], c["sl"], c["extra_K"], c["ei"], c["el"], scale=SCALE, sink=c["sink"])
+        assert_attention_close(got, ref, f"static scratch vs oracle, seed {seed}")
+    # automatic split choice goes through the same array
+    c = _case(303, T=1)
+    got, want = torch.empty_like(c["q"]), torch.empty_like(c["q"])
+    c_abi.check(lib.smla_sparse_mla_decode_static_scratch(_params(c_abi, c, got, 0), stream))
+    c_abi.check(lib.smla_sparse_mla_decode(_params(c_abi, c, want, 1), stream))
+    torch.cuda.synchronize()
+    assert_attention_close(got, want.float().cpu().numpy(), "auto splits vs one split")
+    assert device_status() == 0
+
+
+def test_static_scratch_rejects_requests_beyond_its_capacity():
+    from flash_mla import c_abi
+    lib = c_abi.load()
+    c = _case(404, T=64)
+    out = torch.zeros_like(c["q"])
+    splits = 9
+    assert lib.smla_attn_workspace_bytes(64, 64, splits) > c_abi.SMLA_STATIC_SCRATCH_BYTES
+    rc = lib.smla_sparse_mla_decode_static_scratch(_params(c_abi, c, out, splits), torch.cuda.current_stream().cuda_stream)
+    assert rc == c_abi.SMLA_ETOOBIG
+    assert b"capacity" in lib.smla_error_string(rc)
+    torch.cuda.synchronize()
+    assert torch.all(out == 0)                            # nothing was launched
