@@ -61,6 +61,33 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
 }
 
+// Same contract, but polls with the non-blocking test_wait (the thread is never suspended).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_spin_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+    if (mbar_test_wait(bar, parity)) return true;
+    if (*abort_flag != 0) return false;
+    const uint64_t t0 = globaltimer_ns();
+    for (uint32_t it = 1;; ++it) {
+        if (mbar_test_wait(bar, parity)) return true;
+        if ((it & 1023u) == 0u) {
+            if (*abort_flag != 0) return false;
+            if (globaltimer_ns() - t0 > kWaitLimitNs) return false;
+        }
+    }
+}
+
 // ----------------------------------------------------------------------------- fences / barriers
 __device__ __forceinline__ void fence_async_smem() {   // generic-proxy smem writes -> async proxy (tensor core)
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
