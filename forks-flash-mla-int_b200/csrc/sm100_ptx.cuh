@@ -61,6 +61,19 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
 }
 
+// Time-bounded wait that ignores the CTA's stop word (used to drain the tensor pipe while stopping).
+__device__ __forceinline__ bool mbar_wait_plain(uint32_t bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = globaltimer_ns();
+    for (uint32_t it = 1;; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 63u) == 0u && globaltimer_ns() - t0 > kWaitLimitNs) return false;
+    }
+}
+__device__ __forceinline__ void mbar_inval(uint32_t bar) {
+    asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+
 // Same contract, but polls with the non-blocking test_wait (the thread is never suspended).
 __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;

@@ -1,8 +1,8 @@
 #!/usr/bin/env python3
 """Generate the golden fixtures in this directory FROM THE REFERENCE'S OWN PYTHON CODE.
 
-Run once in a container that has the reference checkout (default /root/reference,
-override with REFERENCE_ROOT); the .npz files it writes are committed and are the only
+Run once in a container that has the reference checkout (path in REFERENCE_ROOT;
+the .npz files it writes are committed and are the only
 thing the tests read.  Imported from the reference (nothing is copied):
 
 * ``_ref``                      tests/test_sparse_mla_prefill_adversarial.py:25-53

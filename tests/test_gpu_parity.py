@@ -334,6 +334,29 @@ def test_outlier_rows_and_large_scores(fm):
     assert_attention_close(out, ref, "outliers")
 
 
+def test_scores_jump_far_above_the_first_tile(fm):
+    """The softmax reference is fixed from the first 64 rows; rows that score more than 2^72 above
+    them make the kernel start the token over with a higher reference.  First rows are zero rows
+    (invalid ids), later rows are large and aligned differently per head, so scores jump by hundreds
+    of log2 units for some heads and fall for others."""
+    rng = np.random.default_rng(77)
+    torch.manual_seed(77)
+    T, H, topk = 2, 64, 448
+    lat = np.zeros((512, 512), np.float32)
+    lat[64:] = rng.standard_normal((448, 512)) * 0.05 + rng.choice([-60.0, 60.0, 90.0], size=(448, 1))
+    cache, K = fp8_cache_from_latent(lat, 64)
+    q = torch.randn(T, H, 512, device="cuda").to(torch.bfloat16)
+    idx = torch.arange(topk, dtype=torch.int32, device="cuda").repeat(T, 1)      # rows 0..63 first
+    idx[:, :64] = -1                                                              # zero rows: score 0
+    idx[1] = torch.flip(idx[1], dims=[0])                                         # token 1: big rows first
+    lens = torch.full((T,), topk, dtype=torch.int32, device="cuda")
+    for sink in (None, torch.randn(H, device="cuda")):
+        ref = oracle_out(q, K, idx, lens, scale=SCALE, sink=sink)
+        for op in (fm.sparse_mla_decode_fp8, fm.sparse_mla_prefill):
+            out = op(q, cache, idx, lens, scale=SCALE, attn_sink=sink)
+            assert_attention_close(out, ref, f"score jump {op.__name__}")
+
+
 # ----------------------------------------------------------------------------- argument errors
 def test_argument_errors(fm):
     q = torch.randn(2, 64, 512, device="cuda").to(torch.bfloat16)
