@@ -54,18 +54,26 @@ const char *smla_error_string(int code) {
 }
 
 int smla_choose_num_splits(int sm_count, int num_tokens, int num_heads, int max_width_rows) {
-    // One CTA per (token, block of 64 heads) occupies one SM; splits only fill SMs that would
-    // otherwise idle, and a split never gets less than one 128-row tile.
-    int rows_per_split = 128;
+    // The attention kernel is persistent.  With plenty of items (token x block of 64 heads) per SM,
+    // whole items dealt out to the CTAs keep every SM busy and nothing needs merging: 1.  Otherwise
+    // the tiles of all items are cut into equal ranges, one per CTA; each CTA may then leave two
+    // partial segments in scratch.  The value returned sizes that scratch through
+    // smla_attn_workspace_bytes(): room for two partial slots per CTA plus the merge descriptors.
+    int rows_per_cta = 128;      // a CTA never gets less than this many rows (one 128-row tile)
     if (const char *e = getenv("FLASH_MLA_SLOTS_PER_SPLIT")) {
         const int v = atoi(e);
-        if (v > 0) rows_per_split = ((v + 127) / 128) * 128;
+        if (v > 0) rows_per_cta = ((v + 127) / 128) * 128;
     }
     const int head_blocks = (num_heads + 63) / 64;
-    const long long ctas = static_cast<long long>(std::max(num_tokens, 1)) * head_blocks;
-    const int by_sms = static_cast<int>(std::max<long long>(1, sm_count / ctas));
-    const int by_rows = std::max(1, (max_width_rows + rows_per_split - 1) / rows_per_split);
-    return std::max(1, std::min(std::min(by_sms, by_rows), 64));
+    const long long items = static_cast<long long>(std::max(num_tokens, 1)) * head_blocks;
+    if (sm_count <= 1 || items >= 4ll * sm_count) return 1;
+    const long long pieces = items * std::max(1, (max_width_rows + rows_per_cta - 1) / rows_per_cta);
+    const long long ctas = std::min<long long>(sm_count, pieces);
+    if (ctas <= 1) return 1;
+    const int npad = num_heads <= 16 ? 16 : (num_heads <= 32 ? 32 : 64);
+    const long long head_rows = static_cast<long long>(std::max(num_tokens, 1)) * num_heads;
+    const long long need = (2 * ctas + 1) * npad;       // head rows of scratch; the extra slot covers the descriptors
+    return static_cast<int>(std::max<long long>(2, (need + head_rows - 1) / head_rows));
 }
 
 size_t smla_attn_workspace_bytes(int num_tokens, int num_heads, int num_splits) {

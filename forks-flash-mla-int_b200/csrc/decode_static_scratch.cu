@@ -23,7 +23,7 @@
 
 namespace {
 
-constexpr size_t kStaticScratchBytes = SMLA_STATIC_SCRATCH_BYTES;   // 32 MiB: e.g. 8 tokens x 64 heads x 28 splits
+constexpr size_t kStaticScratchBytes = SMLA_STATIC_SCRATCH_BYTES;   // 64 MiB: two partial slots per CTA of a 148-SM part need 39 MB
 
 static __device__ __align__(256) unsigned char g_decode_static_scratch[kStaticScratchBytes];
 
@@ -62,12 +62,15 @@ int smla_sparse_mla_decode_static_scratch(const smla_attn_params_t *p, void *str
         const int width = p->swa.topk + (p->extra.cache ? p->extra.topk : 0);
         const int rc = smla_decode_plan(p->num_tokens, p->num_heads, width, &splits, nullptr);
         if (rc != SMLA_OK) return rc;
+        // The automatic choice only sizes scratch, so it is cut down to what the array holds (fewer
+        // CTAs share the tiles); below two it becomes the unsplit schedule.
+        while (splits > 1 && smla_attn_workspace_bytes(p->num_tokens, p->num_heads, splits) > kStaticScratchBytes) --splits;
     } else {
         int unused = 0;
         const int rc = smla_decode_plan(1, 1, 1, &unused, nullptr);   // architecture check only
         if (rc != SMLA_OK) return rc;
     }
-    // The request must fit the fixed array; it is never split differently or shrunk behind the caller's back.
+    // An explicit request must fit the fixed array as it is.
     if (smla_attn_workspace_bytes(p->num_tokens, p->num_heads, splits) > kStaticScratchBytes) return SMLA_ETOOBIG;
     void *scratch = nullptr;
     if (splits > 1) {

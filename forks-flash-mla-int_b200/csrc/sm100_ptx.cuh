@@ -102,6 +102,11 @@ __device__ __forceinline__ bool mbar_spin_wait(uint32_t bar, uint32_t parity, vo
 }
 
 // ----------------------------------------------------------------------------- fences / barriers
+// 16-byte asynchronous copy global -> shared; bytes beyond `src_bytes` (0 or 16) are zero-filled.
+__device__ __forceinline__ void cp_async_16_zfill(uint32_t dst, const void *src, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() {   // generic-proxy smem writes -> async proxy (tensor core)
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }

@@ -37,20 +37,36 @@
 #include <cstdlib>
 
 #include "sm100_ptx.cuh"
+#include <algorithm>
+
 #include "smla_internal.h"
 
 namespace smla {
 
 __device__ int g_device_status = 0;
 
-#ifdef SMLA_TRACE   // developer timing trace of CTA 0 (never defined in the product build)
+#ifdef SMLA_TRACE   // developer timing trace of one CTA (never defined in the product build)
+#ifndef SMLA_TRACE_CTA
+#define SMLA_TRACE_CTA 0
+#endif
 __device__ unsigned long long g_trace[32 * 16];
 #define SMLA_MARK(tile, k)                                                              \
     do {                                                                                \
-        if (blockIdx.x == 0 && blockIdx.y == 0 && (tile) < 32) g_trace[(tile) * 16 + (k)] = clock64(); \
+        if (blockIdx.x == SMLA_TRACE_CTA && (tile) < 32) g_trace[(tile) * 16 + (k)] = clock64(); \
+    } while (0)
+__device__ unsigned long long g_cta_times[256 * 4];
+__device__ __forceinline__ unsigned long long smla_globaltimer() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define SMLA_CTA_MARK(k)                                                                        \
+    do {                                                                                        \
+        if (threadIdx.x == 0 && blockIdx.x < 256) g_cta_times[blockIdx.x * 4 + (k)] = smla_globaltimer(); \
     } while (0)
 #else
 #define SMLA_MARK(tile, k) do {} while (0)
+#define SMLA_CTA_MARK(k) do {} while (0)
 #endif
 
 namespace {
@@ -62,9 +78,9 @@ constexpr int kWorkerThreads = kWorkerWarps * 32;
 constexpr int kMmaWarp = kWorkerWarps;           // one more warp: TMEM allocation and every tcgen05.mma
 constexpr int kThreads = kWorkerThreads + 128;   // 640: the MMA warp plus three idle warps (register
                                                  // files are handed out per group of four warps)
-// No register rebalancing between the roles: setmaxnreg.inc blocks with no time limit until the
-// registers it asks for have been released inside the same CTA, a hang this kernel has no way to
-// bound.  Every thread gets the 96 registers __launch_bounds__(640, 1) allows.
+// No register rebalancing between the roles (setmaxnreg): measured, ptxas spills whatever is live
+// above the lower budget at the release point and the worker code gains nothing.  Every thread has
+// the 96 registers __launch_bounds__(640, 1) allows.
 constexpr int kNumWarps = kThreads / 32;
 constexpr int kCoreBytes = 128;                  // one 8x16B core matrix
 constexpr int kRowGroupBytes = 64 * kCoreBytes;  // 8 rows x 512 dims of bf16
@@ -79,8 +95,9 @@ constexpr int kBarReady = 0;   // [4] K chunk c holds this tile (16 arrivals: on
 constexpr int kBarFree = 4;    // [4] PV of the previous tile has finished reading K chunk c
 constexpr int kBarS = 8;       //     S^T of this tile is complete in TMEM
 constexpr int kBarP = 9;       //     P^T of this tile is in shared memory (16 arrivals)
-constexpr int kBarO = 10;      //     the last PV has completed
-static_assert(kBarO + 1 <= 12, "mbarrier slots reserved in Smem");
+constexpr int kBarO = 10;      //     the last PV of a segment has completed
+constexpr int kBarOFree = 11;  //     the segment's epilogue has read O^T (16 arrivals)
+static_assert(kBarOFree + 1 <= 12, "mbarrier slots reserved in Smem");
 
 struct StreamDev {
     const uint8_t *cache;
@@ -97,10 +114,11 @@ struct KernelArgs {
     __nv_bfloat16 *out;
     long long o_ts, o_hs;
     const float *sink;
-    float *part_o;   // fp32 [T, H, S, 512] un-normalised partial outputs (S > 1)
-    float *part_ml;  // fp32 [T, H, S, 2]   {reference max (log2 units), denominator}
+    float *part_o;   // fp32 [slot, NPAD, 512] un-normalised partial outputs (balanced schedule)
+    float *part_ml;  // fp32 [slot, NPAD, 2]   {reference max (log2 units), denominator}
+    int *desc;       // int4 [CTA] merge descriptors {item, segments, first slot, heads} or {-1}
     StreamDev swa, extra;
-    int T, H, head_blocks, num_splits;
+    int T, H, head_blocks, balanced;
     float scale_log2;
 };
 
@@ -112,10 +130,17 @@ struct Smem {
     static constexpr int kRed = kP + NPAD * 256;         // [4][NPAD] floats
     static constexpr int kM = kRed + 4 * NPAD * 4;       // running reference max per head
     static constexpr int kAlpha = kM + NPAD * 4;         // rescale factor / final 1/l per head
-    static constexpr int kBars = kAlpha + NPAD * 4;      // kNumBars mbarriers
+    static constexpr int kShift = kAlpha + NPAD * 4;     // m_old - m_new of the last reference move
+    static constexpr int kBars = kShift + NPAD * 4;      // kNumBars mbarriers
     static constexpr int kTmemPtr = kBars + 12 * 8;
     static constexpr int kAbort = kTmemPtr + 4;
-    static constexpr int kTotal = kAbort + 4 + 8;
+    static constexpr int kSched = kAbort + 4 + 8;        // 160 ints: work distribution (scan scratch, iterator, segment ring)
+    // Epilogue staging, 8 KB per column-slice group.  With 64 heads only 16 KB are left, so groups 0
+    // and 1 stage in the P buffer (idle between a segment's last PV and the next softmax).
+    static constexpr int kStage = kSched + 640;
+    static constexpr int kStageBytes = (NPAD == 64) ? 16384 : 32768;
+    static constexpr int kTotal = kStage + kStageBytes;
+    static_assert(kTotal <= 232448, "more than 227 KB of shared memory");
 };
 
 // ------------------------------------------------------------------ small device helpers
@@ -326,10 +351,261 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatil
     return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
+// ------------------------------------------------------------------ work distribution
+// The grid is persistent: `gridDim.x` CTAs (at most one per SM) share the launch's work, which is the
+// list of items (token t, block of 64 heads hb), item = t * head_blocks + hb, each made of
+// ceil(rows(t) / 128) tiles.  Two ways of sharing it:
+//   whole items (balanced == 0): CTA c takes items c, c + P, c + 2P, ...; every output is final.
+//   balanced tiles (balanced == 1): the tiles of all items, in item order, are cut into P equal
+//     contiguous ranges.  A CTA's range starts and ends inside items, so its first and last segment
+//     may be partial: those go to scratch slots 2c and 2c + 1 as un-normalised fp32 partials and a
+//     second kernel merges them; the items in between are final.  This is what keeps all SMs busy
+//     when there are fewer items than SMs or the items differ in length (ragged lens).
+// Items without rows count as one tile so that somebody owns (and zeroes) their output.
+struct Seg {
+    int t, hb;       // item
+    int n, ns;       // selected rows of the token: total, and of the swa stream
+    int tile0, ntl;  // tiles of the item this segment covers (ntl == 0: the item has no rows)
+    int slot;        // scratch slot of a partial segment
+    bool complete;   // the segment is the whole item: write the final output
+    bool owns_first; // partial segment holding the item's first tile: it writes the merge descriptor
+    long long gfirst; // global tile index of the item's first tile (balanced mode)
+    int ntS;         // scheduled tiles of the item (max(1, tiles))
+};
+
+__device__ __forceinline__ void token_rows(const KernelArgs &a, int t, int &ns, int &n) {
+    ns = min(max(__ldg(a.swa.lens + t), 0), a.swa.topk);
+    const int ne = (a.extra.cache != nullptr) ? min(max(__ldg(a.extra.lens + t), 0), a.extra.topk) : 0;
+    n = ns + ne;
+}
+__device__ __forceinline__ int sched_tiles(int n) { return max(1, (n + kTileRows - 1) / kTileRows); }
+
+struct SegIter {
+    int t, hb;          // next item
+    int off;            // first tile of that item still to do (balanced mode)
+    long long gpos;     // global tile index of (t, hb, off) (balanced mode)
+    long long rem;      // tiles left in this CTA's range (balanced mode)
+    int item, stride;   // whole-item mode
+    bool first;
+
+};
+
+__device__ __forceinline__ bool iter_next(const KernelArgs &a, SegIter &it, Seg &s) {
+    {
+        int &t = it.t, &hb = it.hb, &off = it.off, &item = it.item;
+        const int stride = it.stride;
+        long long &gpos = it.gpos, &rem = it.rem;
+        bool &first = it.first;
+        if (!a.balanced) {
+            if (item >= a.T * a.head_blocks) return false;
+            s.t = item / a.head_blocks;
+            s.hb = item - s.t * a.head_blocks;
+            token_rows(a, s.t, s.ns, s.n);
+            s.tile0 = 0;
+            s.ntl = (s.n + kTileRows - 1) / kTileRows;
+            s.ntS = max(1, s.ntl);
+            s.slot = 0;
+            s.complete = true;
+            s.owns_first = false;
+            s.gfirst = 0;
+            item += stride;
+            return true;
+        }
+        if (rem <= 0) return false;
+        s.t = t;
+        s.hb = hb;
+        token_rows(a, t, s.ns, s.n);
+        const int nt = (s.n + kTileRows - 1) / kTileRows;
+        s.ntS = max(1, nt);
+        const int take = static_cast<int>(min(static_cast<long long>(s.ntS - off), rem));
+        s.tile0 = off;
+        s.ntl = nt == 0 ? 0 : take;
+        s.complete = (off == 0 && take == s.ntS);
+        s.owns_first = (!s.complete && off == 0);
+        s.slot = 2 * static_cast<int>(blockIdx.x) + (first ? 0 : 1);
+        s.gfirst = gpos - off;
+        first = false;
+        rem -= take;
+        gpos += take;
+        off = 0;
+        if (++hb == a.head_blocks) {
+            hb = 0;
+            ++t;
+        }
+        return true;
+    }
+}
+
+// First tile of CTA c when W tiles are shared by P CTAs, and the CTA a given tile falls to.
+__device__ __forceinline__ long long range_begin(long long c, long long W, long long P) { return c * W / P; }
+__device__ __forceinline__ int cta_of_tile(long long x, long long W, long long P) {
+    return static_cast<int>(((x + 1) * P + W - 1) / W - 1);
+}
+
+// Every thread of the CTA calls this; returns false when the CTA has nothing to do.  `scratch` is a
+// shared-memory array of at least 24 ints.  `W_out` / `P_out`: total scheduled tiles and the number
+// of CTAs that share them (needed later for the merge descriptors).
+__device__ bool make_schedule(const KernelArgs &a, int *scratch, SegIter &it, long long &W_out, int &P_out) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    it.first = true;
+    it.off = 0;
+    it.gpos = 0;
+    it.rem = 0;
+    it.t = it.hb = 0;
+    it.item = blockIdx.x;
+    it.stride = gridDim.x;
+    W_out = 0;
+    P_out = gridDim.x;
+    if (!a.balanced) return it.item < a.T * a.head_blocks;
+
+    // pass 1: W = head_blocks * sum_t max(1, tiles(t))
+    long long mine = 0;
+    for (int t = tid; t < a.T; t += kThreads) {
+        int ns, n;
+        token_rows(a, t, ns, n);
+        mine += sched_tiles(n);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, o);
+    long long *wsum = reinterpret_cast<long long *>(scratch);          // [kNumWarps] then results
+    if (lane == 0) wsum[warp] = mine;
+    __syncthreads();
+    long long W = 0;
+    for (int w = 0; w < kNumWarps; ++w) W += wsum[w];
+    W *= a.head_blocks;
+    __syncthreads();
+    const long long P = min(static_cast<long long>(gridDim.x), W);
+    W_out = W;
+    P_out = static_cast<int>(P);
+    if (static_cast<long long>(blockIdx.x) >= P) return false;
+    const long long lo = range_begin(blockIdx.x, W, P), hi = range_begin(blockIdx.x + 1, W, P);
+
+    // pass 2: the token whose tiles contain global tile `lo`
+    int *found = scratch + 2 * kNumWarps;       // {t, excl_lo, excl_hi}
+    long long run = 0;
+    for (int base = 0; base < a.T; base += kThreads) {
+        const int t = base + tid;
+        long long v = 0;
+        if (t < a.T) {
+            int ns, n;
+            token_rows(a, t, ns, n);
+            v = static_cast<long long>(sched_tiles(n)) * a.head_blocks;
+        }
+        long long incl = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const long long up = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += up;
+        }
+        if (lane == 31) wsum[warp] = incl;
+        __syncthreads();
+        long long before = run, total = 0;
+        for (int w = 0; w < kNumWarps; ++w) {
+            if (w < warp) before += wsum[w];
+            total += wsum[w];
+        }
+        const long long excl = before + incl - v;
+        if (t < a.T && excl <= lo && lo < excl + v) {
+            found[0] = t;
+            found[1] = static_cast<int>(excl & 0xFFFFFFFFll);
+            found[2] = static_cast<int>(excl >> 32);
+        }
+        run += total;
+        __syncthreads();
+        if (run > lo) break;     // uniform: every thread holds the same `run`
+    }
+    const int t0 = found[0];
+    const long long excl0 = (static_cast<long long>(found[2]) << 32) | static_cast<unsigned int>(found[1]);
+    int ns, n;
+    token_rows(a, t0, ns, n);
+    const int ntS = sched_tiles(n);
+    const long long d = lo - excl0;
+    it.t = t0;
+    it.hb = static_cast<int>(d / ntS);
+    it.off = static_cast<int>(d - static_cast<long long>(it.hb) * ntS);
+    it.gpos = lo;
+    it.rem = hi - lo;
+    return true;
+}
+
+// The segments live in shared memory, not in registers: a ring of five records (segment k in record
+// k % 5) that warp 0 fills three segments ahead (the MMA thread reads it too) and the iterator state it
+// continues from.  Offsets in ints from Smem::kSched:
+constexpr int kSchedScan = 0;       // [64]  scratch of make_schedule
+constexpr int kSchedIter = 64;      // [12]  t, hb, off, item, stride, first, gpos(2), rem(2), W(2)
+constexpr int kSchedP = 76;         // [1]   CTAs sharing the tiles
+constexpr int kSchedRec = 80;       // [5][12] t, hb, n, ns, tile0, ntl, slot, flags, last CTA of the item
+constexpr int kSchedInts = kSchedRec + 60;
+static_assert(kSchedInts <= 160, "Smem::kSched holds 160 ints");
+constexpr int kSegValid = 4, kSegOwnsFirst = 2, kSegComplete = 1;
+
+__device__ __forceinline__ void store_iter(int *p, const SegIter &it, long long W) {
+    p[0] = it.t, p[1] = it.hb, p[2] = it.off, p[3] = it.item, p[4] = it.stride, p[5] = it.first ? 1 : 0;
+    p[6] = static_cast<int>(it.gpos & 0xFFFFFFFFll), p[7] = static_cast<int>(it.gpos >> 32);
+    p[8] = static_cast<int>(it.rem & 0xFFFFFFFFll), p[9] = static_cast<int>(it.rem >> 32);
+    p[10] = static_cast<int>(W & 0xFFFFFFFFll), p[11] = static_cast<int>(W >> 32);
+}
+__device__ __forceinline__ void load_iter(const int *p, SegIter &it, long long &W) {
+    it.t = p[0], it.hb = p[1], it.off = p[2], it.item = p[3], it.stride = p[4], it.first = p[5] != 0;
+    it.gpos = (static_cast<long long>(p[7]) << 32) | static_cast<unsigned int>(p[6]);
+    it.rem = (static_cast<long long>(p[9]) << 32) | static_cast<unsigned int>(p[8]);
+    W = (static_cast<long long>(p[11]) << 32) | static_cast<unsigned int>(p[10]);
+}
+
+// An item without rows: its output is zero (the reference's "no selected slot" case).
+__device__ __forceinline__ void zero_item(const KernelArgs &a, const Seg &s, int tid, int nthreads) {
+    const int h0 = s.hb * 64, hv = min(64, a.H - h0);
+    for (int i = tid; i < hv * (kD / 8); i += nthreads) {
+        const int h = i / (kD / 8), d8 = i - h * (kD / 8);
+        *reinterpret_cast<uint4 *>(a.out + static_cast<long long>(s.t) * a.o_ts + static_cast<long long>(h0 + h) * a.o_hs +
+                                   d8 * 8) = make_uint4(0, 0, 0, 0);
+    }
+}
+
+// Warp 0 (all lanes, uniformly): continue the iterator to the next segment that has tiles, zeroing the
+// outputs of items without rows on the way, and publish it as segment `k`.
+__device__ __forceinline__ void publish_segment(const KernelArgs &a, int *sched, int k, int lane) {
+    SegIter it;
+    long long W;
+    load_iter(sched + kSchedIter, it, W);
+    const int P = sched[kSchedP];
+    Seg s = {};
+    bool ok = false;
+    while (iter_next(a, it, s)) {
+        if (s.ntl > 0) {
+            ok = true;
+            break;
+        }
+        zero_item(a, s, lane, 32);
+    }
+    {   // warm the lens of the tokens the next calls will ask for (lane i: i + 1 items ahead)
+        const long long ahead = a.balanced ? static_cast<long long>(it.t) + lane
+                                           : (static_cast<long long>(it.item) + static_cast<long long>(lane) * it.stride) / a.head_blocks;
+        if (ahead < a.T) {
+            asm volatile("prefetch.global.L1 [%0];" ::"l"(a.swa.lens + ahead));
+            if (a.extra.cache != nullptr) asm volatile("prefetch.global.L1 [%0];" ::"l"(a.extra.lens + ahead));
+        }
+    }
+    __syncwarp();
+    if (lane == 0) {
+        store_iter(sched + kSchedIter, it, W);
+        int *r = sched + kSchedRec + 12 * (k % 5);
+        r[0] = s.t, r[1] = s.hb, r[2] = s.n, r[3] = s.ns, r[4] = s.tile0, r[5] = s.ntl, r[6] = s.slot;
+        r[7] = ok ? (kSegValid | (s.owns_first ? kSegOwnsFirst : 0) | (s.complete ? kSegComplete : 0)) : 0;
+        r[8] = (ok && s.owns_first) ? cta_of_tile(s.gfirst + s.ntS - 1, W, P) : 0;
+    }
+    __syncwarp();
+}
+
 // ------------------------------------------------------------------ MMA issue (lane 0 of the MMA warp)
+// Walks the segments the workers publish.  Barrier phases are counted over the CTA's whole life:
+// `gt` tiles for the per-tile barriers, `so` segments for the two accumulator barriers.
 template <int NPAD>
-__device__ __forceinline__ void mma_role(uint8_t *smem, uint32_t tmem_base, int ntl) {
+__device__ __forceinline__ void mma_role(uint8_t *smem, uint32_t tmem_base) {
     using L = Smem<NPAD>;
+    // Segment k is read from record k % 5 of the ring.  Warp 0 wrote it three segments earlier, before
+    // conversions this thread has since waited for, and overwrites it only during segment k + 2.
+    const volatile int *ring = reinterpret_cast<const volatile int *>(smem + L::kSched) + kSchedRec;
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::kAbort);
     const uint32_t bars = smem_u32(smem + L::kBars);
     constexpr uint32_t idesc_qk = umma_idesc_bf16(128, NPAD, 0, 0);
@@ -348,44 +624,82 @@ __device__ __forceinline__ void mma_role(uint8_t *smem, uint32_t tmem_base, int 
     const uint32_t pa_lo = static_cast<uint32_t>(pa), pa_hi = static_cast<uint32_t>(pa >> 32);
     const uint32_t pb_lo = static_cast<uint32_t>(pb), pb_hi = static_cast<uint32_t>(pb >> 32);
 
-    for (int it = 0; it < ntl; ++it) {
-        SMLA_MARK(it, 0);
+    int gt = 0;
+    for (int so = 0;; ++so) {
+        const volatile int *rec = ring + 12 * (so % 5);
+        if ((rec[7] & kSegValid) == 0) break;
+        const int ntl = rec[5];
+        for (int it = 0; it < ntl; ++it, ++gt) {
+            SMLA_MARK(gt, 0);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            if (!mbar_wait(bars + (kBarReady + c) * 8, it & 1, abort_flag)) {
+            for (int c = 0; c < 4; ++c) {
+                if (!mbar_wait(bars + (kBarReady + c) * 8, gt & 1, abort_flag)) {
+                    give_up(abort_flag, kStatusMmaWait);
+                    return;
+                }
+                tc_fence_after_sync();
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const uint32_t off = static_cast<uint32_t>(((16 * c + 2 * k) * kCoreBytes) >> 4);
+                    umma_bf16_ss_lohi(tmem_base, qa_lo + off, qa_hi, qb_lo + off, qb_hi, idesc_qk,
+                                      (c | k) != 0 ? 1u : 0u);
+                }
+            }
+            umma_commit(bars + kBarS * 8);
+            SMLA_MARK(gt, 1);
+            if (!mbar_wait(bars + kBarP * 8, gt & 1, abort_flag)) {
+                give_up(abort_flag, kStatusMmaWait);
+                return;
+            }
+            // The first PV of a segment overwrites O^T: the previous segment's epilogue must have read it.
+            if (it == 0 && so > 0 && !mbar_wait(bars + kBarOFree * 8, (so - 1) & 1, abort_flag)) {
                 give_up(abort_flag, kStatusMmaWait);
                 return;
             }
             tc_fence_after_sync();
+            SMLA_MARK(gt, 5);
+            const uint32_t acc0 = it > 0 ? 1u : 0u;
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                const uint32_t off = static_cast<uint32_t>(((16 * c + 2 * k) * kCoreBytes) >> 4);
-                umma_bf16_ss_lohi(tmem_base, qa_lo + off, qa_hi, qb_lo + off, qb_hi, idesc_qk, (c | k) != 0 ? 1u : 0u);
+            for (int c = 0; c < 4; ++c) {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const uint32_t aoff = static_cast<uint32_t>((c * 16 * kCoreBytes + 2 * k * kRowGroupBytes) >> 4);
+                    const uint32_t boff = static_cast<uint32_t>((2 * k * kCoreBytes) >> 4);
+                    umma_bf16_ss_lohi(tmem_base + kTmemOCol + c * NPAD, pa_lo + aoff, pa_hi, pb_lo + boff, pb_hi,
+                                      idesc_pv, k > 0 ? 1u : acc0);
+                }
+                umma_commit(bars + (kBarFree + c) * 8);   // chunk c of the K buffer may be refilled
             }
+            if (it + 1 == ntl) umma_commit(bars + kBarO * 8);
+            SMLA_MARK(gt, 6);
         }
-        umma_commit(bars + kBarS * 8);
-        SMLA_MARK(it, 1);
-        if (!mbar_wait(bars + kBarP * 8, it & 1, abort_flag)) {
-            give_up(abort_flag, kStatusMmaWait);
-            return;
-        }
-        tc_fence_after_sync();
-        SMLA_MARK(it, 5);
-        const uint32_t acc0 = it > 0 ? 1u : 0u;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                const uint32_t aoff = static_cast<uint32_t>((c * 16 * kCoreBytes + 2 * k * kRowGroupBytes) >> 4);
-                const uint32_t boff = static_cast<uint32_t>((2 * k * kCoreBytes) >> 4);
-                umma_bf16_ss_lohi(tmem_base + kTmemOCol + c * NPAD, pa_lo + aoff, pa_hi, pb_lo + boff, pb_hi, idesc_pv,
-                                  k > 0 ? 1u : acc0);
-            }
-            umma_commit(bars + (kBarFree + c) * 8);   // chunk c of the K buffer may be refilled
-        }
-        if (it + 1 == ntl) umma_commit(bars + kBarO * 8);
-        SMLA_MARK(it, 6);
     }
+}
+
+// ------------------------------------------------------------------ pieces shared by prologue and workers
+// Q tile of one item -> shared memory (K-major core matrices), with cp.async so that no registers are
+// held and all pieces are in flight at once; heads beyond the item's last one are zero-filled.
+// The caller later runs cp_async_wait_all() + fence_async_smem() before the tensor pipe may read it.
+template <int NPAD>
+__device__ __forceinline__ void issue_q_tile(const KernelArgs &a, uint8_t *smem, int t, int h0, int hvalid, int warp,
+                                             int lane, int nwarps) {
+    using L = Smem<NPAD>;
+    const __nv_bfloat16 *qt = a.q + static_cast<long long>(t) * a.q_ts + static_cast<long long>(h0) * a.q_hs;
+    const uint32_t q_addr = smem_u32(smem + L::kQ);
+    for (int idx = warp; idx < (NPAD / 8) * 16; idx += nwarps) {
+        const int hg = idx >> 4, dg = (idx & 15) * 4 + (lane >> 3), h = hg * 8 + (lane & 7);
+        const bool ok = h < hvalid;
+        const __nv_bfloat16 *src = qt + static_cast<long long>(ok ? h : 0) * a.q_hs + dg * 8;
+        cp_async_16_zfill(q_addr + hg * kRowGroupBytes + dg * kCoreBytes + (lane & 7) * 16, src, ok ? 16u : 0u);
+    }
+}
+
+__device__ __forceinline__ float initial_ref(const KernelArgs &a, bool complete, int h0, int hl, int hvalid) {
+    // A complete item folds the sink into its own denominator, so the sink takes part in the reference.
+    // Without a sink the reference starts at 0: it has to be finite (scores are held relative to it)
+    // and the first tile replaces it anyway.
+    if (complete && a.sink != nullptr && hl < hvalid) return ceilf(a.sink[h0 + hl] * kLog2e);
+    return 0.0f;
 }
 
 // ------------------------------------------------------------------ worker warps (0..15)
@@ -393,25 +707,27 @@ __device__ __forceinline__ void mma_role(uint8_t *smem, uint32_t tmem_base, int 
 //   convert: it owns rows 8w..8w+7 of the tile; raw bytes (already in registers) -> bf16 K chunks;
 //   softmax: it owns TMEM lanes 32*(w%4).. (rows of S^T / dims of O^T) and head columns
 //            (NPAD/4)*(w/4)..: scores -> P^T, running denominators, rare accumulator rescale.
+// The raw bytes of the next tile are always in flight, across segment boundaries too, and the next
+// item's Q tile is fetched while the last PV of the current one runs.
 template <int FMT, int NPAD>
-__device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, uint32_t tmem_base, int t, int h0,
-                                            int hvalid, int sp, int ns, int n, int tile0, int ntl, int warp,
-                                            int lane) {
+__device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, uint32_t tmem_base, int warp, int lane) {
     using L = Smem<NPAD>;
     constexpr int J = Steps<FMT>::kCount;
     constexpr int CW = NPAD / 4;   // head columns per warp in the softmax job
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::kAbort);
+    int *sched = reinterpret_cast<int *>(smem + L::kSched);
     const uint32_t bars = smem_u32(smem + L::kBars);
     float *red = reinterpret_cast<float *>(smem + L::kRed);
     float *m_s = reinterpret_cast<float *>(smem + L::kM);
     float *alpha_s = reinterpret_cast<float *>(smem + L::kAlpha);
+    float *shift_s = reinterpret_cast<float *>(smem + L::kShift);
     const int tid = warp * 32 + lane;
-    const bool direct = a.num_splits == 1;
     const bool tracer = (warp == 0 && lane == 0);
     (void)tracer;
 
     // convert job
     const int quarter = lane >> 3;
+    const int my_row = warp * 8 + (lane & 7);
     const uint32_t k_row_addr = smem_u32(smem + L::kK) + warp * kRowGroupBytes + (lane & 7) * 16;
     // softmax job
     const int q = warp & 3, cs = warp >> 2;
@@ -422,168 +738,270 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
                             (col0 & 7) * 2;
     const int group_bar = 1 + cs;
 
-    float lsum[CW];
-#pragma unroll
-    for (int j = 0; j < CW; ++j) lsum[j] = 0.0f;
+    // Softmax denominator: after every tile the warp reduces its 32 rows, so one register per thread
+    // holds the running sum of column col0 + (lane >> kColShift) instead of CW per-row sums.
+    constexpr int kColShift = (CW == 16) ? 1 : (CW == 8) ? 2 : 3;
+    float lacc = 0.0f;
+    int gt = 0;      // tiles done by this CTA (mbarrier phases)
 
-    int g = tile0 * kTileRows + warp * 8 + (lane & 7);
-    RowRef<FMT> cur = make_row_ref<FMT>(a, ns, n, g, load_slot_id(a, t, ns, n, g));
-    uint4 raw[J];
-#pragma unroll
-    for (int j = 0; j < J; ++j) load_step<FMT>(cur, j, quarter, raw[j]);
-    int id_next = (ntl > 1) ? load_slot_id(a, t, ns, n, g + kTileRows) : -1;
-
-    for (int it = 0; it < ntl; ++it) {
-        const bool has_next = it + 1 < ntl;
-        RowRef<FMT> nxt = make_row_ref<FMT>(a, ns, n, has_next ? g + kTileRows : n, id_next);
-        if (it + 2 < ntl) id_next = load_slot_id(a, t, ns, n, g + 2 * kTileRows);
-
-        // ---- convert: raw registers -> K chunks, each as soon as the previous tile's PV released it
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            if (it > 0) warp_wait(bars + (kBarFree + c) * 8, (it - 1) & 1, abort_flag, lane, kStatusGatherWait);
-            if (tracer && c == 0) SMLA_MARK(it, 7);
-#pragma unroll
-            for (int j = 0; j < J; ++j) {
-                const bool mine = (j < 8) ? ((j >> 1) == c) : (c == 3);
-                if (mine) convert_step<FMT>(raw[j], j, quarter, cur.sc0, cur.sc1, k_row_addr);
-            }
-            if (tracer) SMLA_MARK(it, 8 + c);
-            fence_async_smem();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bars + (kBarReady + c) * 8);
-        }
-        if (tracer) SMLA_MARK(it, 12);
-        // Raw bytes of the next tile.  Issued only now, after this tile's last conversion fence: a
-        // proxy fence also waits for the thread's global loads in flight, so loads issued between
-        // the chunks would put a memory latency on every hand-over.  They land while QK^T runs.
-        if (has_next) {
-#pragma unroll
-            for (int j = 0; j < J; ++j) load_step<FMT>(nxt, j, quarter, raw[j]);
-        }
-        cur = nxt;
-        g += kTileRows;
-
-        // ---- softmax of this tile
-        warp_wait(bars + kBarS * 8, it & 1, abort_flag, lane, kStatusSoftmaxWait);
+    // ---- epilogue of a finished segment (record `pg`): O^T / l as final output, or the un-normalised
+    // partial.  `cg`: the segment whose softmax comes next (its reference max is initialised here), or
+    // nullptr.  It runs while the tensor pipe is busy with the next segment's first QK^T, so it must
+    // not touch the K or Q buffers: the final output is turned round (a thread holds one dim of CW
+    // heads, a row of `out` is one head's 512 dims) through a small staging area per column-slice
+    // group, HR heads at a time, so that global stores are 16 bytes per thread and 1 KB per head.
+    auto epilogue = [&](const volatile int *pg, const volatile int *cg, int parity) {
+        constexpr int HR = CW < 8 ? CW : 8;     // heads per staging round
+        const int t = pg[0], h0 = pg[1] * 64, slot = pg[6];
+        const int hvalid = min(NPAD, a.H - h0);
+        const bool direct = (pg[7] & kSegComplete) != 0;
+        warp_wait(bars + kBarO * 8, parity, abort_flag, lane, kStatusEpilogueWait);
         tc_fence_after_sync();
-        if (tracer) SMLA_MARK(it, 2);
-        // sm = S^T * scale - m, with m read once per tile as float4s (the same for all rows).
-        const bool row_valid = (tile0 + it) * kTileRows + row < n;
-        float sm[CW];
-        uint32_t sraw[CW];
-        TmemIO<CW>::ld(tmem_lane + col0, sraw);
-#pragma unroll
-        for (int j = 0; j < CW; ++j)
-            sm[j] = row_valid ? fmaf(__uint_as_float(sraw[j]), a.scale_log2, -m_s[col0 + j]) : -INFINITY;
-        // The reference max m is only moved when some score exceeds it by more than the threshold
-        // (always on the first tile).  The vote spans the four warps that share these columns.
-        bool need = false;
-#pragma unroll
-        for (int j = 0; j < CW; ++j) need |= sm[j] > kRescaleThreshold;
-        if (named_bar_or(group_bar, 128, need)) {
-            float s[CW];
-#pragma unroll
-            for (int j = 0; j < CW; ++j) s[j] = row_valid ? __uint_as_float(sraw[j]) * a.scale_log2 : -INFINITY;
-            float r[1];
-            ColReduce<CW, 16, true>::run(s, lane, r);
-            store_col_partial<CW>(red + q * NPAD + col0, r[0], lane);
-            named_bar_sync(group_bar, 128);
-            if (q == 0 && lane < CW) {
-                const int col = col0 + lane;
-                const float tm = fmaxf(fmaxf(red[col], red[NPAD + col]), fmaxf(red[2 * NPAD + col], red[3 * NPAD + col]));
-                const float m_old = m_s[col];
-                const bool up = tm > m_old + kRescaleThreshold;
-                // m stays INTEGER-valued (log2 units): 2^(s - m) then has the same mantissa whatever m
-                // is, so P rounds to bf16 identically in every split-KV schedule.
-                const float m_new = up ? ceilf(tm) : m_old;
-                alpha_s[col] = up ? fast_exp2(m_old - m_new) : 1.0f;
-                m_s[col] = m_new;
+        if (tracer) SMLA_MARK(gt < 32 ? gt : 31, 13);
+        store_col_partial<CW>(red + q * NPAD + col0, lacc, lane);
+        lacc = 0.0f;
+        named_bar_sync(kAllWorkersBar, kWorkerThreads);
+        if (tid < NPAD) {
+            float l = (red[tid] + red[NPAD + tid]) + (red[2 * NPAD + tid] + red[3 * NPAD + tid]);
+            if (direct) {
+                if (a.sink != nullptr && tid < hvalid) l += fast_exp2(a.sink[h0 + tid] * kLog2e - m_s[tid]);
+                alpha_s[tid] = 1.0f / l;
+            } else if (tid < hvalid) {
+                float *ml = a.part_ml + (static_cast<long long>(slot) * NPAD + tid) * 2;
+                ml[0] = m_s[tid];
+                ml[1] = l;
             }
-            named_bar_sync(group_bar, 128);
-#pragma unroll
-            for (int j = 0; j < CW; ++j) {
-                lsum[j] *= alpha_s[col0 + j];
-                sm[j] = s[j] - m_s[col0 + j];
+            if (cg != nullptr) {   // reference of the segment that follows (read after the barrier)
+                const int c_h0 = cg[1] * 64;
+                m_s[tid] = initial_ref(a, (cg[7] & kSegComplete) != 0, c_h0, tid, min(NPAD, a.H - c_h0));
             }
-            if (it > 0) {   // O^T[:, h] *= alpha[h]; the previous PV completed before this tile's S^T did
+        }
+        named_bar_sync(kAllWorkersBar, kWorkerThreads);
+        if (direct) {
+            const uint32_t stage = (NPAD == 64 && cs < 2) ? smem_u32(smem + L::kP) + cs * 8192
+                                                          : smem_u32(smem + L::kStage) + (NPAD == 64 ? cs - 2 : cs) * 8192;
+            const int gtid = q * 32 + lane;     // thread of the group; also the dim inside a 128-dim chunk
+            __nv_bfloat16 *orow = a.out + static_cast<long long>(t) * a.o_ts + static_cast<long long>(h0 + col0) * a.o_hs;
+#pragma unroll 1
+            for (int r = 0; r < CW / HR; ++r) {
 #pragma unroll 1
                 for (int c = 0; c < 4; ++c) {
-                    uint32_t o[CW];
-                    TmemIO<CW>::ld(tmem_lane + kTmemOCol + c * NPAD + col0, o);
+                    uint32_t o[HR];
+                    TmemIO<HR>::ld(tmem_lane + kTmemOCol + c * NPAD + col0 + r * HR, o);
+                    const uint32_t dst = stage + (c * 128 + gtid) * 2;
 #pragma unroll
-                    for (int j = 0; j < CW; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha_s[col0 + j]);
-                    TmemIO<CW>::st(tmem_lane + kTmemOCol + c * NPAD + col0, o);
+                    for (int j = 0; j < HR; ++j) {
+                        const __nv_bfloat16 v = __float2bfloat16_rn(__uint_as_float(o[j]) * alpha_s[col0 + r * HR + j]);
+                        asm volatile("st.shared.u16 [%0], %1;" ::"r"(dst + j * 1024), "h"(*reinterpret_cast<const uint16_t *>(&v)) : "memory");
+                    }
                 }
-                tmem_st_wait();
-            }
-        }
-        if (tracer) SMLA_MARK(it, 3);
-        {   // P^T = 2^(S^T - m) rounded to bf16, MN-major B-operand layout (8 heads = 16 bytes per row)
-            uint32_t pk[CW / 2];
+                named_bar_sync(group_bar, 128);
 #pragma unroll
-            for (int j = 0; j < CW; j += 2) {
-                const float p0 = fast_exp2(sm[j]);
-                const float p1 = fast_exp2(sm[j + 1]);
-                lsum[j] += p0;
-                lsum[j + 1] += p1;
-                pk[j / 2] = pack_bf16x2(p0, p1);
+                for (int i = 0; i < HR / 2; ++i) {
+                    const int h = 2 * i + (gtid >> 6), piece = gtid & 63;
+                    uint4 v;
+                    asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(stage + h * 1024 + piece * 16));
+                    if (col0 + r * HR + h < hvalid)
+                        *reinterpret_cast<uint4 *>(orow + static_cast<long long>(r * HR + h) * a.o_hs + piece * 8) = v;
+                }
+                named_bar_sync(group_bar, 128);     // the stage may be rewritten
             }
-            if constexpr (CW == 16) {
-                st_shared_v4(p_addr, pk[0], pk[1], pk[2], pk[3]);
-                st_shared_v4(p_addr + 2048, pk[4], pk[5], pk[6], pk[7]);
-            } else if constexpr (CW == 8) {
-                st_shared_v4(p_addr, pk[0], pk[1], pk[2], pk[3]);
-            } else {
-                asm volatile("st.shared.v2.b32 [%0], {%1,%2};" ::"r"(p_addr), "r"(pk[0]), "r"(pk[1]) : "memory");
+        } else {
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t o[CW];
+                TmemIO<CW>::ld(tmem_lane + kTmemOCol + c * NPAD + col0, o);
+                float *dst = a.part_o + (static_cast<long long>(slot) * NPAD + col0) * kD + c * 128 + row;
+#pragma unroll
+                for (int j = 0; j < CW; ++j)
+                    if (col0 + j < hvalid) dst[static_cast<long long>(j) * kD] = __uint_as_float(o[j]);
             }
         }
-        if (tracer) SMLA_MARK(it, 4);
-        fence_async_smem();
+        // Groups 0 and 1 staged in the P buffer, which other groups write in the coming softmax.
+        named_bar_sync(kAllWorkersBar, kWorkerThreads);
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bars + kBarP * 8);
+        if (lane == 0) mbar_arrive(bars + kBarOFree * 8);     // the next segment's first PV may overwrite O^T
+        if (tracer) SMLA_MARK(gt < 32 ? gt : 31, 14);
+    };
+
+    uint4 raw[J];
+    RowRef<FMT> cur;
+    int g;
+    {   // raw bytes of the very first tile
+        const int *r0 = sched + kSchedRec;
+        g = r0[4] * kTileRows + my_row;
+        cur = make_row_ref<FMT>(a, r0[3], r0[2], g, load_slot_id(a, r0[0], r0[3], r0[2], g));
+#pragma unroll
+        for (int j = 0; j < J; ++j) load_step<FMT>(cur, j, quarter, raw[j]);
     }
 
-    // ---- epilogue: O^T / l
-    warp_wait(bars + kBarO * 8, 0, abort_flag, lane, kStatusEpilogueWait);
-    tc_fence_after_sync();
-    {
-        float r[1];
-        ColReduce<CW, 16, false>::run(lsum, lane, r);
-        store_col_partial<CW>(red + q * NPAD + col0, r[0], lane);
-    }
-    named_bar_sync(kAllWorkersBar, kWorkerThreads);
-    if (tid < NPAD) {
-        float l = (red[tid] + red[NPAD + tid]) + (red[2 * NPAD + tid] + red[3 * NPAD + tid]);
-        if (direct) {
-            if (a.sink != nullptr && tid < hvalid) l += fast_exp2(a.sink[h0 + tid] * kLog2e - m_s[tid]);
-            alpha_s[tid] = 1.0f / l;
-        } else if (tid < hvalid) {
-            float *ml = a.part_ml + ((static_cast<long long>(t) * a.H + h0 + tid) * a.num_splits + sp) * 2;
-            ml[0] = m_s[tid];
-            ml[1] = l;
+    for (int k = 0;; ++k) {      // segments
+        // Fields of this segment (sg) and the next (ng) are read from shared memory where they are
+        // used rather than held in registers across the tile loop.
+        const volatile int *sg = sched + kSchedRec + 12 * (k % 5);
+        const volatile int *ng = sched + kSchedRec + 12 * ((k + 1) % 5);
+        const bool have_next = (ng[7] & kSegValid) != 0;
+        if (tid == 0 && (sg[7] & kSegOwnsFirst)) {   // this CTA holds the first tiles of an item that continues elsewhere
+            int4 d;
+            d.x = sg[0] * a.head_blocks + sg[1];
+            d.y = sg[8] - static_cast<int>(blockIdx.x) + 1;     // CTAs (= partial segments) the item spans
+            d.z = sg[6];
+            d.w = min(NPAD, a.H - sg[1] * 64);
+            reinterpret_cast<int4 *>(a.desc)[blockIdx.x] = d;
         }
-    }
-    named_bar_sync(kAllWorkersBar, kWorkerThreads);
+
+        int rows_left = sg[2] - sg[4] * kTileRows;      // rows of the item from this tile on
+        for (int left = sg[5]; left > 0; --left, ++gt, rows_left -= kTileRows) {
+            const bool first_tile = left == sg[5];
+            // ---- which tile comes next (possibly the next segment's first), and its slot id
+            const bool in_seg = left > 1;
+            const bool more = in_seg || have_next;
+            const int n_t = in_seg ? sg[0] : ng[0], n_ns = in_seg ? sg[3] : ng[3], n_n = in_seg ? sg[2] : ng[2];
+            const int g_next = in_seg ? g + kTileRows : ng[4] * kTileRows + my_row;
+            const int id_next = more ? load_slot_id(a, n_t, n_ns, n_n, g_next) : -1;
+
+            // ---- convert: raw registers -> K chunks, each as soon as the previous tile's PV released it
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                if (gt > 0) warp_wait(bars + (kBarFree + c) * 8, (gt - 1) & 1, abort_flag, lane, kStatusGatherWait);
+                if (tracer && c == 0) SMLA_MARK(gt, 7);
+#pragma unroll
+                for (int j = 0; j < J; ++j) {
+                    const bool mine = (j < 8) ? ((j >> 1) == c) : (c == 3);
+                    if (mine) convert_step<FMT>(raw[j], j, quarter, cur.sc0, cur.sc1, k_row_addr);
+                }
+                if (tracer && (c == 0 || c == 3)) SMLA_MARK(gt, 8 + c);
+                if (c == 0 && first_tile) cp_async_wait_all();   // this item's Q tile (fetched by cp.async) has landed
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bars + (kBarReady + c) * 8);
+            }
+            if (tracer) SMLA_MARK(gt, 12);
+            // Raw bytes of the next tile.  Issued only now, after this tile's last conversion fence: a
+            // proxy fence also waits for the thread's global loads in flight, so loads issued between
+            // the chunks would put a memory latency on every hand-over.  They land while QK^T runs.
+            // (Measured: sending half of them after the softmax instead made the tile 25 % slower: the
+            // issue of a load blocks the warp while the SM's load queue is full.)
+            cur = make_row_ref<FMT>(a, n_ns, n_n, more ? g_next : n_n, id_next);
+            if (more) {
+#pragma unroll
+                for (int j = 0; j < J; ++j) load_step<FMT>(cur, j, quarter, raw[j]);
+            }
+            g = g_next;
+
+            // ---- the previous segment's epilogue, while the tensor pipe computes this tile's QK^T
+            if (first_tile && k > 0) epilogue(sched + kSchedRec + 12 * ((k - 1) % 5), sg, (k - 1) & 1);
+
+            // ---- softmax of this tile
+            warp_wait(bars + kBarS * 8, gt & 1, abort_flag, lane, kStatusSoftmaxWait);
+            tc_fence_after_sync();
+            if (tracer) SMLA_MARK(gt, 2);
+            // sm = S^T * scale - m, with m read once per tile (the same for all rows).
+            const bool row_valid = row < rows_left;
+            float sm[CW];
+            {
+                uint32_t sraw[CW];
+                TmemIO<CW>::ld(tmem_lane + col0, sraw);
+#pragma unroll
+                for (int j = 0; j < CW; ++j)
+                    sm[j] = row_valid ? fmaf(__uint_as_float(sraw[j]), a.scale_log2, -m_s[col0 + j]) : -INFINITY;
+            }
+            // The reference max m is only moved when some score exceeds it by more than the threshold
+            // (always on a segment's first tile).  The vote spans the four warps that share these columns.
+            bool need = first_tile;
+#pragma unroll
+            for (int j = 0; j < CW; ++j) need |= sm[j] > kRescaleThreshold;
+            if (named_bar_or(group_bar, 128, need)) {
+                // Scores relative to the OLD reference are kept (not re-read from tensor memory, not held
+                // as raw values): s - m_new = (s - m_old) + (m_old - m_new), and both references are
+                // integers, so the sum is exact whenever s - m_old is finite.
+                float (&s)[CW] = sm;
+                float r[1];
+                ColReduce<CW, 16, true>::run(s, lane, r);
+                store_col_partial<CW>(red + q * NPAD + col0, r[0], lane);
+                named_bar_sync(group_bar, 128);
+                if (q == 0 && lane < CW) {
+                    const int col = col0 + lane;
+                    const float tmr = fmaxf(fmaxf(red[col], red[NPAD + col]), fmaxf(red[2 * NPAD + col], red[3 * NPAD + col]));
+                    const float m_old = m_s[col];
+                    const float tm = tmr + m_old;     // column maximum, back in absolute log2 units
+                    // m stays INTEGER-valued (log2 units): 2^(s - m) then has the same mantissa whatever m
+                    // is, so P rounds to bf16 (almost) identically however the rows are cut into segments.
+                    // The first tile sets it outright (only the sink, if it counts here, holds it up);
+                    // nothing has been accumulated yet, so there is nothing to rescale.
+                    const bool sink_here = (sg[7] & kSegComplete) != 0 && a.sink != nullptr;
+                    const bool up = first_tile ? (!sink_here || ceilf(tm) > m_old) : tm > m_old + kRescaleThreshold;
+                    const float m_new = up ? ceilf(tm) : m_old;
+                    alpha_s[col] = (up && !first_tile) ? fast_exp2(m_old - m_new) : 1.0f;
+                    shift_s[col] = m_old - m_new;
+                    m_s[col] = m_new;
+                }
+                named_bar_sync(group_bar, 128);
+                lacc *= alpha_s[col0 + (lane >> kColShift)];
+#pragma unroll
+                for (int j = 0; j < CW; ++j) sm[j] += shift_s[col0 + j];
+                if (!first_tile) {   // O^T[:, h] *= alpha[h]; the previous PV completed before this tile's S^T did
 #pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
-        uint32_t o[CW];
-        TmemIO<CW>::ld(tmem_lane + kTmemOCol + c * NPAD + col0, o);
-        const int d = c * 128 + row;
-        if (direct) {
-            __nv_bfloat16 *dst = a.out + static_cast<long long>(t) * a.o_ts + static_cast<long long>(h0 + col0) * a.o_hs + d;
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t o[CW];
+                        TmemIO<CW>::ld(tmem_lane + kTmemOCol + c * NPAD + col0, o);
 #pragma unroll
-            for (int j = 0; j < CW; ++j)
-                if (col0 + j < hvalid) dst[j * a.o_hs] = __float2bfloat16_rn(__uint_as_float(o[j]) * alpha_s[col0 + j]);
-        } else {
-            float *dst = a.part_o + ((static_cast<long long>(t) * a.H + h0 + col0) * a.num_splits + sp) * kD + d;
+                        for (int j = 0; j < CW; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha_s[col0 + j]);
+                        TmemIO<CW>::st(tmem_lane + kTmemOCol + c * NPAD + col0, o);
+                    }
+                    tmem_st_wait();
+                }
+            }
+            if (tracer) SMLA_MARK(gt, 3);
+            {   // P^T = 2^(S^T - m) rounded to bf16, MN-major B-operand layout (8 heads = 16 bytes per row)
+                uint32_t pk[CW / 2];
 #pragma unroll
-            for (int j = 0; j < CW; ++j)
-                if (col0 + j < hvalid) dst[static_cast<long long>(j) * a.num_splits * kD] = __uint_as_float(o[j]);
+                for (int j = 0; j < CW; j += 2) {
+                    sm[j] = fast_exp2(sm[j]);
+                    sm[j + 1] = fast_exp2(sm[j + 1]);
+                    pk[j / 2] = pack_bf16x2(sm[j], sm[j + 1]);
+                }
+                if constexpr (CW == 16) {
+                    st_shared_v4(p_addr, pk[0], pk[1], pk[2], pk[3]);
+                    st_shared_v4(p_addr + 2048, pk[4], pk[5], pk[6], pk[7]);
+                } else if constexpr (CW == 8) {
+                    st_shared_v4(p_addr, pk[0], pk[1], pk[2], pk[3]);
+                } else {
+                    asm volatile("st.shared.v2.b32 [%0], {%1,%2};" ::"r"(p_addr), "r"(pk[0]), "r"(pk[1]) : "memory");
+                }
+            }
+            if (tracer) SMLA_MARK(gt, 4);
+            fence_async_smem();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bars + kBarP * 8);
+            {   // denominators, after the hand-over: the tensor pipe is already at work on PV
+                float r[1];
+                ColReduce<CW, 16, false>::run(sm, lane, r);
+                lacc += r[0];
+            }
+            // Warp 0 prepares segment k + 3 once per segment, here where no other warp waits for it.  The
+            // others read that record from segment k + 2 on, after the all-worker barriers of the
+            // epilogue in between; the record it replaces (segment k - 2) is long unused.
+            if (warp == 0 && first_tile) {
+                publish_segment(a, sched, k + 3, lane);
+                if (tracer) SMLA_MARK(gt, 15);
+            }
         }
+
+        // ---- end of the segment.  Every QK^T of it has completed (this warp saw the last S^T), so the
+        // Q buffer is free: fetch the next item's Q tile while the last PV runs.  The segment's epilogue
+        // is run inside the next segment's first tile.
+        if (!have_next) {
+            epilogue(sg, nullptr, k & 1);
+            break;
+        }
+        const int n_h0 = ng[1] * 64;
+        if (tracer) SMLA_MARK(gt < 32 ? gt : 31, 9);
+        issue_q_tile<NPAD>(a, smem, ng[0], n_h0, min(NPAD, a.H - n_h0), warp, lane, kWorkerWarps);
+        if (tracer) SMLA_MARK(gt < 32 ? gt : 31, 10);
     }
-    tc_fence_before_sync();
 }
 
 // ------------------------------------------------------------------ the kernel
@@ -592,34 +1010,31 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const __gri
     extern __shared__ __align__(128) uint8_t smem[];
     using L = Smem<NPAD>;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int t = blockIdx.x / a.head_blocks, hb = blockIdx.x - t * a.head_blocks, sp = blockIdx.y;
-    const int h0 = hb * 64;
-    const int hvalid = min(NPAD, a.H - h0);
 
-    const int ns = min(max(__ldg(a.swa.lens + t), 0), a.swa.topk);
-    const int ne = (a.extra.cache != nullptr) ? min(max(__ldg(a.extra.lens + t), 0), a.extra.topk) : 0;
-    const int n = ns + ne;
-    const int ntiles = (n + kTileRows - 1) / kTileRows;
-    const int tps = (ntiles + a.num_splits - 1) / a.num_splits;
-    const int tile0 = sp * tps;
-    const int ntl = min(ntiles, tile0 + tps) - tile0;
-
-    if (ntl <= 0) {   // nothing selected for this (token, split): zeros / an empty partial
-        if (a.num_splits == 1) {
-            for (int i = tid; i < hvalid * (kD / 8); i += kThreads) {
-                const int h = i / (kD / 8), d8 = i - h * (kD / 8);
-                *reinterpret_cast<uint4 *>(a.out + static_cast<long long>(t) * a.o_ts +
-                                           static_cast<long long>(h0 + h) * a.o_hs + d8 * 8) = make_uint4(0, 0, 0, 0);
-            }
-        } else if (tid < hvalid) {
-            float *ml = a.part_ml + ((static_cast<long long>(t) * a.H + h0 + tid) * a.num_splits + sp) * 2;
-            ml[0] = -INFINITY;
-            ml[1] = 0.0f;
+    SMLA_CTA_MARK(0);
+    // ---- this CTA's share of the work
+    int *sched = reinterpret_cast<int *>(smem + L::kSched);
+    if (a.balanced && tid == 0) reinterpret_cast<int4 *>(a.desc)[blockIdx.x] = make_int4(-1, 0, 0, 0);
+    {
+        SegIter iter;
+        long long W;
+        int P;
+        if (!make_schedule(a, sched + kSchedScan, iter, W, P)) return;
+        if (tid == 0) {
+            store_iter(sched + kSchedIter, iter, W);
+            sched[kSchedP] = P;
         }
-        return;
     }
+    __syncthreads();
+    if (warp == 0) {
+        publish_segment(a, sched, 0, lane);
+        publish_segment(a, sched, 1, lane);
+        publish_segment(a, sched, 2, lane);
+    }
+    __syncthreads();
+    if ((sched[kSchedRec + 7] & kSegValid) == 0) return;   // nothing but items without rows
 
-    // ---- set-up: barriers, TMEM, reference max, Q tile
+    // ---- set-up: barriers, TMEM, reference max and Q tile of the first segment
     if (tid == 0) {
         const uint32_t bars = smem_u32(smem + L::kBars);
         for (int c = 0; c < 4; ++c) mbar_init(bars + (kBarReady + c) * 8, kWorkerWarps);
@@ -627,6 +1042,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const __gri
         mbar_init(bars + kBarS * 8, 1);
         mbar_init(bars + kBarP * 8, kWorkerWarps);
         mbar_init(bars + kBarO * 8, 1);
+        mbar_init(bars + kBarOFree * 8, kWorkerWarps);
         *reinterpret_cast<volatile int *>(smem + L::kAbort) = 0;
         mbar_init_fence();
     }
@@ -634,68 +1050,73 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const __gri
         tmem_alloc(smem_u32(smem + L::kTmemPtr), kTmemCols);
         tmem_relinquish();
     }
-    if (tid < NPAD) {
-        float m0 = -INFINITY;
-        if (a.num_splits == 1 && a.sink != nullptr && tid < hvalid) m0 = ceilf(a.sink[h0 + tid] * kLog2e);
-        reinterpret_cast<float *>(smem + L::kM)[tid] = m0;
-    }
     {
-        const __nv_bfloat16 *qt = a.q + static_cast<long long>(t) * a.q_ts + static_cast<long long>(h0) * a.q_hs;
-        const uint32_t q_addr = smem_u32(smem + L::kQ);
-        for (int idx = warp; idx < (NPAD / 8) * 16; idx += kNumWarps) {
-            const int hg = idx >> 4, dg = (idx & 15) * 4 + (lane >> 3), h = hg * 8 + (lane & 7);
-            uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (h < hvalid) v = __ldg(reinterpret_cast<const uint4 *>(qt + static_cast<long long>(h) * a.q_hs + dg * 8));
-            st_shared_v4(q_addr + hg * kRowGroupBytes + dg * kCoreBytes + (lane & 7) * 16, v.x, v.y, v.z, v.w);
-        }
+        const int *r0 = sched + kSchedRec;
+        const int h0 = r0[1] * 64, hvalid = min(NPAD, a.H - h0);
+        if (tid < NPAD)
+            reinterpret_cast<float *>(smem + L::kM)[tid] = initial_ref(a, (r0[7] & kSegComplete) != 0, h0, tid, hvalid);
+        // Q tile of the first segment: fetched by the worker warps, which wait for it only before
+        // their first hand-over, so the copy overlaps the gather of the first K tile.
+        if (warp < kWorkerWarps) issue_q_tile<NPAD>(a, smem, r0[0], h0, hvalid, warp, lane, kWorkerWarps);
     }
     fence_async_smem();
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(smem + L::kTmemPtr);
+    SMLA_CTA_MARK(1);
 
     if (warp < kWorkerWarps) {
-        worker_role<FMT, NPAD>(a, smem, tmem_base, t, h0, hvalid, sp, ns, n, tile0, ntl, warp, lane);
+        worker_role<FMT, NPAD>(a, smem, tmem_base, warp, lane);
     } else {
-        if (warp == kMmaWarp && lane == 0) mma_role<NPAD>(smem, tmem_base, ntl);
+        if (warp == kMmaWarp && lane == 0) mma_role<NPAD>(smem, tmem_base);
         __syncwarp();
     }
 
     __syncthreads();
+    SMLA_CTA_MARK(2);
     if (warp == kMmaWarp) {
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, kTmemCols);
     }
 }
 
-// ------------------------------------------------------------------ split-KV combine
-// One warp per (token, head): out = sum_s 2^(m_s - M) O_s / (sum_s 2^(m_s - M) l_s + 2^(sink - M)).
-// Lane s first turns {m_s, l_s} into a weight (S <= 64: two per lane); the partial rows are then
-// streamed four splits at a time so that 16 independent 16-byte loads are in flight per lane.
+// ------------------------------------------------------------------ merge of partial segments
+// Block (c, y): if CTA c of the attention kernel left a descriptor {item, S, first slot, heads}, the
+// item's S partial segments sit in slots {first slot, 2(c+1), 2(c+2), ...}.  One warp per head:
+//   out = sum_s 2^(m_s - M) O_s / (sum_s 2^(m_s - M) l_s + 2^(sink - M)),  M = max(m_s, sink).
 __global__ void __launch_bounds__(128) sparse_mla_combine_kernel(const float *__restrict__ part_o,
                                                                  const float *__restrict__ part_ml,
+                                                                 const int4 *__restrict__ desc,
                                                                  const float *__restrict__ sink,
                                                                  __nv_bfloat16 *__restrict__ out, long long o_ts,
-                                                                 long long o_hs, int T, int H, int S) {
+                                                                 long long o_hs, int head_blocks, int npad) {
     const int lane = threadIdx.x & 31;
-    const long long th = static_cast<long long>(blockIdx.x) * 4 + (threadIdx.x >> 5);
-    if (th >= static_cast<long long>(T) * H) return;
-    const int t = static_cast<int>(th / H), h = static_cast<int>(th - static_cast<long long>(t) * H);
-    const float2 *ml = reinterpret_cast<const float2 *>(part_ml + th * S * 2);
+    const int c = blockIdx.x;
+    const int4 d = desc[c];
+    const int hl = blockIdx.y * 4 + (threadIdx.x >> 5);
+    if (d.x < 0 || hl >= d.w) return;
+    const int t = d.x / head_blocks, h = (d.x - t * head_blocks) * 64 + hl;
+    const int S = d.y;
+    auto slot_of = [&](int k) { return k == 0 ? d.z : 2 * (c + k); };
+    auto ml_of = [&](int k) {
+        return __ldg(reinterpret_cast<const float2 *>(part_ml) + static_cast<long long>(slot_of(k)) * npad + hl);
+    };
     const float sink_l2 = sink ? sink[h] * kLog2e : -INFINITY;
-    float2 e0 = make_float2(-INFINITY, 0.0f), e1 = make_float2(-INFINITY, 0.0f);
-    if (lane < S) e0 = ml[lane];
-    if (lane + 32 < S) e1 = ml[lane + 32];
     float M = sink_l2;
-    if (e0.y > 0.0f) M = fmaxf(M, e0.x);
-    if (e1.y > 0.0f) M = fmaxf(M, e1.x);
+    for (int k = lane; k < S; k += 32) {
+        const float2 e = ml_of(k);
+        if (e.y > 0.0f) M = fmaxf(M, e.x);
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
-    // empty splits (l == 0) get weight 0 and their (unwritten) partial rows are never multiplied in
-    const float w0 = (e0.y > 0.0f && M > -INFINITY) ? fast_exp2(e0.x - M) : 0.0f;
-    const float w1 = (e1.y > 0.0f && M > -INFINITY) ? fast_exp2(e1.x - M) : 0.0f;
-    float denom = w0 * e0.y + w1 * e1.y;
+    float denom = 0.0f;
+    if (M > -INFINITY) {
+        for (int k = lane; k < S; k += 32) {
+            const float2 e = ml_of(k);
+            if (e.y > 0.0f) denom += fast_exp2(e.x - M) * e.y;
+        }
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) denom += __shfl_xor_sync(0xffffffffu, denom, o);
     if (M > -INFINITY) denom += fast_exp2(sink_l2 - M);
@@ -703,16 +1124,17 @@ __global__ void __launch_bounds__(128) sparse_mla_combine_kernel(const float *__
     float acc[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) acc[i] = 0.0f;
-    const float4 *base = reinterpret_cast<const float4 *>(part_o + th * S * kD);
-    for (int s0 = 0; s0 < S; s0 += 4) {
+    for (int k0 = 0; k0 < S; k0 += 4) {      // four segments at a time: 16 independent 16-byte loads per lane
         float4 x[4][4];
         float w[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-            const int s = s0 + u;
-            const float ws = __shfl_sync(0xffffffffu, (s < 32) ? w0 : w1, s & 31);
-            w[u] = (s < S) ? ws : 0.0f;
-            const float4 *src = base + static_cast<long long>(min(s, S - 1)) * (kD / 4);
+            const int k = min(k0 + u, S - 1);
+            const float2 e = ml_of(k);      // the same address in every lane: one broadcast load
+            // empty segments (l == 0) get weight 0; their rows are loaded but never multiplied in
+            w[u] = (k0 + u < S && e.y > 0.0f && M > -INFINITY) ? fast_exp2(e.x - M) : 0.0f;
+            const float4 *src = reinterpret_cast<const float4 *>(part_o) +
+                                (static_cast<long long>(slot_of(k)) * npad + hl) * (kD / 4);
 #pragma unroll
             for (int v = 0; v < 4; ++v) x[u][v] = __ldg(src + v * 32 + lane);
         }
@@ -769,7 +1191,7 @@ int fill_stream(const smla_stream_t &s, int fmt, StreamDev &d) {
 }
 
 template <int FMT, int NPAD>
-int launch_fwd(const KernelArgs &a, dim3 grid, cudaStream_t stream) {
+int launch_fwd(const KernelArgs &a, unsigned grid, cudaStream_t stream) {
     constexpr int smem_bytes = Smem<NPAD>::kTotal;
     static bool attr_done[64] = {};
     int dev = 0;
@@ -786,7 +1208,7 @@ int launch_fwd(const KernelArgs &a, dim3 grid, cudaStream_t stream) {
 }
 
 template <int FMT>
-int launch_fwd_npad(int npad, const KernelArgs &a, dim3 grid, cudaStream_t stream) {
+int launch_fwd_npad(int npad, const KernelArgs &a, unsigned grid, cudaStream_t stream) {
     switch (npad) {
         case 16: return launch_fwd<FMT, 16>(a, grid, stream);
         case 32: return launch_fwd<FMT, 32>(a, grid, stream);
@@ -794,8 +1216,26 @@ int launch_fwd_npad(int npad, const KernelArgs &a, dim3 grid, cudaStream_t strea
     }
 }
 
+int sm_count_of_current_device(int &count) {
+    static int cached[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (dev >= 0 && dev < 64 && cached[dev] > 0) {
+        count = cached[dev];
+        return 0;
+    }
+    e = cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (dev >= 0 && dev < 64) cached[dev] = count;
+    return 0;
+}
+
 }  // namespace
 
+// `num_splits` > 1 with a workspace of smla_attn_workspace_bytes(T, H, num_splits) bytes selects the
+// balanced-tiles schedule with as many CTAs as the SM count and the workspace (two partial slots per
+// CTA plus one 16-byte descriptor) allow; otherwise whole items are dealt out to the CTAs.
 int launch_sparse_mla_attention(const smla_attn_params_t &p, int num_splits, void *workspace, cudaStream_t stream) {
     if (p.num_tokens < 0 || p.num_heads <= 0 || !p.q || !p.out) return SMLA_EINVAL;
     if (p.num_tokens == 0) return SMLA_OK;
@@ -823,22 +1263,37 @@ int launch_sparse_mla_attention(const smla_attn_params_t &p, int num_splits, voi
     }
     const int npad = p.num_heads <= 16 ? 16 : (p.num_heads <= 32 ? 32 : 64);
     a.head_blocks = (p.num_heads + 63) / 64;
-    a.num_splits = num_splits < 1 ? 1 : num_splits;
-    if (a.num_splits > 1) {
+    const long long items = static_cast<long long>(p.num_tokens) * a.head_blocks;
+    if (items > 0x7FFFFFFFLL) return SMLA_ETOOBIG;
+    int sms = 0;
+    rc = sm_count_of_current_device(sms);
+    if (rc != 0) return rc;
+
+    long long ctas = 0;
+    if (num_splits > 1) {
         if (!workspace) return SMLA_EWORKSPACE;
-        a.part_o = static_cast<float *>(workspace);
-        a.part_ml = a.part_o + static_cast<size_t>(p.num_tokens) * p.num_heads * a.num_splits * kD;
+        if (reinterpret_cast<uintptr_t>(workspace) & 15u) return SMLA_EALIGN;
+        const long long bytes = static_cast<long long>(smla_attn_workspace_bytes(p.num_tokens, p.num_heads, num_splits));
+        const long long slot_bytes = static_cast<long long>(npad) * (kD + 2) * sizeof(float);
+        ctas = std::min<long long>(sms, (bytes - 16ll * sms) / slot_bytes / 2);
     }
-    const long long gx = static_cast<long long>(p.num_tokens) * a.head_blocks;
-    if (gx > 0x7FFFFFFFLL || a.num_splits > 64) return SMLA_ETOOBIG;   // the combine kernel keeps two weights per lane
-    const dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(a.num_splits));
+    if (ctas >= 2) {
+        a.balanced = 1;
+        a.part_o = static_cast<float *>(workspace);
+        a.part_ml = a.part_o + static_cast<size_t>(2 * ctas) * npad * kD;
+        a.desc = reinterpret_cast<int *>(a.part_ml + static_cast<size_t>(2 * ctas) * npad * 2);
+    } else {
+        a.balanced = 0;
+        ctas = std::min<long long>(items, sms);
+    }
+    const unsigned grid = static_cast<unsigned>(ctas);
     rc = (p.cache_format == SMLA_FP8_DS_MLA) ? launch_fwd_npad<SMLA_FP8_DS_MLA>(npad, a, grid, stream)
                                              : launch_fwd_npad<SMLA_INT8_DS_MLA>(npad, a, grid, stream);
     if (rc != 0) return rc;
-    if (a.num_splits > 1) {
-        const long long th = static_cast<long long>(p.num_tokens) * p.num_heads;
-        sparse_mla_combine_kernel<<<static_cast<unsigned>((th + 3) / 4), 128, 0, stream>>>(
-            a.part_o, a.part_ml, a.sink, a.out, a.o_ts, a.o_hs, a.T, a.H, a.num_splits);
+    if (a.balanced) {
+        sparse_mla_combine_kernel<<<dim3(grid, static_cast<unsigned>((npad + 3) / 4)), 128, 0, stream>>>(
+            a.part_o, a.part_ml, reinterpret_cast<const int4 *>(a.desc), a.sink, a.out, a.o_ts, a.o_hs, a.head_blocks,
+            npad);
         rc = static_cast<int>(cudaGetLastError());
     }
     return rc;
@@ -848,6 +1303,10 @@ int launch_sparse_mla_attention(const smla_attn_params_t &p, int num_splits, voi
 extern "C" __attribute__((visibility("default"))) int smla_debug_read_trace(unsigned long long *host_out) {
     cudaDeviceSynchronize();
     return static_cast<int>(cudaMemcpyFromSymbol(host_out, g_trace, sizeof(unsigned long long) * 32 * 16));
+}
+extern "C" __attribute__((visibility("default"))) int smla_debug_read_cta_times(unsigned long long *host_out) {
+    cudaDeviceSynchronize();
+    return static_cast<int>(cudaMemcpyFromSymbol(host_out, g_cta_times, sizeof(unsigned long long) * 256 * 4));
 }
 #endif
 

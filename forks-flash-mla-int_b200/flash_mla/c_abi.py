@@ -13,7 +13,7 @@ from ._loader import CORE_LIB
 
 SMLA_FP8_DS_MLA = 0
 SMLA_INT8_DS_MLA = 1
-SMLA_STATIC_SCRATCH_BYTES = 32 << 20
+SMLA_STATIC_SCRATCH_BYTES = 64 << 20
 SMLA_ETOOBIG = -5
 
 EXPORTS = (

@@ -75,8 +75,9 @@ typedef struct smla_attn_params {
     const float *attn_sink;     /* fp32 [H] natural-log logits, or NULL                        */
     smla_stream_t swa;
     smla_stream_t extra;        /* extra.cache == NULL when absent                            */
-    int32_t num_splits;         /* split-KV count; 0 = let the library choose                  */
-    void *workspace;            /* >= smla_attn_workspace_bytes(...) when splits > 1, else NULL */
+    int32_t num_splits;         /* scratch partials per (token, head); 0 = let the library choose */
+    void *workspace;            /* 16-byte aligned, >= smla_attn_workspace_bytes(...) when
+                                   num_splits > 1, else NULL                                  */
     size_t workspace_bytes;
 } smla_attn_params_t;
 
@@ -86,14 +87,21 @@ SMLA_API const char *smla_version(void);
 /* Human-readable text for a return code of this library (negative) or of CUDA (positive). */
 SMLA_API const char *smla_error_string(int code);
 
-/* Split-KV policy: how many splits smla_sparse_mla_decode would use for this problem on a
- * device with `sm_count` SMs.  Counterpart of sparse_mla_num_splits (csrc/flash_api.cpp:75-102);
- * the environment variable FLASH_MLA_SLOTS_PER_SPLIT is honoured the same way (read per call). */
+/* Split-KV policy.  The attention kernel is persistent (at most one CTA per SM).  A result of 1 means
+ * whole (token, 64-head block) items are dealt out to the CTAs and nothing is merged.  A result
+ * S > 1 means the 128-row tiles of all items are cut into equal contiguous ranges, one per CTA (so
+ * ragged lens and fewer items than SMs still fill the GPU); a CTA then leaves up to two partial
+ * segments in scratch and a second kernel merges them.  S is the scratch the schedule needs, in
+ * partials per (token, head): two slots of 64 heads per CTA plus the merge descriptors.  Counterpart
+ * of sparse_mla_num_splits (csrc/flash_api.cpp:75-102); the environment variable
+ * FLASH_MLA_SLOTS_PER_SPLIT is honoured as the least number of rows a CTA is given (read per call). */
 SMLA_API int smla_choose_num_splits(int sm_count, int num_tokens, int num_heads, int max_width);
 
 /* Bytes of split-KV scratch (fp32 partial outputs + {max, denominator} pairs) for `num_splits`
- * splits; 0 when num_splits <= 1.  Counterpart of the oaccum/mlse tensors allocated at
- * csrc/flash_api.cpp:388-400. */
+ * partials per (token, head): num_tokens * num_heads * num_splits * (512 + 2) * 4; 0 when
+ * num_splits <= 1.  Counterpart of the oaccum/mlse tensors allocated at csrc/flash_api.cpp:388-400.
+ * An explicit num_splits smaller than the policy's only lowers the number of CTAs that share the
+ * tiles (two slots each); below two CTAs the unsplit schedule is used. */
 SMLA_API size_t smla_attn_workspace_bytes(int num_tokens, int num_heads, int num_splits);
 
 /* Split count smla_sparse_mla_decode would pick on the CURRENT device (queries its SM count) and
@@ -113,13 +121,14 @@ SMLA_API int smla_sparse_mla_decode(const smla_attn_params_t *params, void *stre
  * device memory when a decode step runs: every byte of HBM already belongs to the engine's KV-cache
  * pool, cudaMalloc would synchronise the device inside the latency-critical loop, and it is not
  * allowed during stream capture.  This function calls no allocator of any kind.
- *   - Requests whose scratch (smla_attn_workspace_bytes for the chosen split count) exceeds
- *     SMLA_STATIC_SCRATCH_BYTES are rejected with SMLA_ETOOBIG; nothing is launched.
+ *   - An explicit num_splits whose scratch (smla_attn_workspace_bytes) exceeds
+ *     SMLA_STATIC_SCRATCH_BYTES is rejected with SMLA_ETOOBIG and nothing is launched; the automatic
+ *     choice (num_splits == 0) is lowered until it fits.
  *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress, that
  *     device current); make that first call before any stream capture.
  *   - All calls on a device share the array, which keeps the previous call's contents (nothing in it
  *     needs clearing); calls whose kernels overlap on the GPU race on it. */
-#define SMLA_STATIC_SCRATCH_BYTES (32u << 20)
+#define SMLA_STATIC_SCRATCH_BYTES (64u << 20)
 SMLA_API int smla_sparse_mla_decode_static_scratch(const smla_attn_params_t *params, void *stream);
 
 /* Sparse MLA prefill (many query tokens, never split).  Replaces run_sparse_mla_prefill

@@ -83,16 +83,20 @@ def test_split_policy_and_workspace():
     lib = c_abi.load()
     os.environ.pop("FLASH_MLA_SLOTS_PER_SPLIT", None)
     f = lib.smla_choose_num_splits
-    assert f(148, 128, 64, 2560) == 1            # enough (token, head-block) CTAs to fill the SMs
-    assert f(148, 1, 64, 2560) == 20             # one 128-row tile per split
-    assert f(148, 1, 64, 512) == 4
-    assert f(148, 8, 64, 2560) == 18
-    assert f(148, 8, 128, 2560) == 9             # two head blocks per token
-    assert f(148, 1, 64, 100) == 1
-    assert f(148, 1, 64, 64 * 128 * 4) == 64     # capped
+    # >= 4 items (token x block of 64 heads) per SM: whole items per CTA, nothing to merge
+    assert f(148, 1024, 64, 2560) == 1
+    assert f(148, 296, 128, 2560) == 1
+    # otherwise: scratch for (2 * CTAs + 1) slots of 64 heads, expressed per (token, head)
+    assert f(148, 128, 64, 2560) == 3            # 148 CTAs: ceil(297 * 64 / (128 * 64))
+    assert f(148, 1, 64, 2560) == 41             # 20 tiles -> 20 CTAs -> 41 slots for one token
+    assert f(148, 1, 64, 512) == 9
+    assert f(148, 8, 64, 2560) == 38
+    assert f(148, 8, 128, 2560) == 19            # two head blocks per token
+    assert f(148, 1, 64, 100) == 1               # a single tile: one CTA
+    assert f(148, 1, 16, 2560) == 41             # slots shrink with the head block (16 heads)
     os.environ["FLASH_MLA_SLOTS_PER_SPLIT"] = "512"
     try:
-        assert f(148, 1, 64, 2560) == 5          # read on every call, like the reference
+        assert f(148, 1, 64, 2560) == 11         # at least 512 rows per CTA -> 5 CTAs; read on every call
     finally:
         os.environ.pop("FLASH_MLA_SLOTS_PER_SPLIT")
     w = lib.smla_attn_workspace_bytes
