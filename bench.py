@@ -222,6 +222,10 @@ def run_reference(args_ns):
     print(json.dumps(line))
 
 
+# attention-kernel DRAM traffic per launch measured with ncu (profiles/sparse_mla_fwd_kernel_fp8_decode_T128_H64.md)
+NCU_DRAM_TRAFFIC_BYTES = {"dsv4_fp8_decode_T128_H64": 42.9e6}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -339,7 +343,9 @@ def main():
         else:
             roof = {"bound": "tensor", "achieved": meta["flops"] / dur_s / 1e12, "peak": bf16_tf, "unit": "TFLOP/s"}
         roof["frac"] = roof["achieved"] / roof["peak"]
-        roof["traffic"] = None
+        # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the attention kernel, from the ncu
+        # capture summarised under profiles/ (only captured for the default workload)
+        roof["traffic"] = NCU_DRAM_TRAFFIC_BYTES.get(a.workload)
         roof["peak_kind"] = peak_kind
         roof["kernel"] = "sparse_mla_fwd_kernel"
         roof["algorithmic_bytes_per_launch"] = meta["bytes"]
