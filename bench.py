@@ -62,45 +62,62 @@ def measured_peaks():
 
 
 class ClockSampler:
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """SM clock and slowdown reasons of one GPU, read through NVML (queries only) by a thread every
+    millisecond while the timed region runs; ``sample()`` lets the timing loop add readings of its own
+    (taken while the GPU still works through the queued launches)."""
+    REASONS = ((0x8, "hw_slowdown"), (0x40, "hw_thermal_slowdown"), (0x20, "sw_thermal_slowdown"), (0x4, "sw_power_cap"))
 
-    def __init__(self, index):
-        self.proc = None
+    def __init__(self, device_index):
+        import threading
+        self.h = None
+        self.samples = []
+        self._stop = threading.Event()
+        self.thread = None
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-        except OSError:
-            self.proc = None
+            import pynvml
+            import torch
+            self.nv = pynvml
+            pynvml.nvmlInit()
+            try:
+                uuid = "GPU-" + str(torch.cuda.get_device_properties(device_index).uuid)
+                self.h = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+            except Exception:
+                self.h = pynvml.nvmlDeviceGetHandleByIndex(device_index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+            self.thread = threading.Thread(target=self._loop, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.h = None
+
+    def sample(self):
+        if self.h is None:
+            return
+        try:
+            sm = float(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM))
+            try:
+                mask = int(self.nv.nvmlDeviceGetCurrentClocksEventReasons(self.h))
+            except Exception:
+                mask = int(self.nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h))
+            self.samples.append((sm, mask))
+        except Exception:
+            pass
+
+    def _loop(self):
+        while not self._stop.is_set():
+            self.sample()
+            time.sleep(0.001)
 
     def stop(self):
-        if self.proc is None:
+        if self.h is None:
             return None
-        self.proc.terminate()
-        try:
-            out, _ = self.proc.communicate(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-            out, _ = self.proc.communicate()
-        sm, mx, reasons = [], [], set()
-        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for line in out.splitlines():
-            parts = [x.strip() for x in line.split(",")]
-            if len(parts) < 6:
-                continue
-            try:
-                sm.append(float(parts[0]))
-                mx.append(float(parts[1]))
-            except ValueError:
-                continue
-            for n, v in zip(names, parts[2:6]):
-                if v.lower().startswith("active"):
-                    reasons.add(n)
-        if not sm:
+        self._stop.set()
+        if self.thread is not None:
+            self.thread.join(timeout=2)
+        if not self.samples:
             return None
-        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
-                "samples": len(sm)}
+        reasons = sorted({name for _, mask in self.samples for bit, name in self.REASONS if mask & bit})
+        return {"sm_mhz": statistics.median(x for x, _ in self.samples), "sm_max_mhz": self.max_mhz,
+                "reasons": reasons, "samples": len(self.samples), "source": "NVML, 1 ms period, during the timed region"}
 
 
 def build_workload(name, device, seed):
@@ -291,6 +308,8 @@ def main():
     for i in range(a.steps):
         out = step(i)
     e1.record()
+    if sampler:
+        sampler.sample()      # the GPU is still working through the queued steps
     barrier()
     ms = e0.elapsed_time(e1)
     clocks = sampler.stop() if sampler else None
