@@ -105,7 +105,8 @@ struct StreamDev {
     const int *indices;
     const int *lens;
     long long idx_stride, block_stride, pos_stride, scale_block_stride, scale_pos_stride;
-    int topk, num_slots, block_size, vec16;
+    int topk, num_slots, block_size;
+    int vec;   // widest aligned load of a row piece: 2 = 32 bytes, 1 = 16 bytes, 0 = 8 (fp8) / 4 (int8) bytes
 };
 
 struct KernelArgs {
@@ -157,6 +158,12 @@ __device__ __forceinline__ uint4 ldg_nc_v4(const void *p) {
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                  : "l"(p));
     return v;
+}
+// 32 bytes in one request (sm_100: 256-bit global loads); p must be 32-byte aligned.
+__device__ __forceinline__ void ldg_nc_v8(const void *p, uint4 &lo, uint4 &hi) {
+    asm volatile("ld.global.nc.L1::no_allocate.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(lo.x), "=r"(lo.y), "=r"(lo.z), "=r"(lo.w), "=r"(hi.x), "=r"(hi.y), "=r"(hi.z), "=r"(hi.w)
+                 : "l"(p));
 }
 __device__ __forceinline__ uint2 ldg_nc_v2(const void *p) {
     uint2 v;
@@ -259,7 +266,8 @@ template <int FMT>
 struct RowRef {
     const uint8_t *ptr;   // first data byte of the row (unused when !ok)
     uint32_t sc0, sc1;    // fp8: the 8 UE8M0 bytes; int8: sc0 = fp32 scale bits
-    bool ok, vec16;
+    bool ok;
+    int vec;   // see StreamDev::vec
 };
 
 __device__ __forceinline__ int load_slot_id(const KernelArgs &a, int t, int ns, int n, int g) {
@@ -275,7 +283,7 @@ __device__ __forceinline__ RowRef<FMT> make_row_ref(const KernelArgs &a, int ns,
     r.sc0 = 0u;
     r.sc1 = 0u;
     r.ok = false;
-    r.vec16 = true;
+    r.vec = 2;
     if (g >= n) return r;
     const StreamDev &s = (g < ns) ? a.swa : a.extra;
     if (static_cast<unsigned>(id) >= static_cast<unsigned>(s.num_slots)) return r;
@@ -283,7 +291,7 @@ __device__ __forceinline__ RowRef<FMT> make_row_ref(const KernelArgs &a, int ns,
     const int i = id - b * s.block_size;
     const uint8_t *blk = s.cache + static_cast<long long>(b) * s.block_stride;
     r.ok = true;
-    r.vec16 = s.vec16 != 0;
+    r.vec = s.vec;
     if constexpr (FMT == SMLA_FP8_DS_MLA) {
         r.ptr = blk + static_cast<long long>(i) * 576;
         const uint2 sc = ldg_nc_v2(blk + static_cast<long long>(s.block_size) * 576 + static_cast<long long>(i) * 8);
@@ -297,43 +305,71 @@ __device__ __forceinline__ RowRef<FMT> make_row_ref(const KernelArgs &a, int ns,
     return r;
 }
 
-// Register-chunk schedule: lane (row = lane & 7, quarter = lane >> 3) loads 16-byte piece
-// 4*j + quarter of its row in step j.  int8: 8 steps (512 B); fp8: 9 steps (448 B e4m3 + 128 B rope).
-// K-buffer chunk c (dims 128c..128c+127) is fed by steps {2c, 2c+1}, plus step 8 for fp8 chunk 3.
+// Register-chunk schedule: a row is cut into 16-byte pieces (fp8: 28 pieces of e4m3 + 8 of bf16 RoPE;
+// int8: 32 pieces).  Lane (row = lane & 7, quarter = lane >> 3) holds in raw[j] the piece
+//   piece16(j, quarter) = 8 * (j / 2) + 2 * quarter + (j & 1)   for j < 8,   32 + quarter for j = 8
+// for fp8 (the "wide" order): raw[2c], raw[2c+1] are 32 contiguous bytes of K-buffer chunk c (dims
+// 128c..128c+127) and are fetched by ONE 256-bit load when the rows are 32-byte aligned: 5 (fp8) / 4 (int8) load instructions
+// per lane and tile instead of 9 / 8.  The count matters more than the bytes: while the tensor pipe
+// streams operands, every load instruction takes ~20 cycles of issue (measured: twice as many loads
+// for the same bytes cost 18 % of the kernel).
 template <int FMT> struct Steps { static constexpr int kCount = (FMT == SMLA_FP8_DS_MLA) ? 9 : 8; };
 
+// The order is fixed per cache format at compile time (a run-time choice cost the int8 kernel 10 %):
+// fp8 rows use the wide order (their 576-byte pitch keeps them 32-byte aligned whenever the cache is;
+// otherwise the 32 bytes are fetched by narrower loads).  int8 rows, whose usual 528-byte pitch is only
+// 16-byte aligned, keep piece 4j + quarter: the four lanes of a row then read 64 contiguous bytes per
+// instruction (whole sectors), and chunk c is still raw[2c], raw[2c+1].
 template <int FMT>
-__device__ __forceinline__ void load_step(const RowRef<FMT> &r, int j, int quarter, uint4 &dst) {
-    if (r.ok) dst = load16<FMT>(r.ptr + (4 * j + quarter) * 16, r.vec16);
-    else dst = make_uint4(0u, 0u, 0u, 0u);
+__device__ __forceinline__ int piece16(int j, int quarter) {
+    if (j >= 8) return 32 + quarter;
+    return (FMT == SMLA_FP8_DS_MLA) ? 8 * (j >> 1) + 2 * quarter + (j & 1) : 4 * j + quarter;
+}
+
+template <int FMT>
+__device__ __forceinline__ void load_row_pieces(const RowRef<FMT> &r, int quarter, uint4 (&raw)[Steps<FMT>::kCount]) {
+    constexpr int J = Steps<FMT>::kCount;
+    if (!r.ok) {
+#pragma unroll
+        for (int j = 0; j < J; ++j) raw[j] = make_uint4(0u, 0u, 0u, 0u);
+    } else if (FMT == SMLA_FP8_DS_MLA && r.vec == 2) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) ldg_nc_v8(r.ptr + 128 * c + 32 * quarter, raw[2 * c], raw[2 * c + 1]);
+        raw[J - 1] = ldg_nc_v4(r.ptr + 512 + 16 * quarter);
+    } else {
+#pragma unroll
+        for (int j = 0; j < J; ++j) raw[j] = load16<FMT>(r.ptr + piece16<FMT>(j, quarter) * 16, r.vec >= 1);
+    }
 }
 
 template <int FMT>
 __device__ __forceinline__ void convert_step(const uint4 &raw, int j, int quarter, uint32_t sc0, uint32_t sc1,
                                              uint32_t k_row_addr /* K + rg*8192 + (lane&7)*16 */) {
     uint32_t o[8];
+    const uint32_t p16 = static_cast<uint32_t>(piece16<FMT>(j, quarter));
     if constexpr (FMT == SMLA_INT8_DS_MLA) {
         const float s = __uint_as_float(sc0);
         cvt_i8x4(raw.x, s, o[0], o[1]);
         cvt_i8x4(raw.y, s, o[2], o[3]);
         cvt_i8x4(raw.z, s, o[4], o[5]);
         cvt_i8x4(raw.w, s, o[6], o[7]);
-        const uint32_t dg = 2u * (4u * j + quarter);
+        const uint32_t dg = 2u * p16;
         st_shared_v4(k_row_addr + dg * kCoreBytes, o[0], o[1], o[2], o[3]);
         st_shared_v4(k_row_addr + (dg + 1u) * kCoreBytes, o[4], o[5], o[6], o[7]);
     } else {
-        if (j < 7) {
-            const uint32_t byte = (j < 4) ? ((sc0 >> (8 * j)) & 0xFFu) : ((sc1 >> (8 * (j - 4))) & 0xFFu);
+        if (p16 < 28u) {     // 16 e4m3 values of scale tile p16 / 4
+            const uint32_t tile = p16 >> 2;
+            const uint32_t byte = ((tile < 4u ? sc0 : sc1) >> (8u * (tile & 3u))) & 0xFFu;
             const float mult = __uint_as_float(byte << 23);   // 2^(ue8m0 - 127)
             cvt_e4m3x4(raw.x, mult, o[0], o[1]);
             cvt_e4m3x4(raw.y, mult, o[2], o[3]);
             cvt_e4m3x4(raw.z, mult, o[4], o[5]);
             cvt_e4m3x4(raw.w, mult, o[6], o[7]);
-            const uint32_t dg = 2u * (4u * j + quarter);
+            const uint32_t dg = 2u * p16;
             st_shared_v4(k_row_addr + dg * kCoreBytes, o[0], o[1], o[2], o[3]);
             st_shared_v4(k_row_addr + (dg + 1u) * kCoreBytes, o[4], o[5], o[6], o[7]);
-        } else {
-            const uint32_t dg = 56u + 4u * (j - 7) + quarter;   // RoPE tail: already bf16
+        } else {             // RoPE tail: already bf16, 8 dims per piece
+            const uint32_t dg = 56u + (p16 - 28u);
             st_shared_v4(k_row_addr + dg * kCoreBytes, raw.x, raw.y, raw.z, raw.w);
         }
     }
@@ -832,8 +868,7 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
         const int *r0 = sched + kSchedRec;
         g = r0[4] * kTileRows + my_row;
         cur = make_row_ref<FMT>(a, r0[3], r0[2], g, load_slot_id(a, r0[0], r0[3], r0[2], g));
-#pragma unroll
-        for (int j = 0; j < J; ++j) load_step<FMT>(cur, j, quarter, raw[j]);
+        load_row_pieces<FMT>(cur, quarter, raw);
     }
 
     for (int k = 0;; ++k) {      // segments
@@ -884,10 +919,7 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
             // (Measured: sending half of them after the softmax instead made the tile 25 % slower: the
             // issue of a load blocks the warp while the SM's load queue is full.)
             cur = make_row_ref<FMT>(a, n_ns, n_n, more ? g_next : n_n, id_next);
-            if (more) {
-#pragma unroll
-                for (int j = 0; j < J; ++j) load_step<FMT>(cur, j, quarter, raw[j]);
-            }
+            if (more) load_row_pieces<FMT>(cur, quarter, raw);
             g = g_next;
 
             // ---- the previous segment's epilogue, while the tensor pipe computes this tile's QK^T
@@ -1181,11 +1213,12 @@ int fill_stream(const smla_stream_t &s, int fmt, StreamDev &d) {
     const uintptr_t base = reinterpret_cast<uintptr_t>(s.cache);
     if (fmt == SMLA_FP8_DS_MLA) {
         if ((base & 7u) || (s.block_stride & 7)) return SMLA_EALIGN;
-        d.vec16 = ((base & 15u) == 0 && (s.block_stride & 15) == 0) ? 1 : 0;
+        d.vec = ((base & 31u) == 0 && (s.block_stride & 31) == 0) ? 2 : ((base & 15u) == 0 && (s.block_stride & 15) == 0) ? 1 : 0;
     } else {
         if (!s.scale) return SMLA_EINVAL;
         if ((base & 3u) || (s.block_stride & 3) || (s.pos_stride & 3)) return SMLA_EALIGN;
-        d.vec16 = ((base & 15u) == 0 && (s.block_stride & 15) == 0 && (s.pos_stride & 15) == 0) ? 1 : 0;
+        d.vec = ((base & 31u) == 0 && (s.block_stride & 31) == 0 && (s.pos_stride & 31) == 0) ? 2
+                : ((base & 15u) == 0 && (s.block_stride & 15) == 0 && (s.pos_stride & 15) == 0) ? 1 : 0;
     }
     return SMLA_OK;
 }
