@@ -329,16 +329,21 @@ __device__ __forceinline__ int piece16(int j, int quarter) {
 template <int FMT>
 __device__ __forceinline__ void load_row_pieces(const RowRef<FMT> &r, int quarter, uint4 (&raw)[Steps<FMT>::kCount]) {
     constexpr int J = Steps<FMT>::kCount;
-    if (!r.ok) {
+    // Invalid rows are zero rows; the choice is made per load (a select, no divergent branch).
+    if (FMT == SMLA_FP8_DS_MLA && r.vec == 2) {
 #pragma unroll
-        for (int j = 0; j < J; ++j) raw[j] = make_uint4(0u, 0u, 0u, 0u);
-    } else if (FMT == SMLA_FP8_DS_MLA && r.vec == 2) {
-#pragma unroll
-        for (int c = 0; c < 4; ++c) ldg_nc_v8(r.ptr + 128 * c + 32 * quarter, raw[2 * c], raw[2 * c + 1]);
-        raw[J - 1] = ldg_nc_v4(r.ptr + 512 + 16 * quarter);
+        for (int c = 0; c < 4; ++c) {
+            if (r.ok) ldg_nc_v8(r.ptr + 128 * c + 32 * quarter, raw[2 * c], raw[2 * c + 1]);
+            else raw[2 * c] = raw[2 * c + 1] = make_uint4(0u, 0u, 0u, 0u);
+        }
+        if (r.ok) raw[J - 1] = ldg_nc_v4(r.ptr + 512 + 16 * quarter);
+        else raw[J - 1] = make_uint4(0u, 0u, 0u, 0u);
     } else {
 #pragma unroll
-        for (int j = 0; j < J; ++j) raw[j] = load16<FMT>(r.ptr + piece16<FMT>(j, quarter) * 16, r.vec >= 1);
+        for (int j = 0; j < J; ++j) {
+            if (r.ok) raw[j] = load16<FMT>(r.ptr + piece16<FMT>(j, quarter) * 16, r.vec >= 1);
+            else raw[j] = make_uint4(0u, 0u, 0u, 0u);
+        }
     }
 }
 
