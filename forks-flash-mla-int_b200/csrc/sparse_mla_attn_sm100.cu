@@ -54,7 +54,7 @@ __device__ unsigned long long g_trace[32 * 16];
     do {                                                                                \
         if (blockIdx.x == SMLA_TRACE_CTA && (tile) < 32) g_trace[(tile) * 16 + (k)] = clock64(); \
     } while (0)
-__device__ unsigned long long g_cta_times[256 * 4];
+__device__ unsigned long long g_cta_times[256 * 8];
 __device__ __forceinline__ unsigned long long smla_globaltimer() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -62,7 +62,7 @@ __device__ __forceinline__ unsigned long long smla_globaltimer() {
 }
 #define SMLA_CTA_MARK(k)                                                                        \
     do {                                                                                        \
-        if (threadIdx.x == 0 && blockIdx.x < 256) g_cta_times[blockIdx.x * 4 + (k)] = smla_globaltimer(); \
+        if (threadIdx.x == 0 && blockIdx.x < 256) g_cta_times[blockIdx.x * 8 + (k)] = smla_globaltimer(); \
     } while (0)
 #else
 #define SMLA_MARK(tile, k) do {} while (0)
@@ -499,7 +499,50 @@ __device__ bool make_schedule(const KernelArgs &a, int *scratch, SegIter &it, lo
     P_out = gridDim.x;
     if (!a.balanced) return it.item < a.T * a.head_blocks;
 
-    // pass 1: W = head_blocks * sum_t max(1, tiles(t))
+    long long *wsum = reinterpret_cast<long long *>(scratch);          // [kNumWarps] then results
+    int *found = scratch + 2 * kNumWarps;                               // {t, excl_lo, excl_hi, scheduled tiles}
+    if (a.T <= kThreads) {
+        // The usual case (the balanced schedule is chosen for few items): one token per thread, one
+        // scan gives the total and every token's first global tile at once.
+        int ns = 0, n = 0;
+        if (tid < a.T) token_rows(a, tid, ns, n);
+        const int ntS = sched_tiles(n);
+        const long long v = tid < a.T ? static_cast<long long>(ntS) * a.head_blocks : 0;
+        long long incl = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const long long up = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += up;
+        }
+        if (lane == 31) wsum[warp] = incl;
+        __syncthreads();
+        long long before = 0, W = 0;
+        for (int w = 0; w < kNumWarps; ++w) {
+            if (w < warp) before += wsum[w];
+            W += wsum[w];
+        }
+        const long long P = min(static_cast<long long>(gridDim.x), W);
+        W_out = W;
+        P_out = static_cast<int>(P);
+        if (static_cast<long long>(blockIdx.x) >= P) return false;      // uniform
+        const long long lo = range_begin(blockIdx.x, W, P), hi = range_begin(blockIdx.x + 1, W, P);
+        const long long excl = before + incl - v;
+        if (tid < a.T && excl <= lo && lo < excl + v) {
+            const long long d = lo - excl;
+            found[0] = tid;
+            found[1] = static_cast<int>(d / ntS);                        // head block
+            found[2] = static_cast<int>(d - static_cast<long long>(found[1]) * ntS);   // first tile inside the item
+        }
+        __syncthreads();
+        it.t = found[0];
+        it.hb = found[1];
+        it.off = found[2];
+        it.gpos = lo;
+        it.rem = hi - lo;
+        return true;
+    }
+
+    // Many tokens: two passes.  Pass 1: W = head_blocks * sum_t max(1, tiles(t))
     long long mine = 0;
     for (int t = tid; t < a.T; t += kThreads) {
         int ns, n;
@@ -508,7 +551,6 @@ __device__ bool make_schedule(const KernelArgs &a, int *scratch, SegIter &it, lo
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, o);
-    long long *wsum = reinterpret_cast<long long *>(scratch);          // [kNumWarps] then results
     if (lane == 0) wsum[warp] = mine;
     __syncthreads();
     long long W = 0;
@@ -522,7 +564,6 @@ __device__ bool make_schedule(const KernelArgs &a, int *scratch, SegIter &it, lo
     const long long lo = range_begin(blockIdx.x, W, P), hi = range_begin(blockIdx.x + 1, W, P);
 
     // pass 2: the token whose tiles contain global tile `lo`
-    int *found = scratch + 2 * kNumWarps;       // {t, excl_lo, excl_hi}
     long long run = 0;
     for (int base = 0; base < a.T; base += kThreads) {
         const int t = base + tid;
@@ -869,12 +910,19 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
     uint4 raw[J];
     RowRef<FMT> cur;
     int g;
-    {   // raw bytes of the very first tile
+    {   // raw bytes of the very first tile; while its slot ids are on their way warp 0 prepares
+        // segments 1 and 2 (segment 0 was published before the roles split)
         const int *r0 = sched + kSchedRec;
         g = r0[4] * kTileRows + my_row;
-        cur = make_row_ref<FMT>(a, r0[3], r0[2], g, load_slot_id(a, r0[0], r0[3], r0[2], g));
+        const int id0 = load_slot_id(a, r0[0], r0[3], r0[2], g);
+        if (warp == 0) {
+            publish_segment(a, sched, 1, lane);
+            publish_segment(a, sched, 2, lane);
+        }
+        cur = make_row_ref<FMT>(a, r0[3], r0[2], g, id0);
         load_row_pieces<FMT>(cur, quarter, raw);
     }
+    named_bar_sync(kAllWorkersBar, kWorkerThreads);     // records 1 and 2 are visible to every worker
 
     for (int k = 0;; ++k) {      // segments
         // Fields of this segment (sg) and the next (ng) are read from shared memory where they are
@@ -1052,6 +1100,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const __gri
     // ---- this CTA's share of the work
     int *sched = reinterpret_cast<int *>(smem + L::kSched);
     if (a.balanced && tid == 0) reinterpret_cast<int4 *>(a.desc)[blockIdx.x] = make_int4(-1, 0, 0, 0);
+    if (a.sink != nullptr && tid * 32 < a.H) asm volatile("prefetch.global.L1 [%0];" ::"l"(a.sink + tid * 32));
     {
         SegIter iter;
         long long W;
@@ -1063,16 +1112,10 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const __gri
         }
     }
     __syncthreads();
-    if (warp == 0) {
-        publish_segment(a, sched, 0, lane);
-        publish_segment(a, sched, 1, lane);
-        publish_segment(a, sched, 2, lane);
-    }
-    __syncthreads();
-    if ((sched[kSchedRec + 7] & kSegValid) == 0) return;   // nothing but items without rows
-
-    // ---- set-up: barriers, TMEM, reference max and Q tile of the first segment
-    if (tid == 0) {
+    SMLA_CTA_MARK(3);
+    // ---- set-up, three things side by side: first segment record, barriers, tensor memory
+    if (warp == 0) publish_segment(a, sched, 0, lane);
+    if (tid == 32) {
         const uint32_t bars = smem_u32(smem + L::kBars);
         for (int c = 0; c < 4; ++c) mbar_init(bars + (kBarReady + c) * 8, kWorkerWarps);
         for (int c = 0; c < 4; ++c) mbar_init(bars + (kBarFree + c) * 8, 1);
@@ -1087,6 +1130,16 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const __gri
         tmem_alloc(smem_u32(smem + L::kTmemPtr), kTmemCols);
         tmem_relinquish();
     }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    SMLA_CTA_MARK(4);
+    if ((sched[kSchedRec + 7] & kSegValid) == 0) {   // nothing but items without rows
+        if (warp == kMmaWarp) tmem_dealloc(*reinterpret_cast<volatile uint32_t *>(smem + L::kTmemPtr), kTmemCols);
+        return;
+    }
+
+    // ---- reference max and Q tile of the first segment
     {
         const int *r0 = sched + kSchedRec;
         const int h0 = r0[1] * 64, hvalid = min(NPAD, a.H - h0);
@@ -1096,6 +1149,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const __gri
         // their first hand-over, so the copy overlaps the gather of the first K tile.
         if (warp < kWorkerWarps) issue_q_tile<NPAD>(a, smem, r0[0], h0, hvalid, warp, lane, kWorkerWarps);
     }
+    SMLA_CTA_MARK(5);
     fence_async_smem();
     tc_fence_before_sync();
     __syncthreads();
@@ -1344,7 +1398,7 @@ extern "C" __attribute__((visibility("default"))) int smla_debug_read_trace(unsi
 }
 extern "C" __attribute__((visibility("default"))) int smla_debug_read_cta_times(unsigned long long *host_out) {
     cudaDeviceSynchronize();
-    return static_cast<int>(cudaMemcpyFromSymbol(host_out, g_cta_times, sizeof(unsigned long long) * 256 * 4));
+    return static_cast<int>(cudaMemcpyFromSymbol(host_out, g_cta_times, sizeof(unsigned long long) * 256 * 8));
 }
 #endif
 
