@@ -6,6 +6,8 @@ tests/test_sparse_mla_decode_int8_adversarial.py, tests/test_sparse_mla_prefill_
 """
 import math
 
+import ctypes
+
 import numpy as np
 import pytest
 import torch
@@ -273,6 +275,47 @@ def test_decode_int8_split_stability(fm, monkeypatch):
     assert torch.equal(again, auto)     # 96 rounds up to one 128-row tile: same schedule, same bits
 
 
+@pytest.mark.parametrize("T,H,splits", [(5, 64, 3), (37, 128, 2), (700, 16, 2), (9, 96, 40)])
+def test_balanced_schedule_edge_cases(fm, T, H, splits):
+    """The persistent kernel cuts the 128-row tiles of all (token, 64-head block) items into equal ranges,
+    one per CTA.  Ragged lens with empty tokens (first, last and in between), a partial second head
+    block (H=96), head blocks of 16, more tokens than threads in a CTA (the two-pass scan) and far more
+    scratch than CTAs must all give the unsplit result and the oracle's."""
+    from flash_mla import c_abi
+    rng = np.random.default_rng(1000 + T)
+    torch.manual_seed(1000 + T)
+    topk = 704 if T < 100 else 200
+    cache, K = fp8_cache_from_latent(_rand_latent(rng, 1024, 1.0), 64)
+    q = torch.randn(T, H, 512, device="cuda").to(torch.bfloat16)
+    idx = torch.randint(0, 1024, (T, topk), dtype=torch.int32, device="cuda")
+    idx[torch.rand(T, topk, device="cuda") < 0.03] = -1
+    lens = torch.randint(0, topk + 1, (T,), dtype=torch.int32, device="cuda")
+    lens[0] = 0
+    lens[-1] = 0
+    if T > 4:
+        lens[2] = 0
+        lens[3] = topk
+    sink = torch.randn(H, device="cuda")
+    ref = oracle_out(q, K, idx, lens, scale=SCALE, sink=sink)
+    lib = c_abi.load()
+    outs = []
+    for s in (1, splits):
+        out = torch.full_like(q, 7.0)
+        ws = torch.empty(lib.smla_attn_workspace_bytes(T, H, s) // 4 + 4, dtype=torch.float32, device="cuda") if s > 1 else None
+        p = c_abi.attn_params(q, out, c_abi.SMLA_FP8_DS_MLA, SCALE, c_abi.stream_from_tensors(cache, None, idx, lens),
+                              None, sink, num_splits=s, workspace=ws)
+        c_abi.check(lib.smla_sparse_mla_decode(p, torch.cuda.current_stream().cuda_stream))
+        torch.cuda.synchronize()
+        assert_attention_close(out, ref, f"T={T} H={H} num_splits={s}")
+        assert torch.all(out[0] == 0) and torch.all(out[-1] == 0)
+        outs.append(out.float())
+    d = outs[1] - outs[0]
+    assert d.pow(2).mean().sqrt().item() < 5e-4 and d.abs().max().item() <= 2.0 ** -7
+    status = ctypes.c_int(0)
+    lib.smla_read_device_status(ctypes.byref(status))
+    assert status.value == 0
+
+
 def test_decode_int8_many_tokens_single_split(fm):
     """...int8_adversarial.py:130-151: T=64 fills the SMs, one split."""
     rng = np.random.default_rng(41)
@@ -335,10 +378,9 @@ def test_outlier_rows_and_large_scores(fm):
 
 
 def test_scores_jump_far_above_the_first_tile(fm):
-    """The softmax reference is fixed from the first 64 rows; rows that score more than 2^72 above
-    them make the kernel start the token over with a higher reference.  First rows are zero rows
-    (invalid ids), later rows are large and aligned differently per head, so scores jump by hundreds
-    of log2 units for some heads and fall for others."""
+    """The softmax reference max is moved lazily; here the first rows are zero rows (invalid ids) and
+    later rows are large and aligned differently per head, so scores jump by hundreds of log2 units
+    for some heads and fall for others, in both row orders."""
     rng = np.random.default_rng(77)
     torch.manual_seed(77)
     T, H, topk = 2, 64, 448
