@@ -30,6 +30,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
+#include <cuda.h>            // CUtensorMap and its enums only; the encoder is looked up at run time, libcuda is not linked
 #include <cuda_runtime.h>
 
 #include <cmath>
@@ -97,7 +98,9 @@ constexpr int kBarS = 8;       //     S^T of this tile is complete in TMEM
 constexpr int kBarP = 9;       //     P^T of this tile is in shared memory (16 arrivals)
 constexpr int kBarO = 10;      //     the last PV of a segment has completed
 constexpr int kBarOFree = 11;  //     the segment's epilogue has read O^T (16 arrivals)
-static_assert(kBarOFree + 1 <= 12, "mbarrier slots reserved in Smem");
+constexpr int kBarQ = 12;      //     the segment's Q tile is in shared memory (3 arrivals: the Q-loader warps)
+static_assert(kBarQ + 1 <= 14, "mbarrier slots reserved in Smem");
+constexpr int kQLoadWarps = 3;                   // warps 17..19
 
 struct StreamDev {
     const uint8_t *cache;
@@ -121,6 +124,8 @@ struct KernelArgs {
     StreamDev swa, extra;
     int T, H, head_blocks, balanced;
     float scale_log2;
+    int q_tma;            // the Q tile is fetched with one TMA tensor copy through q_map (else cp.async)
+    CUtensorMap q_map;    // 5-D view of q: {8 dims, 8 heads, 64 dim groups, H/8 head groups, T}
 };
 
 template <int NPAD>
@@ -133,7 +138,7 @@ struct Smem {
     static constexpr int kAlpha = kM + NPAD * 4;         // rescale factor / final 1/l per head
     static constexpr int kShift = kAlpha + NPAD * 4;     // m_old - m_new of the last reference move
     static constexpr int kBars = kShift + NPAD * 4;      // kNumBars mbarriers
-    static constexpr int kTmemPtr = kBars + 12 * 8;
+    static constexpr int kTmemPtr = kBars + 14 * 8;
     static constexpr int kAbort = kTmemPtr + 4;
     static constexpr int kSched = kAbort + 4 + 8;        // 160 ints: work distribution (scan scratch, iterator, segment ring)
     // Epilogue staging, 8 KB per column-slice group.  With 64 heads only 16 KB are left, so groups 0
@@ -713,6 +718,10 @@ __device__ __forceinline__ void mma_role(uint8_t *smem, uint32_t tmem_base) {
         const int ntl = rec[5];
         for (int it = 0; it < ntl; ++it, ++gt) {
             SMLA_MARK(gt, 0);
+            if (it == 0 && !mbar_wait(bars + kBarQ * 8, so & 1, abort_flag)) {   // this item's Q tile
+                give_up(abort_flag, kStatusMmaWait);
+                return;
+            }
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 if (!mbar_wait(bars + (kBarReady + c) * 8, gt & 1, abort_flag)) {
@@ -784,13 +793,50 @@ __device__ __forceinline__ float initial_ref(const KernelArgs &a, bool complete,
     return 0.0f;
 }
 
+// ------------------------------------------------------------------ Q-loader warps (17..19)
+// Fetching a 64 KB Q tile takes ~4.5k cycles of load issue; done by the worker warps it sat on the
+// critical path of every segment boundary.  These three warps have nothing else to do: they follow
+// the segments in the ring, wait for every tile's S^T barrier so that they know when the last QK^T of
+// a segment has completed (the Q buffer is then free), fetch the next item's Q tile with cp.async
+// and hand it to the MMA thread through the Q barrier.
+template <int NPAD>
+__device__ __forceinline__ void qload_role(const KernelArgs &a, uint8_t *smem, int qwarp, int lane) {
+    using L = Smem<NPAD>;
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::kAbort);
+    const uint32_t bars = smem_u32(smem + L::kBars);
+    const volatile int *ring = reinterpret_cast<const volatile int *>(smem + L::kSched) + kSchedRec;
+    int gt = 0;
+    for (int so = 0;; ++so) {
+        const volatile int *rec = ring + 12 * (so % 5);
+        if ((rec[7] & kSegValid) == 0) break;
+        const int h0 = rec[1] * 64;
+        if (a.q_tma) {
+            // One tensor copy: box {8, 8, 64, NPAD/8, 1} of the 5-D view lands as [head group][dim group]
+            // [head % 8][8 dims], which is the K-major core-matrix layout of the Q operand; head groups
+            // beyond H are zero-filled.  The innermost coordinate is 0 (TMA needs it 16-byte aligned).
+            if (qwarp == 0 && lane == 0) {
+                mbar_arrive_expect_tx(bars + kBarQ * 8, NPAD * 1024);
+                tma_load_5d(smem_u32(smem + L::kQ), &a.q_map, bars + kBarQ * 8, 0, 0, 0, h0 / 8, rec[0]);
+            }
+        } else {
+            issue_q_tile<NPAD>(a, smem, rec[0], h0, min(NPAD, a.H - h0), qwarp, lane, kQLoadWarps);
+            cp_async_wait_all();
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bars + kBarQ * 8);
+        }
+        const int ntl = rec[5];
+        for (int it = 0; it < ntl; ++it, ++gt)
+            if (!warp_wait(bars + kBarS * 8, gt & 1, abort_flag, lane, kStatusSoftmaxWait)) return;
+    }
+}
+
 // ------------------------------------------------------------------ worker warps (0..15)
 // Each worker warp alternates between two jobs that never overlap in time for one tile:
 //   convert: it owns rows 8w..8w+7 of the tile; raw bytes (already in registers) -> bf16 K chunks;
 //   softmax: it owns TMEM lanes 32*(w%4).. (rows of S^T / dims of O^T) and head columns
 //            (NPAD/4)*(w/4)..: scores -> P^T, running denominators, rare accumulator rescale.
-// The raw bytes of the next tile are always in flight, across segment boundaries too, and the next
-// item's Q tile is fetched while the last PV of the current one runs.
+// The raw bytes of the next tile are always in flight, across segment boundaries too.
 template <int FMT, int NPAD>
 __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, uint32_t tmem_base, int warp, int lane) {
     using L = Smem<NPAD>;
@@ -960,7 +1006,6 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
                     if (mine) convert_step<FMT>(raw[j], j, quarter, cur.sc0, cur.sc1, k_row_addr);
                 }
                 if (tracer && (c == 0 || c == 3)) SMLA_MARK(gt, 8 + c);
-                if (c == 0 && first_tile) cp_async_wait_all();   // this item's Q tile (fetched by cp.async) has landed
                 fence_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bars + (kBarReady + c) * 8);
@@ -1075,17 +1120,11 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
             }
         }
 
-        // ---- end of the segment.  Every QK^T of it has completed (this warp saw the last S^T), so the
-        // Q buffer is free: fetch the next item's Q tile while the last PV runs.  The segment's epilogue
-        // is run inside the next segment's first tile.
+        // ---- end of the segment; its epilogue is run inside the next segment's first tile
         if (!have_next) {
             epilogue(sg, nullptr, k & 1);
             break;
         }
-        const int n_h0 = ng[1] * 64;
-        if (tracer) SMLA_MARK(gt < 32 ? gt : 31, 9);
-        issue_q_tile<NPAD>(a, smem, ng[0], n_h0, min(NPAD, a.H - n_h0), warp, lane, kWorkerWarps);
-        if (tracer) SMLA_MARK(gt < 32 ? gt : 31, 10);
     }
 }
 
@@ -1123,6 +1162,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const __gri
         mbar_init(bars + kBarP * 8, kWorkerWarps);
         mbar_init(bars + kBarO * 8, 1);
         mbar_init(bars + kBarOFree * 8, kWorkerWarps);
+        mbar_init(bars + kBarQ * 8, a.q_tma ? 1 : kQLoadWarps);
         *reinterpret_cast<volatile int *>(smem + L::kAbort) = 0;
         mbar_init_fence();
     }
@@ -1145,9 +1185,6 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const __gri
         const int h0 = r0[1] * 64, hvalid = min(NPAD, a.H - h0);
         if (tid < NPAD)
             reinterpret_cast<float *>(smem + L::kM)[tid] = initial_ref(a, (r0[7] & kSegComplete) != 0, h0, tid, hvalid);
-        // Q tile of the first segment: fetched by the worker warps, which wait for it only before
-        // their first hand-over, so the copy overlaps the gather of the first K tile.
-        if (warp < kWorkerWarps) issue_q_tile<NPAD>(a, smem, r0[0], h0, hvalid, warp, lane, kWorkerWarps);
     }
     SMLA_CTA_MARK(5);
     fence_async_smem();
@@ -1159,9 +1196,11 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const __gri
 
     if (warp < kWorkerWarps) {
         worker_role<FMT, NPAD>(a, smem, tmem_base, warp, lane);
-    } else {
-        if (warp == kMmaWarp && lane == 0) mma_role<NPAD>(smem, tmem_base);
+    } else if (warp == kMmaWarp) {
+        if (lane == 0) mma_role<NPAD>(smem, tmem_base);
         __syncwarp();
+    } else {
+        qload_role<NPAD>(a, smem, warp - kMmaWarp - 1, lane);
     }
 
     __syncthreads();
@@ -1308,6 +1347,39 @@ int launch_fwd_npad(int npad, const KernelArgs &a, unsigned grid, cudaStream_t s
     }
 }
 
+// cuTensorMapEncodeTiled, fetched through the runtime so that libcuda need not be linked.
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn tensor_map_encoder() {
+    static EncodeTiledFn fn = [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// 5-D view of q [T, H, 512] whose box {8, 8, 64, npad/8, 1} is the Q operand's shared-memory layout.
+// False (the kernel then uses cp.async) when H is not a multiple of 8 or the driver refuses the map.
+bool make_q_tensor_map(const KernelArgs &a, int npad, CUtensorMap *map) {
+    if (a.H % 8 != 0 || getenv("SMLA_NO_TMA") != nullptr) return false;
+    EncodeTiledFn enc = tensor_map_encoder();
+    if (enc == nullptr) return false;
+    const cuuint64_t dims[5] = {8, 8, 64, static_cast<cuuint64_t>(a.H / 8), static_cast<cuuint64_t>(a.T)};
+    const cuuint64_t strides[4] = {static_cast<cuuint64_t>(a.q_hs) * 2, 16, static_cast<cuuint64_t>(a.q_hs) * 16,
+                                   static_cast<cuuint64_t>(a.q_ts) * 2};
+    const cuuint32_t box[5] = {8, 8, 64, static_cast<cuuint32_t>(npad / 8), 1};
+    const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<__nv_bfloat16 *>(a.q), dims, strides, box,
+                           estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                           CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
 int sm_count_of_current_device(int &count) {
     static int cached[64] = {};
     int dev = 0;
@@ -1378,6 +1450,7 @@ int launch_sparse_mla_attention(const smla_attn_params_t &p, int num_splits, voi
         a.balanced = 0;
         ctas = std::min<long long>(items, sms);
     }
+    a.q_tma = make_q_tensor_map(a, npad, &a.q_map) ? 1 : 0;
     const unsigned grid = static_cast<unsigned>(ctas);
     rc = (p.cache_format == SMLA_FP8_DS_MLA) ? launch_fwd_npad<SMLA_FP8_DS_MLA>(npad, a, grid, stream)
                                              : launch_fwd_npad<SMLA_INT8_DS_MLA>(npad, a, grid, stream);
