@@ -98,9 +98,9 @@ constexpr int kBarS = 8;       //     S^T of this tile is complete in TMEM
 constexpr int kBarP = 9;       //     P^T of this tile is in shared memory (16 arrivals)
 constexpr int kBarO = 10;      //     the last PV of a segment has completed
 constexpr int kBarOFree = 11;  //     the segment's epilogue has read O^T (16 arrivals)
-constexpr int kBarQ = 12;      //     the segment's Q tile is in shared memory (3 arrivals: the Q-loader warps)
+constexpr int kBarQ = 12;      //     the segment's Q tile is in shared memory (TMA: 1 arrival + bytes; else 2 warps)
 static_assert(kBarQ + 1 <= 14, "mbarrier slots reserved in Smem");
-constexpr int kQLoadWarps = 3;                   // warps 17..19
+constexpr int kQLoadWarps = 2;                   // warps 17 and 19 (cp.async fallback; with TMA warp 17 alone)
 
 struct StreamDev {
     const uint8_t *cache;
@@ -616,11 +616,14 @@ __device__ bool make_schedule(const KernelArgs &a, int *scratch, SegIter &it, lo
 }
 
 // The segments live in shared memory, not in registers: a ring of five records (segment k in record
-// k % 5) that warp 0 fills three segments ahead (the MMA thread reads it too) and the iterator state it
-// continues from.  Offsets in ints from Smem::kSched:
+// k % 5) filled by the scheduler warp (warp 18, otherwise idle) three segments ahead, the iterator
+// state it continues from, and the count of records published so far, which every reader checks
+// before it looks at a record (the count is written after a fence, read volatile).  Offsets in ints
+// from Smem::kSched:
 constexpr int kSchedScan = 0;       // [64]  scratch of make_schedule
 constexpr int kSchedIter = 64;      // [12]  t, hb, off, item, stride, first, gpos(2), rem(2), W(2)
 constexpr int kSchedP = 76;         // [1]   CTAs sharing the tiles
+constexpr int kSchedPub = 77;       // [1]   records published so far
 constexpr int kSchedRec = 80;       // [5][12] t, hb, n, ns, tile0, ntl, slot, flags, last CTA of the item
 constexpr int kSchedInts = kSchedRec + 60;
 static_assert(kSchedInts <= 160, "Smem::kSched holds 160 ints");
@@ -649,8 +652,8 @@ __device__ __forceinline__ void zero_item(const KernelArgs &a, const Seg &s, int
     }
 }
 
-// Warp 0 (all lanes, uniformly): continue the iterator to the next segment that has tiles, zeroing the
-// outputs of items without rows on the way, and publish it as segment `k`.
+// One warp (all lanes, uniformly): continue the iterator to the next segment that has tiles, zeroing the
+// outputs of items without rows on the way, and publish it as segment `k` (records are published in order).
 __device__ __forceinline__ void publish_segment(const KernelArgs &a, int *sched, int k, int lane) {
     SegIter it;
     long long W;
@@ -680,8 +683,28 @@ __device__ __forceinline__ void publish_segment(const KernelArgs &a, int *sched,
         r[0] = s.t, r[1] = s.hb, r[2] = s.n, r[3] = s.ns, r[4] = s.tile0, r[5] = s.ntl, r[6] = s.slot;
         r[7] = ok ? (kSegValid | (s.owns_first ? kSegOwnsFirst : 0) | (s.complete ? kSegComplete : 0)) : 0;
         r[8] = (ok && s.owns_first) ? cta_of_tile(s.gfirst + s.ntS - 1, W, P) : 0;
+        __threadfence_block();
+        reinterpret_cast<volatile int *>(sched)[kSchedPub] = k + 1;
     }
     __syncwarp();
+}
+
+// Readers call this before they look at record k.  In practice it never waits (records are three
+// segments ahead); the wait is time-bounded like every other one.
+__device__ __forceinline__ bool wait_published(const int *sched, int k, volatile int *abort_flag) {
+    const volatile int *pub = reinterpret_cast<const volatile int *>(sched) + kSchedPub;
+    if (*pub > k) return true;
+    const uint64_t t0 = globaltimer_ns();
+    for (uint32_t it = 1;; ++it) {
+        if (*pub > k) return true;
+        if ((it & 63u) == 0u) {
+            if (*abort_flag != 0) return false;
+            if (globaltimer_ns() - t0 > kWaitLimitNs) {
+                give_up(abort_flag, kStatusMmaWait);
+                return false;
+            }
+        }
+    }
 }
 
 // ------------------------------------------------------------------ MMA issue (lane 0 of the MMA warp)
@@ -714,6 +737,7 @@ __device__ __forceinline__ void mma_role(uint8_t *smem, uint32_t tmem_base) {
     int gt = 0;
     for (int so = 0;; ++so) {
         const volatile int *rec = ring + 12 * (so % 5);
+        if (!wait_published(reinterpret_cast<const int *>(smem + L::kSched), so, abort_flag)) return;
         if ((rec[7] & kSegValid) == 0) break;
         const int ntl = rec[5];
         for (int it = 0; it < ntl; ++it, ++gt) {
@@ -808,6 +832,7 @@ __device__ __forceinline__ void qload_role(const KernelArgs &a, uint8_t *smem, i
     int gt = 0;
     for (int so = 0;; ++so) {
         const volatile int *rec = ring + 12 * (so % 5);
+        if (!wait_published(reinterpret_cast<const int *>(smem + L::kSched), so, abort_flag)) return;
         if ((rec[7] & kSegValid) == 0) break;
         const int h0 = rec[1] * 64;
         if (a.q_tma) {
@@ -828,6 +853,29 @@ __device__ __forceinline__ void qload_role(const KernelArgs &a, uint8_t *smem, i
         const int ntl = rec[5];
         for (int it = 0; it < ntl; ++it, ++gt)
             if (!warp_wait(bars + kBarS * 8, gt & 1, abort_flag, lane, kStatusSoftmaxWait)) return;
+    }
+}
+
+// ------------------------------------------------------------------ scheduler warp (18)
+// Publishes the segment records.  Records 1..4 at once, then record s + 3 when the first tile of
+// segment s has been scored: the ring slot it overwrites belonged to segment s - 2, whose last reader
+// (its epilogue, run in the first tile of segment s - 1) has finished by then.
+template <int NPAD>
+__device__ __forceinline__ void scheduler_role(const KernelArgs &a, uint8_t *smem, int lane) {
+    using L = Smem<NPAD>;
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::kAbort);
+    const uint32_t bars = smem_u32(smem + L::kBars);
+    int *sched = reinterpret_cast<int *>(smem + L::kSched);
+    for (int k = 1; k < 5; ++k) publish_segment(a, sched, k, lane);
+    int gt = 0;
+    for (int s = 0;; ++s) {
+        const volatile int *rec = sched + kSchedRec + 12 * (s % 5);
+        if ((rec[7] & kSegValid) == 0) break;
+        const int ntl = rec[5];
+        for (int it = 0; it < ntl; ++it, ++gt) {
+            if (!warp_wait(bars + kBarS * 8, gt & 1, abort_flag, lane, kStatusSoftmaxWait)) return;
+            if (it == 0 && s >= 2) publish_segment(a, sched, s + 3, lane);
+        }
     }
 }
 
@@ -956,25 +1004,19 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
     uint4 raw[J];
     RowRef<FMT> cur;
     int g;
-    {   // raw bytes of the very first tile; while its slot ids are on their way warp 0 prepares
-        // segments 1 and 2 (segment 0 was published before the roles split)
+    {   // raw bytes of the very first tile (segment 0 was published before the roles split)
         const int *r0 = sched + kSchedRec;
         g = r0[4] * kTileRows + my_row;
-        const int id0 = load_slot_id(a, r0[0], r0[3], r0[2], g);
-        if (warp == 0) {
-            publish_segment(a, sched, 1, lane);
-            publish_segment(a, sched, 2, lane);
-        }
-        cur = make_row_ref<FMT>(a, r0[3], r0[2], g, id0);
+        cur = make_row_ref<FMT>(a, r0[3], r0[2], g, load_slot_id(a, r0[0], r0[3], r0[2], g));
         load_row_pieces<FMT>(cur, quarter, raw);
     }
-    named_bar_sync(kAllWorkersBar, kWorkerThreads);     // records 1 and 2 are visible to every worker
 
     for (int k = 0;; ++k) {      // segments
         // Fields of this segment (sg) and the next (ng) are read from shared memory where they are
         // used rather than held in registers across the tile loop.
         const volatile int *sg = sched + kSchedRec + 12 * (k % 5);
         const volatile int *ng = sched + kSchedRec + 12 * ((k + 1) % 5);
+        wait_published(sched, k + 1, abort_flag);
         const bool have_next = (ng[7] & kSegValid) != 0;
         if (tid == 0 && (sg[7] & kSegOwnsFirst)) {   // this CTA holds the first tiles of an item that continues elsewhere
             int4 d;
@@ -1111,13 +1153,6 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
                 ColReduce<CW, 16, false>::run(sm, lane, r);
                 lacc += r[0];
             }
-            // Warp 0 prepares segment k + 3 once per segment, here where no other warp waits for it.  The
-            // others read that record from segment k + 2 on, after the all-worker barriers of the
-            // epilogue in between; the record it replaces (segment k - 2) is long unused.
-            if (warp == 0 && first_tile) {
-                publish_segment(a, sched, k + 3, lane);
-                if (tracer) SMLA_MARK(gt, 15);
-            }
         }
 
         // ---- end of the segment; its epilogue is run inside the next segment's first tile
@@ -1153,7 +1188,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const __gri
     __syncthreads();
     SMLA_CTA_MARK(3);
     // ---- set-up, three things side by side: first segment record, barriers, tensor memory
-    if (warp == 0) publish_segment(a, sched, 0, lane);
+    if (warp == 0) publish_segment(a, sched, 0, lane);      // sets the published count to 1
     if (tid == 32) {
         const uint32_t bars = smem_u32(smem + L::kBars);
         for (int c = 0; c < 4; ++c) mbar_init(bars + (kBarReady + c) * 8, kWorkerWarps);
@@ -1199,8 +1234,14 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const __gri
     } else if (warp == kMmaWarp) {
         if (lane == 0) mma_role<NPAD>(smem, tmem_base);
         __syncwarp();
+    } else if (a.q_tma) {
+        // one tensor copy per item needs one thread; the next warp publishes the schedule
+        if (warp == kMmaWarp + 1) qload_role<NPAD>(a, smem, 0, lane);
+        if (warp == kMmaWarp + 2) scheduler_role<NPAD>(a, smem, lane);
     } else {
-        qload_role<NPAD>(a, smem, warp - kMmaWarp - 1, lane);
+        // cp.async fallback for Q: two loader warps, one scheduler warp
+        if (warp == kMmaWarp + 2) scheduler_role<NPAD>(a, smem, lane);
+        else qload_role<NPAD>(a, smem, warp == kMmaWarp + 1 ? 0 : 1, lane);
     }
 
     __syncthreads();
