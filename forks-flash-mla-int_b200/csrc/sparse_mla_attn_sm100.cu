@@ -39,6 +39,8 @@
 
 #include "sm100_ptx.cuh"
 #include <algorithm>
+#include <atomic>
+#include <random>
 
 #include "smla_internal.h"
 
@@ -120,7 +122,11 @@ struct KernelArgs {
     const float *sink;
     float *part_o;   // fp32 [slot, NPAD, 512] un-normalised partial outputs (balanced schedule)
     float *part_ml;  // fp32 [slot, NPAD, 2]   {reference max (log2 units), denominator}
-    int *desc;       // int4 [CTA] merge descriptors {item, segments, first slot, heads} or {-1}
+    int *desc;       // int4 [CTA] merge descriptors {item, segments, first slot, heads} or {-1} (combine kernel)
+    unsigned long long *flags;    // [slot] launch tag once the slot's partial is complete (fused merge)
+    unsigned long long tag;       // unique per launch
+    int fused_merge;              // the CTA that holds an item's first tiles merges the other partials in
+                                  // its own epilogue; no second kernel
     StreamDev swa, extra;
     int T, H, head_blocks, balanced;
     float scale_log2;
@@ -817,6 +823,73 @@ __device__ __forceinline__ float initial_ref(const KernelArgs &a, bool complete,
     return 0.0f;
 }
 
+// ------------------------------------------------------------------ merging one head (one warp)
+// out = sum_s 2^(m_s - M) O_s / (sum_s 2^(m_s - M) l_s + 2^(sink - M)),  M = max(m_s, sink), over the S
+// partial segments whose slots `slot_of(k)` names.  Four segments in flight per lane; partials are read
+// past L1 (another SM wrote them).
+template <typename SlotOf>
+__device__ __forceinline__ void merge_head(const float *part_o, const float *part_ml, SlotOf slot_of, int S, int npad,
+                                           int hl, float sink_l2, __nv_bfloat16 *dst, int lane) {
+    auto ml_of = [&](int k) {
+        return __ldcg(reinterpret_cast<const float2 *>(part_ml) + static_cast<long long>(slot_of(k)) * npad + hl);
+    };
+    float M = sink_l2;
+    for (int k = lane; k < S; k += 32) {
+        const float2 e = ml_of(k);
+        if (e.y > 0.0f) M = fmaxf(M, e.x);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    float denom = 0.0f;
+    if (M > -INFINITY) {
+        for (int k = lane; k < S; k += 32) {
+            const float2 e = ml_of(k);
+            if (e.y > 0.0f) denom += fast_exp2(e.x - M) * e.y;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) denom += __shfl_xor_sync(0xffffffffu, denom, o);
+    if (M > -INFINITY) denom += fast_exp2(sink_l2 - M);
+
+    float acc[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) acc[i] = 0.0f;
+    for (int k0 = 0; k0 < S; k0 += 4) {
+        float4 x[4][4];
+        float w[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int k = min(k0 + u, S - 1);
+            const float2 e = ml_of(k);      // the same address in every lane: one broadcast load
+            // empty segments (l == 0) get weight 0; their rows are loaded but never multiplied in
+            w[u] = (k0 + u < S && e.y > 0.0f && M > -INFINITY) ? fast_exp2(e.x - M) : 0.0f;
+            const float4 *src = reinterpret_cast<const float4 *>(part_o) +
+                                (static_cast<long long>(slot_of(k)) * npad + hl) * (kD / 4);
+#pragma unroll
+            for (int v = 0; v < 4; ++v) x[u][v] = __ldcg(src + v * 32 + lane);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (w[u] != 0.0f) {
+#pragma unroll
+                for (int v = 0; v < 4; ++v) {
+                    acc[4 * v] += w[u] * x[u][v].x;
+                    acc[4 * v + 1] += w[u] * x[u][v].y;
+                    acc[4 * v + 2] += w[u] * x[u][v].z;
+                    acc[4 * v + 3] += w[u] * x[u][v].w;
+                }
+            }
+        }
+    }
+    const float inv = denom > 0.0f ? 1.0f / denom : 0.0f;
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+        const uint2 pk = make_uint2(pack_bf16x2(acc[4 * v] * inv, acc[4 * v + 1] * inv),
+                                    pack_bf16x2(acc[4 * v + 2] * inv, acc[4 * v + 3] * inv));
+        *reinterpret_cast<uint2 *>(dst + (v * 32 + lane) * 4) = pk;
+    }
+}
+
 // ------------------------------------------------------------------ Q-loader warps (17..19)
 // Fetching a 64 KB Q tile takes ~4.5k cycles of load issue; done by the worker warps it sat on the
 // critical path of every segment boundary.  These three warps have nothing else to do: they follow
@@ -930,16 +1003,61 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
         constexpr int HR = CW < 8 ? CW : 8;     // heads per staging round
         const int t = pg[0], h0 = pg[1] * 64, slot = pg[6];
         const int hvalid = min(NPAD, a.H - h0);
-        const bool direct = (pg[7] & kSegComplete) != 0;
+        // Fused merge: the segment that holds an item's first tiles (always its CTA's last one) takes
+        // the item's other partial segments, slots 2(c+1), 2(c+2), ..., into its own output.
+        const bool owner = a.fused_merge && (pg[7] & kSegOwnsFirst) != 0;
+        const bool direct = (pg[7] & kSegComplete) != 0 || owner;
+        const int others = owner ? pg[8] - static_cast<int>(blockIdx.x) : 0;
+        float *wk_s = reinterpret_cast<float *>(smem + L::kK);     // [others][NPAD] weights (the K buffer is idle: last segment)
         warp_wait(bars + kBarO * 8, parity, abort_flag, lane, kStatusEpilogueWait);
         tc_fence_after_sync();
         if (tracer) SMLA_MARK(gt < 32 ? gt : 31, 13);
         store_col_partial<CW>(red + q * NPAD + col0, lacc, lane);
         lacc = 0.0f;
+        if (owner && warp == 0) {
+            // The others wrote their partials at the start of their runs (or, for an item spread over
+            // three or more CTAs, finish about now): wait, time-bounded, for their flags.
+            bool ok = true;
+            for (int k = lane; k < others; k += 32) {
+                const volatile unsigned long long *f = a.flags + 2 * (static_cast<int>(blockIdx.x) + 1 + k);
+                if (*f != a.tag) {
+                    const uint64_t t0 = globaltimer_ns();
+                    while (*f != a.tag) {
+                        __nanosleep(200);
+                        if (*abort_flag != 0 || globaltimer_ns() - t0 > kWaitLimitNs) {
+                            ok = false;
+                            break;
+                        }
+                    }
+                }
+            }
+            if (!__all_sync(0xffffffffu, ok) && lane == 0) give_up(abort_flag, kStatusEpilogueWait);
+            __threadfence();
+        }
         named_bar_sync(kAllWorkersBar, kWorkerThreads);
         if (tid < NPAD) {
             float l = (red[tid] + red[NPAD + tid]) + (red[2 * NPAD + tid] + red[3 * NPAD + tid]);
-            if (direct) {
+            if (owner) {
+                const float sink_l2 = (a.sink != nullptr && tid < hvalid) ? a.sink[h0 + tid] * kLog2e : -INFINITY;
+                float M = fmaxf(m_s[tid], sink_l2);
+                for (int k = 0; k < others; ++k) {
+                    const float2 e = __ldcg(reinterpret_cast<const float2 *>(a.part_ml) +
+                                            static_cast<long long>(2 * (blockIdx.x + 1 + k)) * NPAD + tid);
+                    if (e.y > 0.0f) M = fmaxf(M, e.x);
+                }
+                const float w_own = fast_exp2(m_s[tid] - M);
+                float denom = w_own * l + fast_exp2(sink_l2 - M);
+                for (int k = 0; k < others; ++k) {
+                    const float2 e = __ldcg(reinterpret_cast<const float2 *>(a.part_ml) +
+                                            static_cast<long long>(2 * (blockIdx.x + 1 + k)) * NPAD + tid);
+                    const float w = e.y > 0.0f ? fast_exp2(e.x - M) : 0.0f;
+                    denom += w * e.y;
+                    wk_s[k * NPAD + tid] = w;
+                }
+                const float inv = 1.0f / denom;
+                alpha_s[tid] = w_own * inv;
+                for (int k = 0; k < others; ++k) wk_s[k * NPAD + tid] *= inv;
+            } else if (direct) {
                 if (a.sink != nullptr && tid < hvalid) l += fast_exp2(a.sink[h0 + tid] * kLog2e - m_s[tid]);
                 alpha_s[tid] = 1.0f / l;
             } else if (tid < hvalid) {
@@ -965,9 +1083,18 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
                     uint32_t o[HR];
                     TmemIO<HR>::ld(tmem_lane + kTmemOCol + c * NPAD + col0 + r * HR, o);
                     const uint32_t dst = stage + (c * 128 + gtid) * 2;
+                    float val[HR];
+#pragma unroll
+                    for (int j = 0; j < HR; ++j) val[j] = __uint_as_float(o[j]) * alpha_s[col0 + r * HR + j];
+                    for (int k = 0; k < others; ++k) {      // un-normalised rows of the item's other segments
+                        const float *src = a.part_o + (static_cast<long long>(2 * (blockIdx.x + 1 + k)) * NPAD + col0 + r * HR) * kD +
+                                           c * 128 + gtid;
+#pragma unroll
+                        for (int j = 0; j < HR; ++j) val[j] = fmaf(wk_s[k * NPAD + col0 + r * HR + j], __ldcg(src + j * kD), val[j]);
+                    }
 #pragma unroll
                     for (int j = 0; j < HR; ++j) {
-                        const __nv_bfloat16 v = __float2bfloat16_rn(__uint_as_float(o[j]) * alpha_s[col0 + r * HR + j]);
+                        const __nv_bfloat16 v = __float2bfloat16_rn(val[j]);
                         asm volatile("st.shared.u16 [%0], %1;" ::"r"(dst + j * 1024), "h"(*reinterpret_cast<const uint16_t *>(&v)) : "memory");
                     }
                 }
@@ -995,6 +1122,10 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
         }
         // Groups 0 and 1 staged in the P buffer, which other groups write in the coming softmax.
         named_bar_sync(kAllWorkersBar, kWorkerThreads);
+        if (a.fused_merge && !direct && tid == 0) {     // this partial is complete: tell the item's owner
+            __threadfence();
+            *reinterpret_cast<volatile unsigned long long *>(a.flags + slot) = a.tag;
+        }
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(bars + kBarOFree * 8);     // the next segment's first PV may overwrite O^T
@@ -1018,7 +1149,7 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
         const volatile int *ng = sched + kSchedRec + 12 * ((k + 1) % 5);
         wait_published(sched, k + 1, abort_flag);
         const bool have_next = (ng[7] & kSegValid) != 0;
-        if (tid == 0 && (sg[7] & kSegOwnsFirst)) {   // this CTA holds the first tiles of an item that continues elsewhere
+        if (tid == 0 && !a.fused_merge && (sg[7] & kSegOwnsFirst)) {   // descriptor for the combine kernel: this CTA holds the first tiles of an item that continues elsewhere
             int4 d;
             d.x = sg[0] * a.head_blocks + sg[1];
             d.y = sg[8] - static_cast<int>(blockIdx.x) + 1;     // CTAs (= partial segments) the item spans
@@ -1173,7 +1304,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const __gri
     SMLA_CTA_MARK(0);
     // ---- this CTA's share of the work
     int *sched = reinterpret_cast<int *>(smem + L::kSched);
-    if (a.balanced && tid == 0) reinterpret_cast<int4 *>(a.desc)[blockIdx.x] = make_int4(-1, 0, 0, 0);
+    if (a.balanced && !a.fused_merge && tid == 0) reinterpret_cast<int4 *>(a.desc)[blockIdx.x] = make_int4(-1, 0, 0, 0);
     if (a.sink != nullptr && tid * 32 < a.H) asm volatile("prefetch.global.L1 [%0];" ::"l"(a.sink + tid * 32));
     {
         SegIter iter;
@@ -1268,68 +1399,9 @@ __global__ void __launch_bounds__(128) sparse_mla_combine_kernel(const float *__
     const int hl = blockIdx.y * 4 + (threadIdx.x >> 5);
     if (d.x < 0 || hl >= d.w) return;
     const int t = d.x / head_blocks, h = (d.x - t * head_blocks) * 64 + hl;
-    const int S = d.y;
     auto slot_of = [&](int k) { return k == 0 ? d.z : 2 * (c + k); };
-    auto ml_of = [&](int k) {
-        return __ldg(reinterpret_cast<const float2 *>(part_ml) + static_cast<long long>(slot_of(k)) * npad + hl);
-    };
-    const float sink_l2 = sink ? sink[h] * kLog2e : -INFINITY;
-    float M = sink_l2;
-    for (int k = lane; k < S; k += 32) {
-        const float2 e = ml_of(k);
-        if (e.y > 0.0f) M = fmaxf(M, e.x);
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
-    float denom = 0.0f;
-    if (M > -INFINITY) {
-        for (int k = lane; k < S; k += 32) {
-            const float2 e = ml_of(k);
-            if (e.y > 0.0f) denom += fast_exp2(e.x - M) * e.y;
-        }
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) denom += __shfl_xor_sync(0xffffffffu, denom, o);
-    if (M > -INFINITY) denom += fast_exp2(sink_l2 - M);
-
-    float acc[16];
-#pragma unroll
-    for (int i = 0; i < 16; ++i) acc[i] = 0.0f;
-    for (int k0 = 0; k0 < S; k0 += 4) {      // four segments at a time: 16 independent 16-byte loads per lane
-        float4 x[4][4];
-        float w[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int k = min(k0 + u, S - 1);
-            const float2 e = ml_of(k);      // the same address in every lane: one broadcast load
-            // empty segments (l == 0) get weight 0; their rows are loaded but never multiplied in
-            w[u] = (k0 + u < S && e.y > 0.0f && M > -INFINITY) ? fast_exp2(e.x - M) : 0.0f;
-            const float4 *src = reinterpret_cast<const float4 *>(part_o) +
-                                (static_cast<long long>(slot_of(k)) * npad + hl) * (kD / 4);
-#pragma unroll
-            for (int v = 0; v < 4; ++v) x[u][v] = __ldg(src + v * 32 + lane);
-        }
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            if (w[u] != 0.0f) {
-#pragma unroll
-                for (int v = 0; v < 4; ++v) {
-                    acc[4 * v] += w[u] * x[u][v].x;
-                    acc[4 * v + 1] += w[u] * x[u][v].y;
-                    acc[4 * v + 2] += w[u] * x[u][v].z;
-                    acc[4 * v + 3] += w[u] * x[u][v].w;
-                }
-            }
-        }
-    }
-    const float inv = denom > 0.0f ? 1.0f / denom : 0.0f;
-    __nv_bfloat16 *dst = out + static_cast<long long>(t) * o_ts + static_cast<long long>(h) * o_hs;
-#pragma unroll
-    for (int v = 0; v < 4; ++v) {
-        const uint2 pk = make_uint2(pack_bf16x2(acc[4 * v] * inv, acc[4 * v + 1] * inv),
-                                    pack_bf16x2(acc[4 * v + 2] * inv, acc[4 * v + 3] * inv));
-        *reinterpret_cast<uint2 *>(dst + (v * 32 + lane) * 4) = pk;
-    }
+    merge_head(part_o, part_ml, slot_of, d.y, npad, hl, sink ? sink[h] * kLog2e : -INFINITY,
+               out + static_cast<long long>(t) * o_ts + static_cast<long long>(h) * o_hs, lane);
 }
 
 // ------------------------------------------------------------------ host side
@@ -1421,6 +1493,16 @@ bool make_q_tensor_map(const KernelArgs &a, int npad, CUtensorMap *map) {
     return r == CUDA_SUCCESS;
 }
 
+// 64-bit value that no earlier launch of this process has used and that memory left over from
+// anything else will not hold: a random start, then steps of an odd constant.
+unsigned long long next_launch_tag() {
+    static std::atomic<unsigned long long> seq{[] {
+        std::random_device rd;
+        return (static_cast<unsigned long long>(rd()) << 32) ^ rd() ^ 0x5851F42D4C957F2Dull;
+    }()};
+    return seq.fetch_add(0x9E3779B97F4A7C15ull) | 1ull;
+}
+
 int sm_count_of_current_device(int &count) {
     static int cached[64] = {};
     int dev = 0;
@@ -1480,13 +1562,20 @@ int launch_sparse_mla_attention(const smla_attn_params_t &p, int num_splits, voi
         if (reinterpret_cast<uintptr_t>(workspace) & 15u) return SMLA_EALIGN;
         const long long bytes = static_cast<long long>(smla_attn_workspace_bytes(p.num_tokens, p.num_heads, num_splits));
         const long long slot_bytes = static_cast<long long>(npad) * (kD + 2) * sizeof(float);
-        ctas = std::min<long long>(sms, (bytes - 16ll * sms) / slot_bytes / 2);
+        ctas = std::min<long long>(sms, (bytes - 64ll * sms) / slot_bytes / 2);
     }
     if (ctas >= 2) {
         a.balanced = 1;
         a.part_o = static_cast<float *>(workspace);
         a.part_ml = a.part_o + static_cast<size_t>(2 * ctas) * npad * kD;
-        a.desc = reinterpret_cast<int *>(a.part_ml + static_cast<size_t>(2 * ctas) * npad * 2);
+        a.desc = reinterpret_cast<int *>(a.part_ml + static_cast<size_t>(2 * ctas) * npad * 2);      // 16 B per CTA
+        a.flags = reinterpret_cast<unsigned long long *>(a.desc + 4 * ctas);                         // 16 B per CTA
+        // With at least a quarter as many items as CTAs an item is cut into a handful of segments
+        // and the CTA that holds its first tiles merges the rest in its epilogue; an item spread over
+        // many CTAs (a few tokens on the whole GPU) is merged by the combine kernel, one warp per head
+        // across all SMs.
+        a.fused_merge = (items * 4 >= ctas && getenv("SMLA_NO_FUSED_MERGE") == nullptr) ? 1 : 0;
+        a.tag = next_launch_tag();
     } else {
         a.balanced = 0;
         ctas = std::min<long long>(items, sms);
@@ -1496,7 +1585,7 @@ int launch_sparse_mla_attention(const smla_attn_params_t &p, int num_splits, voi
     rc = (p.cache_format == SMLA_FP8_DS_MLA) ? launch_fwd_npad<SMLA_FP8_DS_MLA>(npad, a, grid, stream)
                                              : launch_fwd_npad<SMLA_INT8_DS_MLA>(npad, a, grid, stream);
     if (rc != 0) return rc;
-    if (a.balanced) {
+    if (a.balanced && !a.fused_merge) {
         sparse_mla_combine_kernel<<<dim3(grid, static_cast<unsigned>((npad + 3) / 4)), 128, 0, stream>>>(
             a.part_o, a.part_ml, reinterpret_cast<const int4 *>(a.desc), a.sink, a.out, a.o_ts, a.o_hs, a.head_blocks,
             npad);
