@@ -289,7 +289,8 @@ def main():
         kw.update(reps[i % len(reps)])
         return op(**kw)
 
-    # launches per step (claimed): the attention kernel, plus the combine kernel when split
+    # launches per step (claimed): the attention kernel, plus the combine kernel when a few tokens are
+    # spread over the whole GPU (otherwise the merge is fused into the attention kernel)
     from flash_mla import c_abi
     import ctypes
     lib = c_abi.load()
@@ -297,7 +298,10 @@ def main():
     splits = ctypes.c_int(1)
     if kind.startswith("decode"):
         lib.smla_decode_plan(T, H, width, ctypes.byref(splits), None)
-    launches_per_step = 1 + (1 if splits.value > 1 else 0)
+    launches_per_step = 1
+    if kind.startswith("decode"):
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        launches_per_step = lib.smla_decode_kernel_launches(sms, T, H, splits.value)
 
     for i in range(a.warmup):
         step(i)

@@ -81,6 +81,15 @@ size_t smla_attn_workspace_bytes(int num_tokens, int num_heads, int num_splits) 
     return static_cast<size_t>(num_tokens) * num_heads * num_splits * (SMLA_HEAD_DIM + 2) * sizeof(float);
 }
 
+int smla_decode_kernel_launches(int sm_count, int num_tokens, int num_heads, int num_splits) {
+    if (num_splits <= 1 || num_tokens <= 0 || num_heads <= 0) return 1;
+    const long long ctas = smla::balanced_ctas(sm_count, smla::head_pad(num_heads),
+                                               static_cast<long long>(smla_attn_workspace_bytes(num_tokens, num_heads, num_splits)));
+    if (ctas < 2) return 1;
+    const long long items = static_cast<long long>(num_tokens) * ((num_heads + 63) / 64);
+    return smla::fused_merge_policy(items, ctas) ? 1 : 2;
+}
+
 int smla_decode_plan(int num_tokens, int num_heads, int max_width_rows, int *num_splits, size_t *workspace_bytes) {
     DevInfo d;
     const int rc = device_info(d);

@@ -24,4 +24,17 @@ int launch_sparse_mla_attention(const smla_attn_params_t &p, int num_splits, voi
 
 int read_and_clear_device_status(int *status_out);
 
+// CTAs of the balanced schedule for a workspace of `workspace_bytes` (two partial slots of `npad` heads
+// per CTA, 64 bytes of flags and descriptors per SM); fewer than 2 means whole items are dealt out.
+inline long long balanced_ctas(int sm_count, int npad, long long workspace_bytes) {
+    const long long slot_bytes = static_cast<long long>(npad) * (SMLA_HEAD_DIM + 2) * 4;
+    const long long n = (workspace_bytes - 64ll * sm_count) / slot_bytes / 2;
+    return n < sm_count ? n : sm_count;
+}
+// With at least a quarter as many items as CTAs an item is cut into a handful of segments and the CTA
+// that holds its first tiles merges the rest in its epilogue; an item spread over many CTAs (a few
+// tokens on the whole GPU) is merged by the combine kernel, one warp per head across all SMs.
+inline bool fused_merge_policy(long long items, long long ctas) { return items * 4 >= ctas; }
+inline int head_pad(int num_heads) { return num_heads <= 16 ? 16 : (num_heads <= 32 ? 32 : 64); }
+
 }  // namespace smla

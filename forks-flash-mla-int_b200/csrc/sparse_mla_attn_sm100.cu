@@ -1548,7 +1548,7 @@ int launch_sparse_mla_attention(const smla_attn_params_t &p, int num_splits, voi
         rc = fill_stream(p.extra, p.cache_format, a.extra);
         if (rc != SMLA_OK) return rc;
     }
-    const int npad = p.num_heads <= 16 ? 16 : (p.num_heads <= 32 ? 32 : 64);
+    const int npad = head_pad(p.num_heads);
     a.head_blocks = (p.num_heads + 63) / 64;
     const long long items = static_cast<long long>(p.num_tokens) * a.head_blocks;
     if (items > 0x7FFFFFFFLL) return SMLA_ETOOBIG;
@@ -1560,9 +1560,7 @@ int launch_sparse_mla_attention(const smla_attn_params_t &p, int num_splits, voi
     if (num_splits > 1) {
         if (!workspace) return SMLA_EWORKSPACE;
         if (reinterpret_cast<uintptr_t>(workspace) & 15u) return SMLA_EALIGN;
-        const long long bytes = static_cast<long long>(smla_attn_workspace_bytes(p.num_tokens, p.num_heads, num_splits));
-        const long long slot_bytes = static_cast<long long>(npad) * (kD + 2) * sizeof(float);
-        ctas = std::min<long long>(sms, (bytes - 64ll * sms) / slot_bytes / 2);
+        ctas = balanced_ctas(sms, npad, static_cast<long long>(smla_attn_workspace_bytes(p.num_tokens, p.num_heads, num_splits)));
     }
     if (ctas >= 2) {
         a.balanced = 1;
@@ -1570,11 +1568,7 @@ int launch_sparse_mla_attention(const smla_attn_params_t &p, int num_splits, voi
         a.part_ml = a.part_o + static_cast<size_t>(2 * ctas) * npad * kD;
         a.desc = reinterpret_cast<int *>(a.part_ml + static_cast<size_t>(2 * ctas) * npad * 2);      // 16 B per CTA
         a.flags = reinterpret_cast<unsigned long long *>(a.desc + 4 * ctas);                         // 16 B per CTA
-        // With at least a quarter as many items as CTAs an item is cut into a handful of segments
-        // and the CTA that holds its first tiles merges the rest in its epilogue; an item spread over
-        // many CTAs (a few tokens on the whole GPU) is merged by the combine kernel, one warp per head
-        // across all SMs.
-        a.fused_merge = (items * 4 >= ctas && getenv("SMLA_NO_FUSED_MERGE") == nullptr) ? 1 : 0;
+        a.fused_merge = (fused_merge_policy(items, ctas) && getenv("SMLA_NO_FUSED_MERGE") == nullptr) ? 1 : 0;
         a.tag = next_launch_tag();
     } else {
         a.balanced = 0;

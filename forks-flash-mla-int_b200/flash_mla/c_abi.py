@@ -18,7 +18,7 @@ SMLA_ETOOBIG = -5
 
 EXPORTS = (
     "smla_version", "smla_error_string", "smla_choose_num_splits", "smla_attn_workspace_bytes",
-    "smla_decode_plan", "smla_sparse_mla_decode", "smla_sparse_mla_decode_static_scratch", "smla_sparse_mla_prefill",
+    "smla_decode_plan", "smla_decode_kernel_launches", "smla_sparse_mla_decode", "smla_sparse_mla_decode_static_scratch", "smla_sparse_mla_prefill",
     "smla_quantize_int8_ds_mla_rows", "smla_read_device_status",
 )
 
@@ -79,6 +79,8 @@ def load() -> C.CDLL:
     lib.smla_attn_workspace_bytes.restype = C.c_size_t
     lib.smla_attn_workspace_bytes.argtypes = [C.c_int] * 3
     lib.smla_decode_plan.argtypes = [C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_size_t)]
+    lib.smla_decode_kernel_launches.argtypes = [C.c_int] * 4
+    lib.smla_decode_kernel_launches.restype = C.c_int
     lib.smla_sparse_mla_decode.argtypes = [C.POINTER(SmlaAttnParams), C.c_void_p]
     lib.smla_sparse_mla_prefill.argtypes = [C.POINTER(SmlaAttnParams), C.c_void_p]
     lib.smla_sparse_mla_decode_static_scratch.argtypes = [C.POINTER(SmlaAttnParams), C.c_void_p]

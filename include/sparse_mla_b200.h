@@ -109,6 +109,12 @@ SMLA_API size_t smla_attn_workspace_bytes(int num_tokens, int num_heads, int num
  * csrc/flash_api.cpp:381-405 before it allocates oaccum / mlse. */
 SMLA_API int smla_decode_plan(int num_tokens, int num_heads, int max_width, int *num_splits, size_t *workspace_bytes);
 
+/* Kernels one decode call launches on a device with `sm_count` SMs when given `num_splits` and its
+ * workspace: 1 (whole items, or the balanced schedule with the merge fused into the attention kernel)
+ * or 2 (a few tokens spread over the whole GPU: attention kernel + combine kernel).  For accounting
+ * (benchmarks, CUDA-graph node counts); no counterpart in the reference. */
+SMLA_API int smla_decode_kernel_launches(int sm_count, int num_tokens, int num_heads, int num_splits);
+
 /* Sparse MLA decode.  Replaces run_sparse_mla_decode (csrc/flash_mla.h:125,
  * csrc/flash_sparse_mla_decode_sm80.cu:1198-1275) for both cache formats. */
 SMLA_API int smla_sparse_mla_decode(const smla_attn_params_t *params, void *stream);
