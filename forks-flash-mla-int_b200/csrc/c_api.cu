@@ -87,7 +87,7 @@ int smla_decode_kernel_launches(int sm_count, int num_tokens, int num_heads, int
                                                static_cast<long long>(smla_attn_workspace_bytes(num_tokens, num_heads, num_splits)));
     if (ctas < 2) return 1;
     const long long items = static_cast<long long>(num_tokens) * ((num_heads + 63) / 64);
-    return smla::fused_merge_policy(items, ctas) ? 1 : 2;
+    return smla::merge_mode_policy(items, ctas) == 0 ? 2 : 1;
 }
 
 int smla_decode_plan(int num_tokens, int num_heads, int max_width_rows, int *num_splits, size_t *workspace_bytes) {

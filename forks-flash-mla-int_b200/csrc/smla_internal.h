@@ -31,10 +31,17 @@ inline long long balanced_ctas(int sm_count, int npad, long long workspace_bytes
     const long long n = (workspace_bytes - 64ll * sm_count) / slot_bytes / 2;
     return n < sm_count ? n : sm_count;
 }
-// With at least a quarter as many items as CTAs an item is cut into a handful of segments and the CTA
-// that holds its first tiles merges the rest in its epilogue; an item spread over many CTAs (a few
-// tokens on the whole GPU) is merged by the combine kernel, one warp per head across all SMs.
-inline bool fused_merge_policy(long long items, long long ctas) { return items * 4 >= ctas; }
+// How the partial segments of the balanced schedule are merged (measured on B200, int8, 64 heads):
+//   1  at least half as many items as CTAs (an item is cut in two or three): the CTA that holds the
+//      item's first tiles merges the rest in its own epilogue (T=128: 91 us against 98 us);
+//   2  sixteen or more CTAs per item (T <= 8): every CTA of the item merges a slice of its heads at the
+//      end of its run (T=1: 25 against 27 us, T=8: 27 against 30 us);
+//   0  in between: a second kernel, one warp per head on all SMs (T=16..64: equal or 1-4 % better).
+inline int merge_mode_policy(long long items, long long ctas) {
+    if (items * 2 >= ctas) return 1;
+    if (items * 16 <= ctas) return 2;
+    return 0;
+}
 inline int head_pad(int num_heads) { return num_heads <= 16 ? 16 : (num_heads <= 32 ? 32 : 64); }
 
 }  // namespace smla

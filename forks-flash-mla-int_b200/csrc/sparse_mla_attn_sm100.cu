@@ -125,8 +125,9 @@ struct KernelArgs {
     int *desc;       // int4 [CTA] merge descriptors {item, segments, first slot, heads} or {-1} (combine kernel)
     unsigned long long *flags;    // [slot] launch tag once the slot's partial is complete (fused merge)
     unsigned long long tag;       // unique per launch
-    int fused_merge;              // the CTA that holds an item's first tiles merges the other partials in
-                                  // its own epilogue; no second kernel
+    int fused_merge;              // 0: combine kernel; 1: the CTA that holds an item's first tiles merges the
+                                  // other partials in its own epilogue; 2: every CTA of an item merges a
+                                  // slice of its heads at the end of its run
     StreamDev swa, extra;
     int T, H, head_blocks, balanced;
     float scale_log2;
@@ -631,7 +632,8 @@ constexpr int kSchedIter = 64;      // [12]  t, hb, off, item, stride, first, gp
 constexpr int kSchedP = 76;         // [1]   CTAs sharing the tiles
 constexpr int kSchedPub = 77;       // [1]   records published so far
 constexpr int kSchedRec = 80;       // [5][12] t, hb, n, ns, tile0, ntl, slot, flags, last CTA of the item
-constexpr int kSchedInts = kSchedRec + 60;
+constexpr int kSchedFin = kSchedRec + 60;   // [2][5] this CTA's partial segments: {valid, item, first CTA, last CTA, first CTA's slot}
+constexpr int kSchedInts = kSchedFin + 10;
 static_assert(kSchedInts <= 160, "Smem::kSched holds 160 ints");
 constexpr int kSegValid = 4, kSegOwnsFirst = 2, kSegComplete = 1;
 
@@ -689,6 +691,15 @@ __device__ __forceinline__ void publish_segment(const KernelArgs &a, int *sched,
         r[0] = s.t, r[1] = s.hb, r[2] = s.n, r[3] = s.ns, r[4] = s.tile0, r[5] = s.ntl, r[6] = s.slot;
         r[7] = ok ? (kSegValid | (s.owns_first ? kSegOwnsFirst : 0) | (s.complete ? kSegComplete : 0)) : 0;
         r[8] = (ok && s.owns_first) ? cta_of_tile(s.gfirst + s.ntS - 1, W, P) : 0;
+        if (ok && !s.complete && a.fused_merge == 2) {   // at most two per CTA: its first segment (slot 2c), its last (2c + 1)
+            int *f = sched + kSchedFin + 5 * (s.slot & 1);
+            const int c0 = cta_of_tile(s.gfirst, W, P);
+            f[1] = s.t * a.head_blocks + s.hb;
+            f[2] = c0;
+            f[3] = cta_of_tile(s.gfirst + s.ntS - 1, W, P);
+            f[4] = range_begin(c0, W, P) == s.gfirst ? 2 * c0 : 2 * c0 + 1;   // the first CTA's segment of the item
+            f[0] = 1;
+        }
         __threadfence_block();
         reinterpret_cast<volatile int *>(sched)[kSchedPub] = k + 1;
     }
@@ -890,6 +901,55 @@ __device__ __forceinline__ void merge_head(const float *part_o, const float *par
     }
 }
 
+// ------------------------------------------------------------------ slice merge (worker warps, end of the CTA)
+// A few tokens spread over the whole GPU: an item is cut into many segments, one per CTA.  Every segment
+// goes to scratch and raises its flag (the launch's tag).  When a CTA has finished all its tiles it
+// waits, time-bounded, for the flags of all segments of each item it took part in and merges ITS SHARE
+// of the item's heads (CTA j of S: heads [j*H/S, (j+1)*H/S)), so the merge is spread over as many SMs
+// as the item was.  Every CTA has raised all its flags before it waits for anybody's: no cycles.
+template <int NPAD>
+__device__ __forceinline__ void merge_head_slices(const KernelArgs &a, uint8_t *smem, int tid, int warp, int lane) {
+    using L = Smem<NPAD>;
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::kAbort);
+    const volatile int *fin = reinterpret_cast<const volatile int *>(smem + L::kSched) + kSchedFin;
+#pragma unroll 1
+    for (int e = 0; e < 2; ++e) {
+        const volatile int *f = fin + 5 * e;
+        if (f[0] == 0) continue;                                // uniform: shared memory, same for every thread
+        const int item = f[1], c0 = f[2], c1 = f[3], first_slot = f[4];
+        auto slot_of = [&](int k) { return k == 0 ? first_slot : 2 * (c0 + k); };
+        const int S = c1 - c0 + 1;
+        if (warp == 0) {
+            bool ok = true;
+            for (int k = lane; k < S; k += 32) {
+                const volatile unsigned long long *fl = a.flags + slot_of(k);
+                if (*fl != a.tag) {
+                    const uint64_t t0 = globaltimer_ns();
+                    while (*fl != a.tag) {
+                        __nanosleep(100);
+                        if (*abort_flag != 0 || globaltimer_ns() - t0 > kWaitLimitNs) {
+                            ok = false;
+                            break;
+                        }
+                    }
+                }
+            }
+            if (!__all_sync(0xffffffffu, ok) && lane == 0) give_up(abort_flag, kStatusEpilogueWait);
+            __threadfence();
+        }
+        named_bar_sync(kAllWorkersBar, kWorkerThreads);
+        const int t = item / a.head_blocks, h0 = (item - t * a.head_blocks) * 64;
+        const int hvalid = min(NPAD, a.H - h0);
+        const int j = static_cast<int>(blockIdx.x) - c0;
+        const int hbeg = j * hvalid / S, hend = (j + 1) * hvalid / S;
+        for (int hl = hbeg + warp; hl < hend; hl += kWorkerWarps) {
+            const float sink_l2 = a.sink ? a.sink[h0 + hl] * kLog2e : -INFINITY;
+            merge_head(a.part_o, a.part_ml, slot_of, S, NPAD, hl, sink_l2,
+                       a.out + static_cast<long long>(t) * a.o_ts + static_cast<long long>(h0 + hl) * a.o_hs, lane);
+        }
+    }
+}
+
 // ------------------------------------------------------------------ Q-loader warps (17..19)
 // Fetching a 64 KB Q tile takes ~4.5k cycles of load issue; done by the worker warps it sat on the
 // critical path of every segment boundary.  These three warps have nothing else to do: they follow
@@ -1005,7 +1065,7 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
         const int hvalid = min(NPAD, a.H - h0);
         // Fused merge: the segment that holds an item's first tiles (always its CTA's last one) takes
         // the item's other partial segments, slots 2(c+1), 2(c+2), ..., into its own output.
-        const bool owner = a.fused_merge && (pg[7] & kSegOwnsFirst) != 0;
+        const bool owner = a.fused_merge == 1 && (pg[7] & kSegOwnsFirst) != 0;
         const bool direct = (pg[7] & kSegComplete) != 0 || owner;
         const int others = owner ? pg[8] - static_cast<int>(blockIdx.x) : 0;
         float *wk_s = reinterpret_cast<float *>(smem + L::kK);     // [others][NPAD] weights (the K buffer is idle: last segment)
@@ -1292,6 +1352,7 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
             break;
         }
     }
+    if (a.fused_merge == 2) merge_head_slices<NPAD>(a, smem, tid, warp, lane);
 }
 
 // ------------------------------------------------------------------ the kernel
@@ -1305,6 +1366,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const __gri
     // ---- this CTA's share of the work
     int *sched = reinterpret_cast<int *>(smem + L::kSched);
     if (a.balanced && !a.fused_merge && tid == 0) reinterpret_cast<int4 *>(a.desc)[blockIdx.x] = make_int4(-1, 0, 0, 0);
+    if (tid == 0) sched[kSchedFin] = sched[kSchedFin + 5] = 0;
     if (a.sink != nullptr && tid * 32 < a.H) asm volatile("prefetch.global.L1 [%0];" ::"l"(a.sink + tid * 32));
     {
         SegIter iter;
@@ -1568,7 +1630,8 @@ int launch_sparse_mla_attention(const smla_attn_params_t &p, int num_splits, voi
         a.part_ml = a.part_o + static_cast<size_t>(2 * ctas) * npad * kD;
         a.desc = reinterpret_cast<int *>(a.part_ml + static_cast<size_t>(2 * ctas) * npad * 2);      // 16 B per CTA
         a.flags = reinterpret_cast<unsigned long long *>(a.desc + 4 * ctas);                         // 16 B per CTA
-        a.fused_merge = (fused_merge_policy(items, ctas) && getenv("SMLA_NO_FUSED_MERGE") == nullptr) ? 1 : 0;
+        a.fused_merge = merge_mode_policy(items, ctas);
+        if (const char *e = getenv("SMLA_MERGE")) a.fused_merge = atoi(e);     // developer switch: 0 combine kernel, 1, 2
         a.tag = next_launch_tag();
     } else {
         a.balanced = 0;

@@ -111,7 +111,7 @@ SMLA_API int smla_decode_plan(int num_tokens, int num_heads, int max_width, int 
 
 /* Kernels one decode call launches on a device with `sm_count` SMs when given `num_splits` and its
  * workspace: 1 (whole items, or the balanced schedule with the merge fused into the attention kernel)
- * or 2 (a few tokens spread over the whole GPU: attention kernel + combine kernel).  For accounting
+ * or 2 (attention kernel + combine kernel: between ~10 and ~70 items on a 148-SM part).  For accounting
  * (benchmarks, CUDA-graph node counts); no counterpart in the reference. */
 SMLA_API int smla_decode_kernel_launches(int sm_count, int num_tokens, int num_heads, int num_splits);
 
