@@ -190,6 +190,25 @@ __device__ __forceinline__ void tmem_st_x4(uint32_t taddr, const uint32_t (&r)[4
         : "memory");
 }
 
+// A 16-lane x 8-column (32-bit) block in the accumulator-fragment layout: thread T of the warp gets
+// {lane T/4: columns 2(T%4), 2(T%4)+1; lane T/4 + 8: the same two columns}.  The lane field of `taddr`
+// selects the 16-lane half (offset 0 or 16 inside the warp's 32-lane quadrant).  Complete on return.
+__device__ __forceinline__ void tmem_ld_16x256b(uint32_t taddr, uint32_t (&r)[4]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.16x256b.x1.b32 {%0,%1,%2,%3}, [%4];\n\t"
+        "tcgen05.wait::ld.sync.aligned;"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+        : "r"(taddr)
+        : "memory");
+}
+// Four 8x8 matrices of 16-bit elements, registers -> shared memory, each stored TRANSPOSED: register i
+// of thread T holds elements (row T/4, columns 2(T%4), 2(T%4)+1) of matrix i, which land in rows
+// 2(T%4), 2(T%4)+1, column T/4.  Thread 8i + j supplies the address of (16-byte) row j of matrix i.
+__device__ __forceinline__ void stmatrix_x4_trans(uint32_t row_addr, uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3) {
+    asm volatile("stmatrix.sync.aligned.m8n8.x4.trans.shared.b16 [%0], {%1,%2,%3,%4};" ::"r"(row_addr), "r"(r0), "r"(r1),
+                 "r"(r2), "r"(r3)
+                 : "memory");
+}
 // 8 consecutive 32-bit columns of this thread's TMEM lane -> registers, complete on return.
 __device__ __forceinline__ void tmem_ld_x8(uint32_t taddr, uint32_t (&r)[8]) {
     asm volatile(

@@ -1186,6 +1186,12 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
             __threadfence();
             *reinterpret_cast<volatile unsigned long long *>(a.flags + slot) = a.tag;
         }
+        if (owner && tid < others) {
+            // Every read of the other partials is behind the barrier above: lower their flags again.
+            // A launch replayed from a CUDA graph carries the same tag every time, so a flag left up
+            // would let the next replay read a partial that has not been rewritten yet.
+            *reinterpret_cast<volatile unsigned long long *>(a.flags + 2 * (blockIdx.x + 1 + tid)) = 0ull;
+        }
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(bars + kBarOFree * 8);     // the next segment's first PV may overwrite O^T
@@ -1631,6 +1637,12 @@ int launch_sparse_mla_attention(const smla_attn_params_t &p, int num_splits, voi
         a.desc = reinterpret_cast<int *>(a.part_ml + static_cast<size_t>(2 * ctas) * npad * 2);      // 16 B per CTA
         a.flags = reinterpret_cast<unsigned long long *>(a.desc + 4 * ctas);                         // 16 B per CTA
         a.fused_merge = merge_mode_policy(items, ctas);
+        if (a.fused_merge == 2) {
+            // The slice merge relies on the tag being new for every execution; a graph replays the same
+            // arguments, so a capturing stream gets the combine kernel instead.
+            cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+            if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) a.fused_merge = 0;
+        }
         if (const char *e = getenv("SMLA_MERGE")) a.fused_merge = atoi(e);     // developer switch: 0 combine kernel, 1, 2
         a.tag = next_launch_tag();
     } else {

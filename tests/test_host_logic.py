@@ -99,6 +99,14 @@ def test_split_policy_and_workspace():
         assert f(148, 1, 64, 2560) == 11         # at least 512 rows per CTA -> 5 CTAs; read on every call
     finally:
         os.environ.pop("FLASH_MLA_SLOTS_PER_SPLIT")
+    # kernels per decode call: the merge is fused unless ~10..70 items are spread over the SMs
+    k = lib.smla_decode_kernel_launches
+    assert k(148, 128, 64, f(148, 128, 64, 2560)) == 1      # an item cut in two or three: merged in the owner's epilogue
+    assert k(148, 1, 64, f(148, 1, 64, 2560)) == 1          # one token on 20 SMs: every CTA merges a slice of the heads
+    assert k(148, 8, 64, f(148, 8, 64, 2560)) == 1
+    assert k(148, 32, 64, f(148, 32, 64, 2560)) == 2        # in between: attention kernel + combine kernel
+    assert k(148, 1024, 64, 1) == 1                         # whole items, nothing to merge
+    assert k(148, 128, 64, 2) == 1                          # scratch for 62 CTAs only: still two or three segments per item
     w = lib.smla_attn_workspace_bytes
     assert w(4, 64, 1) == 0
     assert w(4, 64, 8) == 4 * 64 * 8 * (512 + 2) * 4
