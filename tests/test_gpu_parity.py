@@ -399,6 +399,42 @@ def test_scores_jump_far_above_the_first_tile(fm):
             assert_attention_close(out, ref, f"score jump {op.__name__}")
 
 
+@pytest.mark.parametrize("T", [96, 4])
+def test_decode_replays_from_a_cuda_graph(fm, T):
+    """The serving engine captures decode in a CUDA graph and replays it with new contents in the same
+    buffers.  A replay repeats the launch arguments exactly, so whatever the kernels use to tell one
+    execution's partial results from the previous one's must not depend on them (T=96: merge fused
+    into the attention kernel; T=4: few tokens spread over the GPU).  Lens change between replays, so
+    the schedule changes too."""
+    rng = np.random.default_rng(2024 + T)
+    torch.manual_seed(2024 + T)
+    H, topk = 64, 704
+    cache, K = fp8_cache_from_latent(_rand_latent(rng, 1024, 1.0), 64)
+    q = torch.randn(T, H, 512, device="cuda").to(torch.bfloat16)
+    idx = torch.randint(0, 1024, (T, topk), dtype=torch.int32, device="cuda")
+    lens = torch.randint(1, topk + 1, (T,), dtype=torch.int32, device="cuda")
+    sink = torch.randn(H, device="cuda")
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            fm.sparse_mla_decode_fp8(q, cache, idx, lens, scale=SCALE, attn_sink=sink)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = fm.sparse_mla_decode_fp8(q, cache, idx, lens, scale=SCALE, attn_sink=sink)
+    for rep in range(4):
+        q.copy_(torch.randn(T, H, 512, device="cuda").to(torch.bfloat16))
+        idx.copy_(torch.randint(0, 1024, (T, topk), dtype=torch.int32, device="cuda"))
+        lens.copy_(torch.randint(1, topk + 1, (T,), dtype=torch.int32, device="cuda"))
+        graph.replay()
+        torch.cuda.synchronize()
+        ref = oracle_out(q, K, idx, lens, scale=SCALE, sink=sink)
+        assert_attention_close(out, ref, f"graph replay {rep}, T={T}")
+    assert device_status() == 0
+
+
 # ----------------------------------------------------------------------------- argument errors
 def test_argument_errors(fm):
     q = torch.randn(2, 64, 512, device="cuda").to(torch.bfloat16)
