@@ -75,6 +75,9 @@ __device__ __forceinline__ unsigned long long smla_globaltimer() {
 namespace {
 
 constexpr int kD = 512;
+// Third value of the kernels' FMT parameter: int8_ds_mla rows that are 16-byte aligned inside 32-byte
+// aligned blocks (the usual 528-byte tokens), gathered with 256-bit loads (see load_row_pieces).
+constexpr int kFmtInt8Wide = 2;
 constexpr int kTileRows = 128;
 constexpr int kWorkerWarps = 16;                 // gather/dequant + softmax + epilogue
 constexpr int kWorkerThreads = kWorkerWarps * 32;
@@ -279,6 +282,7 @@ struct RowRef {
     const uint8_t *ptr;   // first data byte of the row (unused when !ok)
     uint32_t sc0, sc1;    // fp8: the 8 UE8M0 bytes; int8: sc0 = fp32 scale bits
     bool ok;
+    bool odd;  // kFmtInt8Wide: the row starts 16 bytes past a 32-byte boundary
     int vec;   // see StreamDev::vec
 };
 
@@ -295,6 +299,7 @@ __device__ __forceinline__ RowRef<FMT> make_row_ref(const KernelArgs &a, int ns,
     r.sc0 = 0u;
     r.sc1 = 0u;
     r.ok = false;
+    r.odd = false;
     r.vec = 2;
     if (g >= n) return r;
     const StreamDev &s = (g < ns) ? a.swa : a.extra;
@@ -311,6 +316,7 @@ __device__ __forceinline__ RowRef<FMT> make_row_ref(const KernelArgs &a, int ns,
         r.sc1 = sc.y;
     } else {
         r.ptr = blk + static_cast<long long>(i) * s.pos_stride;
+        if constexpr (FMT == kFmtInt8Wide) r.odd = ((reinterpret_cast<uintptr_t>(r.ptr) >> 4) & 1u) != 0;
         r.sc0 = __float_as_uint(__ldg(s.scale + static_cast<long long>(b) * s.scale_block_stride +
                                       static_cast<long long>(i) * s.scale_pos_stride));
     }
@@ -321,11 +327,11 @@ __device__ __forceinline__ RowRef<FMT> make_row_ref(const KernelArgs &a, int ns,
 // int8: 32 pieces).  Lane (row = lane & 7, quarter = lane >> 3) holds in raw[j] the piece
 //   piece16(j, quarter) = 8 * (j / 2) + 2 * quarter + (j & 1)   for j < 8,   32 + quarter for j = 8
 // for fp8 (the "wide" order): raw[2c], raw[2c+1] are 32 contiguous bytes of K-buffer chunk c (dims
-// 128c..128c+127) and are fetched by ONE 256-bit load when the rows are 32-byte aligned: 5 (fp8) / 4 (int8) load instructions
-// per lane and tile instead of 9 / 8.  The count matters more than the bytes: while the tensor pipe
+// 128c..128c+127) and are fetched by ONE 256-bit load when the rows are 32-byte aligned: 5 load
+// instructions per lane and tile instead of 9 (int8 rows: see kFmtInt8Wide).  The count matters more than the bytes: while the tensor pipe
 // streams operands, every load instruction takes ~20 cycles of issue (measured: twice as many loads
 // for the same bytes cost 18 % of the kernel).
-template <int FMT> struct Steps { static constexpr int kCount = (FMT == SMLA_FP8_DS_MLA) ? 9 : 8; };
+template <int FMT> struct Steps { static constexpr int kCount = (FMT == SMLA_INT8_DS_MLA) ? 8 : 9; };
 
 // The order is fixed per cache format at compile time (a run-time choice cost the int8 kernel 10 %):
 // fp8 rows use the wide order (their 576-byte pitch keeps them 32-byte aligned whenever the cache is;
@@ -342,7 +348,20 @@ template <int FMT>
 __device__ __forceinline__ void load_row_pieces(const RowRef<FMT> &r, int quarter, uint4 (&raw)[Steps<FMT>::kCount]) {
     constexpr int J = Steps<FMT>::kCount;
     // Invalid rows are zero rows; the choice is made per load (a select, no divergent branch).
-    if (FMT == SMLA_FP8_DS_MLA && r.vec == 2) {
+    if constexpr (FMT == kFmtInt8Wide) {
+        // 512 data bytes from a 16-byte aligned address: an even row is 16 aligned 32-byte windows; an
+        // odd row is fetched from 16 bytes earlier (the tail of the token before it, readable), so
+        // that its windows are aligned too: raw[2c] is then piece 8c + 2q - 1 and raw[2c + 1] piece
+        // 8c + 2q, and the last piece, 31, comes with one 16-byte load in lane quarter 0.
+        const uint8_t *base = r.ptr - (r.odd ? 16 : 0);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            if (r.ok) ldg_nc_v8(base + 128 * c + 32 * quarter, raw[2 * c], raw[2 * c + 1]);
+            else raw[2 * c] = raw[2 * c + 1] = make_uint4(0u, 0u, 0u, 0u);
+        }
+        if (r.ok && r.odd && quarter == 0) raw[8] = ldg_nc_v4(r.ptr + 496);
+        else raw[8] = make_uint4(0u, 0u, 0u, 0u);
+    } else if (FMT == SMLA_FP8_DS_MLA && r.vec == 2) {
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
             if (r.ok) ldg_nc_v8(r.ptr + 128 * c + 32 * quarter, raw[2 * c], raw[2 * c + 1]);
@@ -359,20 +378,25 @@ __device__ __forceinline__ void load_row_pieces(const RowRef<FMT> &r, int quarte
     }
 }
 
+// 16 int8 values (piece p16 of the row) -> bf16(value * scale), two core-matrix rows of the K buffer.
+__device__ __forceinline__ void convert_int8_piece(const uint4 &raw, uint32_t p16, float s, uint32_t k_row_addr) {
+    uint32_t o[8];
+    cvt_i8x4(raw.x, s, o[0], o[1]);
+    cvt_i8x4(raw.y, s, o[2], o[3]);
+    cvt_i8x4(raw.z, s, o[4], o[5]);
+    cvt_i8x4(raw.w, s, o[6], o[7]);
+    const uint32_t dg = 2u * p16;
+    st_shared_v4(k_row_addr + dg * kCoreBytes, o[0], o[1], o[2], o[3]);
+    st_shared_v4(k_row_addr + (dg + 1u) * kCoreBytes, o[4], o[5], o[6], o[7]);
+}
+
 template <int FMT>
 __device__ __forceinline__ void convert_step(const uint4 &raw, int j, int quarter, uint32_t sc0, uint32_t sc1,
                                              uint32_t k_row_addr /* K + rg*8192 + (lane&7)*16 */) {
     uint32_t o[8];
     const uint32_t p16 = static_cast<uint32_t>(piece16<FMT>(j, quarter));
     if constexpr (FMT == SMLA_INT8_DS_MLA) {
-        const float s = __uint_as_float(sc0);
-        cvt_i8x4(raw.x, s, o[0], o[1]);
-        cvt_i8x4(raw.y, s, o[2], o[3]);
-        cvt_i8x4(raw.z, s, o[4], o[5]);
-        cvt_i8x4(raw.w, s, o[6], o[7]);
-        const uint32_t dg = 2u * p16;
-        st_shared_v4(k_row_addr + dg * kCoreBytes, o[0], o[1], o[2], o[3]);
-        st_shared_v4(k_row_addr + (dg + 1u) * kCoreBytes, o[4], o[5], o[6], o[7]);
+        convert_int8_piece(raw, p16, __uint_as_float(sc0), k_row_addr);
     } else {
         if (p16 < 28u) {     // 16 e4m3 values of scale tile p16 / 4
             const uint32_t tile = p16 >> 2;
@@ -1239,10 +1263,22 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
             for (int c = 0; c < 4; ++c) {
                 if (gt > 0) warp_wait(bars + (kBarFree + c) * 8, (gt - 1) & 1, abort_flag, lane, kStatusGatherWait);
                 if (tracer && c == 0) SMLA_MARK(gt, 7);
+                if constexpr (FMT == kFmtInt8Wide) {
+                    // chunk c = pieces 8c .. 8c+7 of the row; which registers hold them depends on the
+                    // row's alignment (see load_row_pieces)
+                    const bool q0 = cur.odd && quarter == 0;
+                    const uint4 &next_first = raw[c < 3 ? 2 * c + 2 : 8];
+                    const uint4 x = q0 ? next_first : raw[2 * c];
+                    const uint32_t px = cur.odd ? (quarter == 0 ? 8u * c + 7u : 8u * c + 2u * quarter - 1u) : 8u * c + 2u * quarter;
+                    const uint32_t py = cur.odd ? 8u * c + 2u * quarter : 8u * c + 2u * quarter + 1u;
+                    convert_int8_piece(x, px, __uint_as_float(cur.sc0), k_row_addr);
+                    convert_int8_piece(raw[2 * c + 1], py, __uint_as_float(cur.sc0), k_row_addr);
+                } else {
 #pragma unroll
-                for (int j = 0; j < J; ++j) {
-                    const bool mine = (j < 8) ? ((j >> 1) == c) : (c == 3);
-                    if (mine) convert_step<FMT>(raw[j], j, quarter, cur.sc0, cur.sc1, k_row_addr);
+                    for (int j = 0; j < J; ++j) {
+                        const bool mine = (j < 8) ? ((j >> 1) == c) : (c == 3);
+                        if (mine) convert_step<FMT>(raw[j], j, quarter, cur.sc0, cur.sc1, k_row_addr);
+                    }
                 }
                 if (tracer && (c == 0 || c == 3)) SMLA_MARK(gt, 8 + c);
                 fence_async_smem();
@@ -1496,8 +1532,12 @@ int fill_stream(const smla_stream_t &s, int fmt, StreamDev &d) {
     } else {
         if (!s.scale) return SMLA_EINVAL;
         if ((base & 3u) || (s.block_stride & 3) || (s.pos_stride & 3)) return SMLA_EALIGN;
-        d.vec = ((base & 31u) == 0 && (s.block_stride & 31) == 0 && (s.pos_stride & 31) == 0) ? 2
-                : ((base & 15u) == 0 && (s.block_stride & 15) == 0 && (s.pos_stride & 15) == 0) ? 1 : 0;
+        // 2: every row starts on a 16-byte boundary inside 32-byte aligned blocks and is followed by at
+        // least 16 readable bytes of its own token (528-byte tokens, or 512-byte rows that are 32-byte
+        // aligned): the wide gather (kFmtInt8Wide) applies.
+        const bool wide = (base & 31u) == 0 && (s.block_stride & 31) == 0 && (s.pos_stride & 15) == 0 &&
+                          ((s.pos_stride & 31) == 0 || s.pos_stride >= 528);
+        d.vec = wide ? 2 : ((base & 15u) == 0 && (s.block_stride & 15) == 0 && (s.pos_stride & 15) == 0) ? 1 : 0;
     }
     return SMLA_OK;
 }
@@ -1651,7 +1691,10 @@ int launch_sparse_mla_attention(const smla_attn_params_t &p, int num_splits, voi
     }
     a.q_tma = make_q_tensor_map(a, npad, &a.q_map) ? 1 : 0;
     const unsigned grid = static_cast<unsigned>(ctas);
+    const bool int8_wide = p.cache_format == SMLA_INT8_DS_MLA && a.swa.vec == 2 &&
+                           (p.extra.cache == nullptr || a.extra.vec == 2) && getenv("SMLA_NO_WIDE_INT8") == nullptr;
     rc = (p.cache_format == SMLA_FP8_DS_MLA) ? launch_fwd_npad<SMLA_FP8_DS_MLA>(npad, a, grid, stream)
+         : int8_wide                         ? launch_fwd_npad<kFmtInt8Wide>(npad, a, grid, stream)
                                              : launch_fwd_npad<SMLA_INT8_DS_MLA>(npad, a, grid, stream);
     if (rc != 0) return rc;
     if (a.balanced && !a.fused_merge) {
