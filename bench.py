@@ -401,8 +401,21 @@ def main():
             err = np.abs(got - ref[:n])
             line["cpu_baseline"] = {"value": n / dt, "unit": "tokens/s", "cores": cores, "kind": "port",
                                     "sample": f"first {n} of {T} tokens of the same step; caches dequantised once outside the timed region"}
+            # the same gate as tests/helpers.py: elementwise atol 2e-2 + rtol 2e-2 + one bf16 quantum of the
+            # row (outputs of the x50 outlier rows reach |out| ~ 160, where bf16 rounding alone is 0.5),
+            # mean-abs 2e-3 + 2^-8 mean|ref|, and the reference's cos_diff < 8e-5
+            r = ref[:n]
+            excess = float((err - (2e-2 + 2e-2 * np.abs(r) + 2.0 ** -7 * np.abs(r).max(-1, keepdims=True))).max())
+            mean_bound = 2e-3 + 2.0 ** -8 * float(np.abs(r).mean())
+            num = 2.0 * float((got.astype(np.float64) * r.astype(np.float64)).sum())
+            den = float((got.astype(np.float64) ** 2).sum() + (r.astype(np.float64) ** 2).sum())
+            cos_diff = 1.0 - num / max(den, 1e-300)
             line["parity"] = {"tokens_checked": n, "max_abs": float(err.max()), "mean_abs": float(err.mean()),
-                              "tolerance": {"max_abs": 2e-2, "mean_abs": 2e-3}}
+                              "max_abs_ref": float(np.abs(r).max()), "cos_diff": cos_diff,
+                              "within_gate": bool(excess <= 0 and float(err.mean()) <= mean_bound and cos_diff < 8e-5),
+                              "gate": "|d| <= 2e-2 + 2e-2|ref| + 2^-7 rowmax|ref|; mean|d| <= 2e-3 + 2^-8 mean|ref|; cos_diff < 8e-5",
+                              "north_star_abs": {"max_abs": 2e-2, "mean_abs": 2e-3,
+                                                 "met": bool(err.max() <= 2e-2 and err.mean() <= 2e-3)}}
         print(json.dumps(line))
     if world > 1:
         dist.barrier()
