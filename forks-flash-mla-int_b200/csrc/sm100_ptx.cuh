@@ -1,7 +1,7 @@
 // Thin inline-PTX wrappers for the sm_100a features the sparse-MLA kernels use:
 // mbarrier (with time-bounded waits), tcgen05 tensor-memory allocation, tcgen05.mma with
-// shared-memory matrix descriptors, tcgen05.ld/st, proxy fences, named barriers.
-// Single-CTA (cta_group::1) forms only; no cluster multicast anywhere.
+// shared-memory matrix descriptors, tcgen05.ld/st, one TMA tiled tensor load, cp.async, proxy fences,
+// named barriers.  Single-CTA (cta_group::1) forms only; every copy lands in the issuing CTA.
 #pragma once
 #include <cstdint>
 #include <cuda_runtime.h>
