@@ -8,7 +8,7 @@
 // (tests/test_sparse_mla_prefill_adversarial.py:25-53): invalid slot ids are zero rows that stay
 // in the softmax, positions >= lens are excluded, attn_sink joins the denominator once.
 //
-// Orientation.  One CTA owns one (token, block of <= 64 heads[, split]).  The selected rows are
+// Orientation.  The work is a list of items (token, block of <= 64 heads).  The selected rows are
 // the MMA M dimension, 128 per tile:
 //     S^T[128 rows, N heads]   = K_tile[128, 512] . Q[N, 512]^T         (A, B both K-major)
 //     O^T[512 dims, N heads]  += K_tile^T[512, 128] . P^T[128, N]       (A, B both MN-major)
@@ -16,14 +16,20 @@
 // serves both products: it is stored as 8x16-byte core matrices (8 rows x 8 dims) which a
 // no-swizzle descriptor can walk row-group-first (K-major) or dim-group-first (MN-major).
 //
-// Roles (544 threads, no register rebalancing: setmaxnreg.inc can block without any time limit).
-// Warps 0-15 are workers that alternate between two jobs: (1) convert -- warp w owns rows 8w..8w+7
-// of the tile, keeps their raw bytes for the NEXT tile in registers (16-byte loads issued a tile
-// ahead) and writes them as bf16 into the single K buffer chunk by chunk (128 dims), each chunk as
-// soon as the previous tile's PV has released it; (2) softmax -- warp w owns TMEM lanes
-// 32*(w%4).. and head columns (N/4)*(w/4)..: S^T -> P^T with a lazily moved, integer-valued
-// reference max, running denominators, and the epilogue.  Warp 16 allocates TMEM and its lane 0
-// issues every tcgen05.mma.
+// Schedule.  The grid is persistent (at most one CTA per SM).  Either whole items are dealt out to
+// the CTAs, or -- when there are few items or their lengths differ -- the 128-row tiles of all items
+// are cut into equal contiguous ranges, one per CTA; the pieces of an item that was cut are merged
+// inside this kernel (by the CTA that holds the item's first tiles, or slice-wise by all CTAs of the
+// item) or by a small second kernel; see "work distribution" below.
+//
+// Roles (640 threads, no register rebalancing).  Warps 0-15 are workers that alternate between two
+// jobs: (1) convert -- warp w owns rows 8w..8w+7 of the tile, keeps their raw bytes for the NEXT
+// tile in registers (256-bit loads issued a tile ahead) and writes them as bf16 into the single K
+// buffer chunk by chunk (128 dims), each chunk as soon as the previous tile's PV has released it;
+// (2) softmax -- warp w owns TMEM lanes 32*(w%4).. and head columns (N/4)*(w/4)..: S^T -> P^T with a
+// lazily moved, integer-valued reference max, running denominators, and the epilogue.  Warp 16
+// allocates TMEM and its lane 0 issues every tcgen05.mma; warp 17 fetches each item's Q tile (one TMA
+// tensor copy); warp 18 publishes the CTA's segments into a ring in shared memory.
 //
 // Every spin is time-bounded; a wait that runs out sets a bit in the device status word and the
 // CTA leaves through the normal teardown.
