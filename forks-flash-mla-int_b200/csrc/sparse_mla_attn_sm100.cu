@@ -47,6 +47,7 @@
 #include <algorithm>
 #include <atomic>
 #include <random>
+#include <type_traits>
 
 #include "smla_internal.h"
 
@@ -1089,13 +1090,14 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
     // not touch the K or Q buffers: the final output is turned round (a thread holds one dim of CW
     // heads, a row of `out` is one head's 512 dims) through a small staging area per column-slice
     // group, HR heads at a time, so that global stores are 16 bytes per thread and 1 KB per head.
-    auto epilogue = [&](const volatile int *pg, const volatile int *cg, int parity) {
+    auto epilogue = [&](auto final_tag, const volatile int *pg, const volatile int *cg, int parity) {
+        constexpr bool kFinal = decltype(final_tag)::value;      // the CTA's last epilogue (only there can it own an item)
         constexpr int HR = CW < 8 ? CW : 8;     // heads per staging round
         const int t = pg[0], h0 = pg[1] * 64, slot = pg[6];
         const int hvalid = min(NPAD, a.H - h0);
         // Fused merge: the segment that holds an item's first tiles (always its CTA's last one) takes
         // the item's other partial segments, slots 2(c+1), 2(c+2), ..., into its own output.
-        const bool owner = a.fused_merge == 1 && (pg[7] & kSegOwnsFirst) != 0;
+        const bool owner = kFinal && a.fused_merge == 1 && (pg[7] & kSegOwnsFirst) != 0;
         const bool direct = (pg[7] & kSegComplete) != 0 || owner;
         const int others = owner ? pg[8] - static_cast<int>(blockIdx.x) : 0;
         float *wk_s = reinterpret_cast<float *>(smem + L::kK);     // [others][NPAD] weights (the K buffer is idle: last segment)
@@ -1168,7 +1170,20 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
             __nv_bfloat16 *orow = a.out + static_cast<long long>(t) * a.o_ts + static_cast<long long>(h0 + col0) * a.o_hs;
 #pragma unroll 1
             for (int r = 0; r < CW / HR; ++r) {
-#pragma unroll 1
+                // Owner: the first other segment's rows of this round are fetched for all four chunks at
+                // once (this is the CTA's last epilogue: the gather registers are free), so that their
+                // latency is paid once per round and not once per chunk.
+                float pv[kFinal ? 4 : 1][HR];
+                if constexpr (kFinal) {
+                    if (owner) {
+                        const float *src = a.part_o + (static_cast<long long>(2 * (blockIdx.x + 1)) * NPAD + col0 + r * HR) * kD + gtid;
+#pragma unroll
+                        for (int c = 0; c < 4; ++c)
+#pragma unroll
+                            for (int j = 0; j < HR; ++j) pv[c][j] = __ldcg(src + c * 128 + j * kD);
+                    }
+                }
+#pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     uint32_t o[HR];
                     TmemIO<HR>::ld(tmem_lane + kTmemOCol + c * NPAD + col0 + r * HR, o);
@@ -1176,11 +1191,17 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
                     float val[HR];
 #pragma unroll
                     for (int j = 0; j < HR; ++j) val[j] = __uint_as_float(o[j]) * alpha_s[col0 + r * HR + j];
-                    for (int k = 0; k < others; ++k) {      // un-normalised rows of the item's other segments
-                        const float *src = a.part_o + (static_cast<long long>(2 * (blockIdx.x + 1 + k)) * NPAD + col0 + r * HR) * kD +
-                                           c * 128 + gtid;
+                    if constexpr (kFinal) {
+                        if (owner) {
 #pragma unroll
-                        for (int j = 0; j < HR; ++j) val[j] = fmaf(wk_s[k * NPAD + col0 + r * HR + j], __ldcg(src + j * kD), val[j]);
+                            for (int j = 0; j < HR; ++j) val[j] = fmaf(wk_s[col0 + r * HR + j], pv[c][j], val[j]);
+                        }
+                        for (int k = 1; k < others; ++k) {      // un-normalised rows of the item's further segments
+                            const float *src = a.part_o + (static_cast<long long>(2 * (blockIdx.x + 1 + k)) * NPAD + col0 + r * HR) * kD +
+                                               c * 128 + gtid;
+#pragma unroll
+                            for (int j = 0; j < HR; ++j) val[j] = fmaf(wk_s[k * NPAD + col0 + r * HR + j], __ldcg(src + j * kD), val[j]);
+                        }
                     }
 #pragma unroll
                     for (int j = 0; j < HR; ++j) {
@@ -1302,7 +1323,7 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
             g = g_next;
 
             // ---- the previous segment's epilogue, while the tensor pipe computes this tile's QK^T
-            if (first_tile && k > 0) epilogue(sched + kSchedRec + 12 * ((k - 1) % 5), sg, (k - 1) & 1);
+            if (first_tile && k > 0) epilogue(std::false_type{}, sched + kSchedRec + 12 * ((k - 1) % 5), sg, (k - 1) & 1);
 
             // ---- softmax of this tile
             warp_wait(bars + kBarS * 8, gt & 1, abort_flag, lane, kStatusSoftmaxWait);
@@ -1396,7 +1417,7 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
 
         // ---- end of the segment; its epilogue is run inside the next segment's first tile
         if (!have_next) {
-            epilogue(sg, nullptr, k & 1);
+            epilogue(std::true_type{}, sg, nullptr, k & 1);
             break;
         }
     }
