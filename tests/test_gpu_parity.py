@@ -435,6 +435,40 @@ def test_decode_replays_from_a_cuda_graph(fm, T):
     assert device_status() == 0
 
 
+@pytest.mark.parametrize("T", [150, 3])
+def test_merges_inside_the_kernel_are_repeatable(fm, T):
+    """Partial segments are handed between CTAs through flags in scratch (T=150: to the CTA that owns
+    the item; T=3: to every CTA of the item).  A partial read before it was complete would change with
+    timing: sixty launches on the same inputs, reusing one scratch buffer, must give identical bits."""
+    from flash_mla import c_abi
+    rng = np.random.default_rng(7 + T)
+    torch.manual_seed(7 + T)
+    H, topk = 64, 1500
+    cache, K = fp8_cache_from_latent(_rand_latent(rng, 2048, 1.0), 64)
+    q = torch.randn(T, H, 512, device="cuda").to(torch.bfloat16)
+    idx = torch.randint(0, 2048, (T, topk), dtype=torch.int32, device="cuda")
+    lens = torch.randint(topk // 2, topk + 1, (T,), dtype=torch.int32, device="cuda")
+    sink = torch.randn(H, device="cuda")
+    lib = c_abi.load()
+    splits = lib.smla_choose_num_splits(torch.cuda.get_device_properties(0).multi_processor_count, T, H, topk)
+    assert splits > 1
+    ws = torch.empty(lib.smla_attn_workspace_bytes(T, H, splits) // 4 + 4, dtype=torch.float32, device="cuda")
+    outs = []
+    for rep in range(60):
+        out = torch.empty_like(q)
+        p = c_abi.attn_params(q, out, c_abi.SMLA_FP8_DS_MLA, SCALE, c_abi.stream_from_tensors(cache, None, idx, lens),
+                              None, sink, num_splits=splits, workspace=ws)
+        c_abi.check(lib.smla_sparse_mla_decode(p, torch.cuda.current_stream().cuda_stream))
+        outs.append(out)
+    torch.cuda.synchronize()
+    for rep in range(1, 60):
+        assert torch.equal(outs[rep], outs[0]), f"launch {rep} differs from launch 0"
+    n = min(T, 6)      # parity on the first tokens (the oracle is slow at 1500 rows x 64 heads)
+    ref = oracle_out(q[:n], K, idx[:n], lens[:n], scale=SCALE, sink=sink)
+    assert_attention_close(outs[0][:n], ref, f"T={T}")
+    assert device_status() == 0
+
+
 # ----------------------------------------------------------------------------- argument errors
 def test_argument_errors(fm):
     q = torch.randn(2, 64, 512, device="cuda").to(torch.bfloat16)
