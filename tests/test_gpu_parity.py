@@ -469,6 +469,29 @@ def test_merges_inside_the_kernel_are_repeatable(fm, T):
     assert device_status() == 0
 
 
+@pytest.mark.parametrize("H", [4, 20, 72])
+def test_head_counts_that_are_not_multiples_of_eight_or_sixty_four(fm, H):
+    """H=4 and H=20 cannot use the TMA view of q (its head groups are 8 wide) and take the cp.async Q
+    loaders; H=72 has a second head block of 8 heads.  Both cache formats, split and unsplit."""
+    rng = np.random.default_rng(300 + H)
+    torch.manual_seed(300 + H)
+    T, topk = 9, 600
+    lat = _rand_latent(rng, 1024, 1.0)
+    cache, Kf = fp8_cache_from_latent(lat, 64)
+    sq, ss, Ki, _ = int8_cache_from_latent(lat, 64, "inline528")
+    q = torch.randn(T, H, 512, device="cuda").to(torch.bfloat16)
+    idx = torch.randint(0, 1024, (T, topk), dtype=torch.int32, device="cuda")
+    lens = torch.randint(1, topk + 1, (T,), dtype=torch.int32, device="cuda")
+    sink = torch.randn(H, device="cuda")
+    ref_f = oracle_out(q, Kf, idx, lens, scale=SCALE, sink=sink)
+    ref_i = oracle_out(q, Ki, idx, lens, scale=SCALE, sink=sink)
+    assert_attention_close(fm.sparse_mla_decode_fp8(q, cache, idx, lens, scale=SCALE, attn_sink=sink), ref_f, f"fp8 decode H={H}")
+    assert_attention_close(fm.sparse_mla_prefill(q, cache, idx, lens, scale=SCALE, attn_sink=sink), ref_f, f"fp8 prefill H={H}")
+    assert_attention_close(fm.sparse_mla_decode_int8(q, sq, ss, idx, lens, scale=SCALE, attn_sink=sink), ref_i, f"int8 decode H={H}")
+    assert_attention_close(fm.sparse_mla_prefill_int8(q, sq, ss, idx, lens, scale=SCALE, attn_sink=sink), ref_i, f"int8 prefill H={H}")
+    assert device_status() == 0
+
+
 # ----------------------------------------------------------------------------- argument errors
 def test_argument_errors(fm):
     q = torch.randn(2, 64, 512, device="cuda").to(torch.bfloat16)
