@@ -662,6 +662,7 @@ constexpr int kSchedScan = 0;       // [64]  scratch of make_schedule
 constexpr int kSchedIter = 64;      // [12]  t, hb, off, item, stride, first, gpos(2), rem(2), W(2)
 constexpr int kSchedP = 76;         // [1]   CTAs sharing the tiles
 constexpr int kSchedPub = 77;       // [1]   records published so far
+constexpr int kSchedTiles = 78;     // [1]   tiles whose S^T has been scored (written by the MMA thread)
 constexpr int kSchedRec = 80;       // [5][12] t, hb, n, ns, tile0, ntl, slot, flags, last CTA of the item
 constexpr int kSchedFin = kSchedRec + 60;   // [2][5] this CTA's partial segments: {valid, item, first CTA, last CTA, first CTA's slot}
 constexpr int kSchedInts = kSchedFin + 10;
@@ -735,6 +736,31 @@ __device__ __forceinline__ void publish_segment(const KernelArgs &a, int *sched,
         reinterpret_cast<volatile int *>(sched)[kSchedPub] = k + 1;
     }
     __syncwarp();
+}
+
+// The following warps wait until `count` tiles of this CTA have been scored (QK^T complete, softmax
+// done).  Lane 0 polls, the result is broadcast; time-bounded.
+__device__ __forceinline__ bool wait_tiles(const int *sched, int count, volatile int *abort_flag, int lane) {
+    int ok = 1;
+    if (lane == 0) {
+        const volatile int *done = reinterpret_cast<const volatile int *>(sched) + kSchedTiles;
+        if (*done < count) {
+            const uint64_t t0 = globaltimer_ns();
+            while (*done < count) {
+                __nanosleep(64);
+                if (*abort_flag != 0) {
+                    ok = 0;
+                    break;
+                }
+                if (globaltimer_ns() - t0 > kWaitLimitNs) {
+                    give_up(abort_flag, kStatusSoftmaxWait);
+                    ok = 0;
+                    break;
+                }
+            }
+        }
+    }
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
 // Readers call this before they look at record k.  In practice it never waits (records are three
@@ -814,6 +840,9 @@ __device__ __forceinline__ void mma_role(uint8_t *smem, uint32_t tmem_base) {
                 give_up(abort_flag, kStatusMmaWait);
                 return;
             }
+            // Progress for the warps that only follow (Q loader, scheduler): a count cannot be missed
+            // the way an mbarrier phase can by a waiter that falls two phases behind.
+            reinterpret_cast<volatile int *>(smem + L::kSched)[kSchedTiles] = gt + 1;
             // The first PV of a segment overwrites O^T: the previous segment's epilogue must have read it.
             if (it == 0 && so > 0 && !mbar_wait(bars + kBarOFree * 8, (so - 1) & 1, abort_flag)) {
                 give_up(abort_flag, kStatusMmaWait);
@@ -1014,9 +1043,8 @@ __device__ __forceinline__ void qload_role(const KernelArgs &a, uint8_t *smem, i
             __syncwarp();
             if (lane == 0) mbar_arrive(bars + kBarQ * 8);
         }
-        const int ntl = rec[5];
-        for (int it = 0; it < ntl; ++it, ++gt)
-            if (!warp_wait(bars + kBarS * 8, gt & 1, abort_flag, lane, kStatusSoftmaxWait)) return;
+        gt += rec[5];      // the Q buffer is free again when the segment's last tile has been scored
+        if (!wait_tiles(reinterpret_cast<const int *>(smem + L::kSched), gt, abort_flag, lane)) return;
     }
 }
 
@@ -1036,10 +1064,9 @@ __device__ __forceinline__ void scheduler_role(const KernelArgs &a, uint8_t *sme
         const volatile int *rec = sched + kSchedRec + 12 * (s % 5);
         if ((rec[7] & kSegValid) == 0) break;
         const int ntl = rec[5];
-        for (int it = 0; it < ntl; ++it, ++gt) {
-            if (!warp_wait(bars + kBarS * 8, gt & 1, abort_flag, lane, kStatusSoftmaxWait)) return;
-            if (it == 0 && s >= 2) publish_segment(a, sched, s + 3, lane);
-        }
+        if (!wait_tiles(sched, gt + 1, abort_flag, lane)) return;      // first tile of segment s scored
+        if (s >= 2) publish_segment(a, sched, s + 3, lane);
+        gt += ntl;
     }
 }
 
@@ -1461,6 +1488,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const __gri
         mbar_init(bars + kBarOFree * 8, kWorkerWarps);
         mbar_init(bars + kBarQ * 8, a.q_tma ? 1 : kQLoadWarps);
         *reinterpret_cast<volatile int *>(smem + L::kAbort) = 0;
+        sched[kSchedTiles] = 0;
         mbar_init_fence();
     }
     if (warp == kMmaWarp) {
