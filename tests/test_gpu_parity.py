@@ -492,6 +492,59 @@ def test_head_counts_that_are_not_multiples_of_eight_or_sixty_four(fm, H):
     assert device_status() == 0
 
 
+@pytest.mark.parametrize("seed", [101, 102])
+def test_random_small_problems_match_the_oracle(fm, seed):
+    """Forty random small problems per seed through all four operators: 1..128 heads (also counts that are
+    not multiples of 8), top-k 1..513 with and without the extra stream, block sizes 16..256, both int8
+    layouts, strided q, slot ids from -1 to past the end, lens from 0."""
+    rng = np.random.default_rng(seed)
+    torch.manual_seed(seed)
+    for it in range(40):
+        T = int(rng.choice([1, 2, 3, 7, 12, 33]))
+        H = int(rng.choice([1, 4, 8, 20, 32, 64, 72, 128]))
+        st = int(rng.choice([1, 17, 128, 129, 300]))
+        et = int(rng.choice([0, 0, 5, 200, 513]))
+        bs_s, bs_e = int(rng.choice([16, 64, 256])), int(rng.choice([16, 64]))
+        slots_s = ((max(st, 64) * 2 + bs_s - 1) // bs_s) * bs_s
+        slots_e = ((max(et, 64) * 2 + bs_e - 1) // bs_e) * bs_e
+        lat_s = (rng.standard_normal((slots_s, 512)) * rng.choice([0.3, 1.0, 3.0])).astype(np.float32)
+        lat_e = rng.standard_normal((slots_e, 512)).astype(np.float32)
+        fmt, layout = str(rng.choice(["fp8", "int8"])), str(rng.choice(["inline528", "separate"]))
+        q = torch.randn(T, H + 3, 512, device="cuda").to(torch.bfloat16)[:, :H]
+        if rng.integers(2):
+            q = q.contiguous()
+        si = torch.randint(-1, slots_s + 2, (T, st), dtype=torch.int32, device="cuda")
+        sl = torch.randint(0, st + 1, (T,), dtype=torch.int32, device="cuda")
+        sink = torch.randn(H, device="cuda") if rng.integers(2) else None
+        extra = {}
+        if fmt == "fp8":
+            sc, sK = fp8_cache_from_latent(lat_s, bs_s)
+            args = (q, sc, si, sl)
+            if et:
+                ec, eK = fp8_cache_from_latent(lat_e, bs_e)
+                extra = dict(extra_cache=ec)
+            ops = (fm.sparse_mla_decode_fp8, fm.sparse_mla_prefill)
+        else:
+            sc, ss, sK, _k1 = int8_cache_from_latent(lat_s, bs_s, layout)
+            args = (q, sc, ss, si, sl)
+            if et:
+                ec, es, eK, _k2 = int8_cache_from_latent(lat_e, bs_e, layout)
+                extra = dict(extra_cache=ec, extra_scale=es)
+            ops = (fm.sparse_mla_decode_int8, fm.sparse_mla_prefill_int8)
+        if et:
+            ei = torch.randint(-1, slots_e + 2, (T, et), dtype=torch.int32, device="cuda")
+            el = torch.randint(0, et + 1, (T,), dtype=torch.int32, device="cuda")
+            extra.update(extra_indices=ei, extra_lens=el)
+            ref = oracle_out(q, sK, si, sl, eK, ei, el, scale=SCALE, sink=sink)
+        else:
+            ref = oracle_out(q, sK, si, sl, scale=SCALE, sink=sink)
+        for op in ops:
+            out = op(*args, scale=SCALE, attn_sink=sink, **extra)
+            assert_attention_close(out, ref, f"seed {seed} case {it}: {op.__name__} T={T} H={H} swa {st} extra {et} "
+                                             f"blocks {bs_s}/{bs_e} {layout}")
+    assert device_status() == 0
+
+
 # ----------------------------------------------------------------------------- argument errors
 def test_argument_errors(fm):
     q = torch.randn(2, 64, 512, device="cuda").to(torch.bfloat16)
