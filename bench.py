@@ -200,6 +200,11 @@ def run_reference(args_ns):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    # all the host threads there are: torchrun sets OMP_NUM_THREADS=1 for its workers
+    try:
+        torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
+    except (AttributeError, OSError):
+        torch.set_num_threads(max(1, os.cpu_count() or 1))
     name = args_ns.workload
     kind, kw = WORKLOADS[name]
     if "int8" in kind:   # the int8 caches come from the product quantizer; use its CPU oracle twin here
