@@ -545,6 +545,39 @@ def test_random_small_problems_match_the_oracle(fm, seed):
     assert device_status() == 0
 
 
+@pytest.mark.parametrize("offset", [0, 16, 8, 4])
+def test_caches_at_odd_byte_offsets(fm, offset):
+    """The gather picks the widest load the cache's alignment allows: 32 bytes, else 16, else 8 (fp8) /
+    4 (int8).  The same caches placed 0, 16, 8 and 4 bytes into a larger buffer must give the same answer."""
+    rng = np.random.default_rng(55)
+    torch.manual_seed(55)
+    T, H, topk = 5, 64, 300
+    lat = _rand_latent(rng, 512, 1.0)
+    q = torch.randn(T, H, 512, device="cuda").to(torch.bfloat16)
+    idx = torch.randint(-1, 514, (T, topk), dtype=torch.int32, device="cuda")
+    lens = torch.randint(1, topk + 1, (T,), dtype=torch.int32, device="cuda")
+    sink = torch.randn(H, device="cuda")
+
+    def shifted(t):      # the same bytes, `offset` bytes into a fresh 256-byte aligned buffer
+        flat = t.contiguous().view(torch.uint8).reshape(-1)
+        big = torch.zeros(flat.numel() + 64, dtype=torch.uint8, device="cuda")
+        big[offset:offset + flat.numel()] = flat
+        return big[offset:offset + flat.numel()], big
+
+    if offset % 8 == 0:
+        cache, K = fp8_cache_from_latent(lat, 64)
+        view, _keep = shifted(cache)
+        out = fm.sparse_mla_decode_fp8(q, view.view(cache.shape), idx, lens, scale=SCALE, attn_sink=sink)
+        assert_attention_close(out, oracle_out(q, K, idx, lens, scale=SCALE, sink=sink), f"fp8 cache at +{offset}")
+    sq, ss, K, buf = int8_cache_from_latent(lat, 64, "inline528")
+    view, _keep = shifted(buf)
+    b = view.view(buf.shape)
+    out = fm.sparse_mla_decode_int8(q, b[:, :, :512].view(torch.int8), b[:, :, 512:516].view(torch.float32).squeeze(-1), idx,
+                                    lens, scale=SCALE, attn_sink=sink)
+    assert_attention_close(out, oracle_out(q, K, idx, lens, scale=SCALE, sink=sink), f"int8 inline cache at +{offset}")
+    assert device_status() == 0
+
+
 # ----------------------------------------------------------------------------- argument errors
 def test_argument_errors(fm):
     q = torch.randn(2, 64, 512, device="cuda").to(torch.bfloat16)
