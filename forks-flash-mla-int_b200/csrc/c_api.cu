@@ -138,6 +138,23 @@ int smla_quantize_int8_ds_mla_rows(const void *x, int x_dtype, int64_t rows, int
                                            static_cast<cudaStream_t>(stream));
 }
 
+int smla_write_int8_ds_mla_cache(const void *x, int x_dtype, int64_t rows, int64_t x_row_stride,
+                                 const void *slot_mapping, int slots_are_int64, void *cache, int64_t num_blocks,
+                                 int block_size, int64_t block_stride_bytes, int64_t token_stride_bytes, int scale_rule,
+                                 void *stream) {
+    return smla::launch_write_int8_ds_mla(x, x_dtype, rows, x_row_stride, slot_mapping, slots_are_int64, cache,
+                                          num_blocks, block_size, block_stride_bytes, token_stride_bytes, scale_rule,
+                                          static_cast<cudaStream_t>(stream));
+}
+
+int smla_write_fp8_ds_mla_cache(const void *x, int x_dtype, int64_t rows, int64_t x_row_stride,
+                                const void *slot_mapping, int slots_are_int64, void *cache, int64_t num_blocks,
+                                int block_size, int64_t block_stride_bytes, void *stream) {
+    return smla::launch_write_fp8_ds_mla(x, x_dtype, rows, x_row_stride, slot_mapping, slots_are_int64, cache,
+                                         num_blocks, block_size, block_stride_bytes,
+                                         static_cast<cudaStream_t>(stream));
+}
+
 int smla_read_device_status(int *status_out) { return smla::read_and_clear_device_status(status_out); }
 
 }  // extern "C"

@@ -5,7 +5,8 @@
 //   flash_mla::fwd_sparse_decode_mla, fwd_sparse_prefill_mla,
 //   flash_mla::fwd_sparse_int8_decode_mla, fwd_sparse_int8_prefill_mla
 // plus flash_mla::quantize_int8_ds_mla_rows (a torch composite in the reference,
-// flash_mla/int8_sparse_mla.py:15-26; a CUDA kernel here).  Only torch/csrc/stable, the AOTI
+// flash_mla/int8_sparse_mla.py:15-26; a CUDA kernel here) and the two cache writers
+// flash_mla::write_int8_ds_mla_cache / write_fp8_ds_mla_cache (no counterpart in the reference).  Only torch/csrc/stable, the AOTI
 // shim and torch/headeronly are used -- no ATen, c10 or pybind -- and every op validates its
 // arguments, allocates its output (and split-KV scratch) with torch's allocator on q's device,
 // and forwards plain pointers to the C ABI in include/sparse_mla_b200.h on the current stream.
@@ -224,6 +225,51 @@ void quantize_int8_ds_mla_rows(const Tensor &k_in, Tensor &q_out, Tensor &scale_
              "int8_ds_mla row quantizer");
 }
 
+// Cache writers: latent [N, 512] (bf16 / fp16 / fp32), slot_mapping int32 / int64 [N], cache uint8
+// [num_blocks, block_size, 528 or 584] written in place.  The reference has no such op; the schemas
+// follow the (rows, slot_mapping, cache) shape of a serving engine's cache-write call.
+void write_ds_mla_cache(const char *what, bool fp8, const Tensor &latent_in, const Tensor &slots_in, const Tensor &cache,
+                        int64_t scale_rule) {
+    STD_TORCH_CHECK(latent_in.is_cuda() && slots_in.is_cuda() && cache.is_cuda(), what, ": tensors must be on CUDA");
+    STD_TORCH_CHECK(latent_in.dim() == 2 && latent_in.size(1) == 512, what, ": latent must be [rows, 512]");
+    STD_TORCH_CHECK(slots_in.dim() == 1 && slots_in.size(0) == latent_in.size(0), what, ": slot_mapping must be [rows]");
+    const int64_t token_bytes = fp8 ? 584 : 528;
+    STD_TORCH_CHECK(cache.dim() == 3 && cache.size(2) == token_bytes && cache.element_size() == 1 &&
+                        cache.stride(2) == 1 && cache.stride(1) == token_bytes && aligned16(cache),
+                    what, ": cache must be a 16-byte aligned byte tensor [num_blocks, block_size, ", token_bytes,
+                    "] with dense blocks");
+    int dtype = -1;
+    switch (latent_in.scalar_type()) {
+        case ScalarType::BFloat16: dtype = 0; break;
+        case ScalarType::Half: dtype = 1; break;
+        case ScalarType::Float: dtype = 2; break;
+        default: STD_TORCH_CHECK(false, what, ": latent must be bfloat16, float16 or float32");
+    }
+    const bool i64 = slots_in.scalar_type() == ScalarType::Long;
+    STD_TORCH_CHECK(i64 || slots_in.scalar_type() == ScalarType::Int, what, ": slot_mapping must be int32 or int64");
+    const int device = latent_in.get_device_index();
+    torch::stable::accelerator::DeviceGuard guard(device);
+    const int64_t elem = dtype == 2 ? 4 : 2;
+    const bool usable = latent_in.stride(1) == 1 && (latent_in.stride(0) * elem) % 16 == 0 && aligned16(latent_in);
+    const Tensor latent = usable ? latent_in : torch::stable::contiguous(latent_in);
+    const Tensor slots = slots_in.is_contiguous() ? slots_in : torch::stable::contiguous(slots_in);
+    const int64_t rows = latent.size(0);
+    const int64_t row_stride = rows > 1 ? latent.stride(0) : 512;
+    const int64_t block_stride = cache.size(0) > 1 ? cache.stride(0) : cache.size(1) * token_bytes;
+    if (fp8) {
+        check_rc(smla_write_fp8_ds_mla_cache(latent.data_ptr(), dtype, rows, row_stride, slots.data_ptr(), i64,
+                                             cache.data_ptr(), cache.size(0), static_cast<int>(cache.size(1)),
+                                             block_stride, current_stream(device)),
+                 what);
+    } else {
+        check_rc(smla_write_int8_ds_mla_cache(latent.data_ptr(), dtype, rows, row_stride, slots.data_ptr(), i64,
+                                              cache.data_ptr(), cache.size(0), static_cast<int>(cache.size(1)),
+                                              block_stride, token_bytes, static_cast<int>(scale_rule),
+                                              current_stream(device)),
+                 what);
+    }
+}
+
 // ------------------------------------------------------------------ boxed shims
 using torch::stable::detail::from;
 using torch::stable::detail::to;
@@ -274,6 +320,16 @@ void boxed_quantize(StableIValue *stack, uint64_t, uint64_t) {
     stack[1] = from(s);
 }
 
+void boxed_write_int8(StableIValue *stack, uint64_t, uint64_t) {
+    write_ds_mla_cache("int8_ds_mla cache writer", false, to<Tensor>(stack[0]), to<Tensor>(stack[1]),
+                       to<Tensor>(stack[2]), to<int64_t>(stack[3]));
+}
+
+void boxed_write_fp8(StableIValue *stack, uint64_t, uint64_t) {
+    write_ds_mla_cache("fp8_ds_mla cache writer", true, to<Tensor>(stack[0]), to<Tensor>(stack[1]),
+                       to<Tensor>(stack[2]), 0);
+}
+
 }  // namespace
 
 STABLE_TORCH_LIBRARY(flash_mla, m) {
@@ -290,6 +346,8 @@ STABLE_TORCH_LIBRARY(flash_mla, m) {
           "Tensor swa_indices, Tensor swa_lens, float scale, Tensor? attn_sink, "
           "Tensor? extra_cache, Tensor? extra_scale, Tensor? extra_indices, Tensor? extra_lens) -> Tensor");
     m.def("quantize_int8_ds_mla_rows(Tensor k) -> (Tensor, Tensor)");
+    m.def("write_int8_ds_mla_cache(Tensor latent, Tensor slot_mapping, Tensor(a!) cache, int scale_rule) -> ()");
+    m.def("write_fp8_ds_mla_cache(Tensor latent, Tensor slot_mapping, Tensor(a!) cache) -> ()");
 }
 
 STABLE_TORCH_LIBRARY_IMPL(flash_mla, CUDA, m) {
@@ -298,6 +356,8 @@ STABLE_TORCH_LIBRARY_IMPL(flash_mla, CUDA, m) {
     m.impl("fwd_sparse_int8_prefill_mla", &boxed_int8<true>);
     m.impl("fwd_sparse_int8_decode_mla", &boxed_int8<false>);
     m.impl("quantize_int8_ds_mla_rows", &boxed_quantize);
+    m.impl("write_int8_ds_mla_cache", &boxed_write_int8);
+    m.impl("write_fp8_ds_mla_cache", &boxed_write_fp8);
 }
 
 // `import flash_mla_cuda` only has to load this library so the static registrars above run.

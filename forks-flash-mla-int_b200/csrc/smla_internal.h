@@ -19,6 +19,13 @@ enum DeviceStatusBits : int {
 int launch_quantize_int8_rows(const void *x, int x_dtype, int64_t rows, int64_t x_row_stride, int8_t *q,
                               float *scale, cudaStream_t stream);
 
+int launch_write_int8_ds_mla(const void *x, int x_dtype, int64_t rows, int64_t x_row_stride, const void *slots,
+                             int slots_i64, void *cache, int64_t num_blocks, int block_size, int64_t block_stride,
+                             int64_t pos_stride, int scale_rule, cudaStream_t stream);
+int launch_write_fp8_ds_mla(const void *x, int x_dtype, int64_t rows, int64_t x_row_stride, const void *slots,
+                            int slots_i64, void *cache, int64_t num_blocks, int block_size, int64_t block_stride,
+                            cudaStream_t stream);
+
 // `force_single` = never split (prefill).  `split_ws`/`num_splits` as resolved by the caller.
 int launch_sparse_mla_attention(const smla_attn_params_t &p, int num_splits, void *workspace, cudaStream_t stream);
 

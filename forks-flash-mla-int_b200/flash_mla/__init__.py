@@ -1,7 +1,8 @@
 """flash_mla for B200 (sm_100a): the sparse-MLA path of AppMana/forks-flash-mla-int.
 
 Same names and argument contract as the reference package (flash_mla/__init__.py:3-15) for
-the sparse ops and the int8 row quantizer.  The dense-MLA entry points and the Triton decoder
+the sparse ops and the int8 row quantizer; ``write_fp8_ds_mla_cache`` / ``write_int8_ds_mla_cache``
+(encode new rows and scatter them into a paged cache) are additions the reference does not have.  The dense-MLA entry points and the Triton decoder
 (``get_mla_metadata``, ``flash_mla_with_kvcache``, ``flash_mla_with_kvcache_int8``,
 ``sparse_mla_decode_int8_triton``) are not part of this library.
 
@@ -13,6 +14,11 @@ __version__ = "2.0.0+b200"
 from .flash_mla_interface import (  # noqa: F401
     sparse_mla_decode_fp8,
     sparse_mla_prefill,
+)
+from .cache_formats import (  # noqa: F401
+    int8_ds_mla_cache_views,
+    write_fp8_ds_mla_cache,
+    write_int8_ds_mla_cache,
 )
 from .int8_sparse_mla import (  # noqa: F401
     quantize_int8_ds_mla_rows,
@@ -26,4 +32,7 @@ __all__ = [
     "sparse_mla_decode_int8",
     "sparse_mla_prefill_int8",
     "quantize_int8_ds_mla_rows",
+    "write_fp8_ds_mla_cache",
+    "write_int8_ds_mla_cache",
+    "int8_ds_mla_cache_views",
 ]

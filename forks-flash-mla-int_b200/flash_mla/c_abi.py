@@ -19,7 +19,8 @@ SMLA_ETOOBIG = -5
 EXPORTS = (
     "smla_version", "smla_error_string", "smla_choose_num_splits", "smla_attn_workspace_bytes",
     "smla_decode_plan", "smla_decode_kernel_launches", "smla_sparse_mla_decode", "smla_sparse_mla_decode_static_scratch", "smla_sparse_mla_prefill",
-    "smla_quantize_int8_ds_mla_rows", "smla_read_device_status",
+    "smla_quantize_int8_ds_mla_rows", "smla_write_int8_ds_mla_cache", "smla_write_fp8_ds_mla_cache",
+    "smla_read_device_status",
 )
 
 
@@ -86,6 +87,11 @@ def load() -> C.CDLL:
     lib.smla_sparse_mla_decode_static_scratch.argtypes = [C.POINTER(SmlaAttnParams), C.c_void_p]
     lib.smla_quantize_int8_ds_mla_rows.argtypes = [C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_void_p,
                                                    C.c_void_p, C.c_void_p]
+    lib.smla_write_int8_ds_mla_cache.argtypes = [C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_void_p, C.c_int,
+                                                 C.c_void_p, C.c_int64, C.c_int, C.c_int64, C.c_int64, C.c_int,
+                                                 C.c_void_p]
+    lib.smla_write_fp8_ds_mla_cache.argtypes = [C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_void_p, C.c_int,
+                                                C.c_void_p, C.c_int64, C.c_int, C.c_int64, C.c_void_p]
     lib.smla_read_device_status.argtypes = [C.POINTER(C.c_int)]
     _lib = lib
     return lib

@@ -149,6 +149,39 @@ SMLA_API int smla_sparse_mla_prefill(const smla_attn_params_t *params, void *str
 SMLA_API int smla_quantize_int8_ds_mla_rows(const void *x, int x_dtype, int64_t rows, int64_t x_row_stride,
                                    int8_t *q, float *scale, void *stream);
 
+/* Cache writers: encode `rows` new latent rows and scatter them into a paged cache in one kernel,
+ * the step that runs right before the attention calls above.  The reference has no device writer
+ * (its tests and benchmarks pack caches with torch composites); the bytes written are the formats
+ * its kernels read.  Common arguments:
+ *   x: [rows, 512] of `x_dtype` (0 = bf16, 1 = fp16, 2 = fp32), `x_row_stride` elements apart,
+ *      16-byte aligned rows (32-byte aligned rows take 256-bit loads);
+ *   slot_mapping: int32 or int64 [rows] (`slots_are_int64`); row i goes to block slot / block_size,
+ *      position slot % block_size; a negative slot, or one >= num_blocks * block_size, skips the row;
+ *      two rows with the same slot race;
+ *   cache: 16-byte aligned base of `num_blocks` blocks, `block_stride_bytes` apart.
+ *
+ * int8_ds_mla inline container (tests/test_sparse_mla_prefill_int8_adversarial.py:5-12): a token is
+ * 512 int8 + the fp32 row scale at +512 + 12 zero bytes, tokens `token_stride_bytes` (>= 528, multiple of
+ * 16) apart.  scale_rule 0: scale and codes bit-exact with quantize_int8_ds_mla_rows
+ * (flash_mla/int8_sparse_mla.py:15-26); scale_rule 1: scale = max(amax / 127, 1e-12), the serving
+ * engine's writer as restated at tests/test_sparse_mla_prefill_int8_adversarial.py:35-40 (the two differ
+ * only for rows with amax < 1.27e-10). */
+SMLA_API int smla_write_int8_ds_mla_cache(const void *x, int x_dtype, int64_t rows, int64_t x_row_stride,
+                                          const void *slot_mapping, int slots_are_int64, void *cache,
+                                          int64_t num_blocks, int block_size, int64_t block_stride_bytes,
+                                          int64_t token_stride_bytes, int scale_rule, void *stream);
+
+/* fp8_ds_mla (docs/sparse_mla_decode_sm86_design.md:23-31, tests/test_sparse_mla_decode_sm86.py:14-44): a
+ * block is [block_size x 576 data bytes][block_size x 8 scale bytes]; a token's data are 448 e4m3 codes
+ * of x / 2^e (round to nearest even, e per 64 dims) and 64 bf16 (the last 64 elements, round to
+ * nearest even); its scale record is 7 bytes e + 127 and one byte 127.  e is the smallest exponent
+ * with amax <= 448 * 2^e, clamped to [-120, 120], 0 for an all-zero group.  block_stride_bytes >=
+ * block_size * 584 and a multiple of 8 (a multiple of 16 takes 16-byte stores). */
+SMLA_API int smla_write_fp8_ds_mla_cache(const void *x, int x_dtype, int64_t rows, int64_t x_row_stride,
+                                         const void *slot_mapping, int slots_are_int64, void *cache,
+                                         int64_t num_blocks, int block_size, int64_t block_stride_bytes,
+                                         void *stream);
+
 /* Reads and clears the per-device error word the kernels set when a bounded wait ran out
  * (0 = none).  Synchronises the device; meant for tests and debugging, not for hot paths. */
 SMLA_API int smla_read_device_status(int *status_out);

@@ -82,11 +82,23 @@ def encode_e4m3(x: np.ndarray) -> np.ndarray:
     return code | sign
 
 
+def ue8m0_exponents(groups: np.ndarray) -> np.ndarray:
+    """fp32 [..., 64] -> int32 [...]: the smallest power-of-two exponent e with
+    ``amax|group| <= 448 * 2**e``, clamped to [-120, 120]; 0 for an all-zero group.
+    Exact (no logarithm): amax = m * 2**k with m in [0.5, 1) and 448 = 0.875 * 2**9, so
+    e = k - 9 when m <= 0.875 and k - 8 otherwise."""
+    amax = np.abs(np.asarray(groups, dtype=np.float32)).max(axis=-1)
+    m, k = np.frexp(amax)
+    e = np.where(m <= np.float32(0.875), k - 9, k - 8)
+    e = np.where(amax > 0, e, 0)
+    return np.clip(e, -120, 120).astype(np.int32)
+
+
 def pack_fp8_ds_mla(latent: np.ndarray, block_size: int, exps: np.ndarray | None = None):
     """Pack fp32 rows [N, 512] (bf16-representable RoPE tail) into a paged fp8_ds_mla cache.
 
     ``exps`` [N, 7] are the per-64-group power-of-two exponents; when None the smallest
-    exponent with ``amax / 2**e <= 448`` is used.  The reference ships no production
+    exponent with ``amax / 2**e <= 448`` is used (``ue8m0_exponents``).  The reference ships no production
     writer, so this choice is ours; parity is defined on ``dequant(bytes)``.
     Returns ``(cache uint8 [nb, bs, 584], K fp32 [nb * bs, 512])`` with K the exact
     dequantised rows.  Slots past N are zero bytes (dequantise to zero rows).
@@ -97,11 +109,7 @@ def pack_fp8_ds_mla(latent: np.ndarray, block_size: int, exps: np.ndarray | None
     total = nb * block_size
     nope = latent[:, :FP8_DIM].reshape(n, N_GROUPS, SCALE_GROUP)
     if exps is None:
-        amax = np.abs(nope).max(axis=-1)
-        with np.errstate(divide="ignore"):
-            e = np.ceil(np.log2(np.maximum(amax, 1e-30) / 448.0))
-        exps = np.where(amax > 0, e, 0).astype(np.int32)
-        exps = np.clip(exps, -120, 120)
+        exps = ue8m0_exponents(nope)
     exps = np.asarray(exps, dtype=np.int32)
     scale = np.exp2(exps.astype(np.float32))[:, :, None]
     codes = encode_e4m3(nope / scale).reshape(n, FP8_DIM)
@@ -164,3 +172,49 @@ def pack_int8_inline528(q: np.ndarray, scale: np.ndarray, block_size: int) -> np
     buf[:n, :HEAD_DIM] = q.view(np.uint8)
     buf[:n, HEAD_DIM:HEAD_DIM + 4] = s.view(np.uint8).reshape(n, 4)
     return buf.reshape(nb, block_size, INT8_TOKEN_BYTES)
+
+
+def quantize_int8_rows_writer(x: np.ndarray):
+    """The cache writer's variant of the row quantizer (reference:
+    tests/test_sparse_mla_prefill_int8_adversarial.py:35-40, ``_quantize_rows``, stated there to
+    mirror the serving engine's writer): ``scale = max(amax|x| / 127, 1e-12)``; the codes are
+    computed as in ``quantize_int8_rows``.  Differs from it only for rows with amax < 1.27e-10."""
+    x = np.asarray(x, dtype=np.float32)
+    amax = np.abs(x).max(axis=-1)
+    scale = np.maximum((amax / np.float32(127.0)).astype(np.float32), np.float32(1e-12))
+    q = np.clip(np.rint(x / scale[..., None]), -127, 127).astype(np.int8)
+    return q, scale
+
+
+def write_int8_inline528(cache: np.ndarray, latent: np.ndarray, slots: np.ndarray, scale_rule: int = 0) -> None:
+    """Quantise rows [N, 512] and scatter them into ``cache`` uint8 [nb, bs, 528] in place:
+    row i goes to block ``slots[i] // bs``, position ``slots[i] % bs``; a negative slot or one
+    past the cache skips the row.  A written token is 512 int8, the fp32 scale and 12 zero bytes.
+    ``scale_rule`` 0 = ``quantize_int8_rows``, 1 = ``quantize_int8_rows_writer``."""
+    nb, bs, tb = cache.shape
+    assert tb == INT8_TOKEN_BYTES and cache.dtype == np.uint8
+    q, s = (quantize_int8_rows if scale_rule == 0 else quantize_int8_rows_writer)(latent)
+    flat = cache.reshape(nb * bs, tb)
+    for i, slot in enumerate(np.asarray(slots).reshape(-1).tolist()):
+        if 0 <= slot < nb * bs:
+            flat[slot, :HEAD_DIM] = q[i].view(np.uint8)
+            flat[slot, HEAD_DIM:HEAD_DIM + 4] = s[i:i + 1].view(np.uint8)
+            flat[slot, HEAD_DIM + 4:] = 0
+
+
+def write_fp8_ds_mla(cache: np.ndarray, latent: np.ndarray, slots: np.ndarray) -> None:
+    """Encode rows [N, 512] and scatter them into ``cache`` uint8 [nb, bs, 584] in place (same
+    slot rule as ``write_int8_inline528``).  Bytes per token as ``pack_fp8_ds_mla`` writes them:
+    448 e4m3 codes of ``x / 2**e``, 64 bf16 (round-to-nearest-even) and the scale record
+    ``[e + 127] * 7 + [127]`` in the block's scale area."""
+    nb, bs, tb = cache.shape
+    assert tb == TOKEN_BYTES_FP8 and cache.dtype == np.uint8
+    latent = np.asarray(latent, dtype=np.float32)
+    packed, _ = pack_fp8_ds_mla(latent, 1)                 # [N, 1, 584]: one token per block
+    packed = packed.reshape(-1, TOKEN_BYTES_FP8)
+    flat = cache.reshape(nb, bs * tb)
+    for i, slot in enumerate(np.asarray(slots).reshape(-1).tolist()):
+        if 0 <= slot < nb * bs:
+            b, p = divmod(slot, bs)
+            flat[b, p * TOKEN_DATA:(p + 1) * TOKEN_DATA] = packed[i, :TOKEN_DATA]
+            flat[b, bs * TOKEN_DATA + p * SCALE_BYTES: bs * TOKEN_DATA + (p + 1) * SCALE_BYTES] = packed[i, TOKEN_DATA:]

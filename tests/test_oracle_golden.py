@@ -116,3 +116,60 @@ def test_pack_roundtrip():
     assert buf.shape == (5, 16, 528)
     assert np.array_equal(buf.reshape(-1, 528)[:70, :512].view(np.int8), q)
     assert np.array_equal(buf.reshape(-1, 528)[:70, 512:516].copy().view(np.float32).ravel(), s)
+
+
+def test_ue8m0_exponent_rule_is_exact():
+    """The writer's exponent is the smallest e with amax <= 448 * 2**e, also right at the boundaries
+    (checked in exact rational arithmetic), 0 for a zero group and clamped to [-120, 120]."""
+    from fractions import Fraction
+    from oracle import ue8m0_exponents
+    rng = np.random.default_rng(5)
+    amax = np.concatenate([
+        np.float32(448.0) * np.exp2(np.arange(-30, 31)).astype(np.float32),                      # on the boundary
+        np.nextafter(np.float32(448.0) * np.exp2(np.arange(-30, 31)).astype(np.float32), np.float32(np.inf)),
+        np.nextafter(np.float32(448.0) * np.exp2(np.arange(-30, 31)).astype(np.float32), np.float32(0)),
+        np.exp(rng.uniform(-60, 60, 400)).astype(np.float32),
+        np.array([0.0, 1e-45, 1e-39, 3e38], np.float32)])
+    groups = np.zeros((amax.size, 64), np.float32)
+    groups[np.arange(amax.size), rng.integers(0, 64, amax.size)] = amax * rng.choice([-1.0, 1.0], amax.size).astype(np.float32)
+    e = ue8m0_exponents(groups)
+    for a, ei in zip(amax.tolist(), e.tolist()):
+        if a == 0.0:
+            assert ei == 0
+            continue
+        fa = Fraction(a)
+        want = 0
+        while fa > 448 * Fraction(2) ** want:
+            want += 1
+        while fa <= 448 * Fraction(2) ** (want - 1):
+            want -= 1
+        assert ei == max(-120, min(120, want)), (a, ei, want)
+
+
+def test_scatter_writers_match_packers():
+    from oracle import quantize_int8_rows_writer, write_fp8_ds_mla, write_int8_inline528
+    rng = np.random.default_rng(6)
+    x = rng.standard_normal((50, 512)).astype(np.float32)
+    x[7] = 0
+    x[8] *= 1e-11
+    cache, _ = pack_fp8_ds_mla(x, 16)
+    mine = np.zeros_like(cache)
+    write_fp8_ds_mla(mine, x, np.arange(50))
+    assert np.array_equal(mine, cache)
+    q, s = quantize_int8_rows(x)
+    buf = np.zeros((4, 16, 528), np.uint8)
+    write_int8_inline528(buf, x, np.arange(50))
+    assert np.array_equal(buf, pack_int8_inline528(q, s, 16))
+    # scattered slots, skipped rows, untouched bytes
+    slots = rng.permutation(64)[:50]
+    slots[3], slots[4] = -1, 64
+    buf2 = np.full((4, 16, 528), 0xA5, np.uint8)
+    write_int8_inline528(buf2, x, slots, scale_rule=1)
+    qw, sw = quantize_int8_rows_writer(x)
+    assert sw[8] == np.float32(1e-12) and s[8] != sw[8] and np.array_equal(s[:7], sw[:7])
+    flat = buf2.reshape(64, 528)
+    for i, sl in enumerate(slots.tolist()):
+        if 0 <= sl < 64:
+            assert np.array_equal(flat[sl, :512].view(np.int8), qw[i]) and flat[sl, 512:516].view(np.float32)[0] == sw[i]
+    untouched = np.setdiff1d(np.arange(64), slots[(slots >= 0) & (slots < 64)])
+    assert (flat[untouched] == 0xA5).all()
