@@ -48,6 +48,14 @@ WORKLOADS = {
                                                           extra_slots=16384, extra_topk=512, mask_frac=0.0,
                                                           full_lens=True)),
     "int8_prefill_T4096_H64": ("prefill_int8", dict(T=4096, H=64)),
+    # cache writers (the step before the attention calls): 2^20 new bf16 latent rows scattered into a paged cache
+    "write_int8_cache_rows1M": ("write_int8", dict(rows=1 << 20, block_size=64)),
+    "write_fp8_cache_rows1M": ("write_fp8", dict(rows=1 << 20, block_size=64)),
+    "write_int8_cache_rows256k": ("write_int8", dict(rows=1 << 18, block_size=64)),
+    "write_fp8_cache_rows256k": ("write_fp8", dict(rows=1 << 18, block_size=64)),
+    # the int8 row quantizer alone (quantize_int8_ds_mla_rows): rows in, int8 rows + fp32 scales out
+    "quantize_int8_rows1M": ("write_quantize", dict(rows=1 << 20, block_size=64)),
+    "quantize_int8_rows256k": ("write_quantize", dict(rows=1 << 18, block_size=64)),
 }
 DEFAULT_WORKLOAD = "dsv4_fp8_decode_T128_H64"
 
@@ -193,6 +201,165 @@ def time_cpu_oracle(oin, T, budget_s=12.0):
     return n, dt, out, torch.get_num_threads()
 
 
+# ----------------------------------------------------------------------------- cache-writer workloads
+WRITER_TOKEN_BYTES = {"write_int8": 528, "write_fp8": 584, "write_quantize": 516}
+WRITER_KERNEL = {"write_int8": "write_ds_mla_cache_kernel<bf16, int8>", "write_fp8": "write_ds_mla_cache_kernel<bf16, fp8>",
+                 "write_quantize": "quantize_int8_rows_kernel<bf16>"}
+
+
+def writer_inputs(kind, kw, device, seed):
+    """Seeded latent rows (N(0,1) times a per-row power of two, bf16), a random injective slot mapping
+    and an empty paged cache with a few spare blocks."""
+    import torch
+    n, bs = kw["rows"], kw["block_size"]
+    nb = n // bs + 16
+    g = torch.Generator(device=device).manual_seed(1234 + seed)
+    x = torch.randn(n, 512, generator=g, device=device)
+    x *= torch.exp2(torch.randint(-4, 5, (n, 1), generator=g, device=device).float())
+    slots = torch.randperm(nb * bs, generator=g, device=device)[:n]
+    tb = 528 if kind == "write_quantize" else WRITER_TOKEN_BYTES[kind]     # the quantizer: checked as inline tokens
+    cache = torch.zeros(nb, bs, tb, dtype=torch.uint8, device=device)
+    return x.to(torch.bfloat16), slots, cache
+
+
+def writer_oracle(kind, x_np, slots_np, nb, bs):
+    import numpy as np
+    import oracle
+    if kind == "write_quantize":
+        t0 = time.perf_counter()
+        q, s = oracle.quantize_int8_rows(x_np)
+        return (q, s), time.perf_counter() - t0
+    ref = np.zeros((nb, bs, WRITER_TOKEN_BYTES[kind]), np.uint8)
+    t0 = time.perf_counter()
+    (oracle.write_int8_inline528 if kind == "write_int8" else oracle.write_fp8_ds_mla)(ref, x_np, slots_np)
+    return ref, time.perf_counter() - t0
+
+
+def run_writer_reference(a, kind, kw):
+    """Reference arm of the writer workloads: the numpy oracle writer on the host, a bounded sample per step."""
+    import torch
+    x, slots, cache = writer_inputs(kind, dict(kw, rows=1 << 15), "cpu", 0)
+    x_np, slots_np = x.float().numpy(), slots.numpy()
+    nb, bs = cache.shape[0], cache.shape[1]
+    for _ in range(min(a.warmup, 1)):
+        writer_oracle(kind, x_np[:2048], slots_np[:2048], nb, bs)
+    dt = sum(writer_oracle(kind, x_np, slots_np, nb, bs)[1] for _ in range(a.steps))
+    val = x_np.shape[0] * a.steps / dt
+    print(json.dumps({
+        "impl": "reference", "metric": "rows quantized/s" if kind == "write_quantize" else "cache rows written/s", "value": val, "unit": "rows/s", "n_gpus": a.gpus,
+        "steps": a.steps, "warmup": a.warmup, "ms_per_step": dt / a.steps * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": a.workload, "rows_per_step_sampled": x_np.shape[0]},
+        "cpu_baseline": {"value": val, "unit": "rows/s", "cores": 1, "kind": "port",
+                         "sample": f"{x_np.shape[0]} rows per step (numpy oracle writer), {a.steps} steps"},
+        "e2e": {"value": val, "unit": "rows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+
+
+def run_writer(a, kind, kw, world, rank, local, dev, barrier):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    import flash_mla
+    x, slots, cache = writer_inputs(kind, kw, dev, rank)
+    n, tb = x.shape[0], WRITER_TOKEN_BYTES[kind]
+    if kind == "write_quantize":
+        last = {}
+
+        def write(rows, _slots, _cache):
+            last["q"], last["s"] = flash_mla.quantize_int8_ds_mla_rows(rows)
+        alg_bytes = n * (1024 + tb)          # bf16 row in, int8 row + fp32 scale out
+    else:
+        write = flash_mla.write_int8_ds_mla_cache if kind == "write_int8" else flash_mla.write_fp8_ds_mla_cache
+        alg_bytes = n * (1024 + tb + 8)      # bf16 row in, token out, int64 slot
+
+    def timed(fn, steps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    for _ in range(a.warmup):
+        write(x, slots, cache)
+    sampler = ClockSampler(local) if rank == 0 else None
+    ms = timed(lambda: write(x, slots, cache), a.steps)
+    clocks = sampler.stop() if sampler else None
+
+    # end to end: the rows and their slots come from pinned host memory every step; the cache is the
+    # result and stays in HBM (as in serving), one written token is read back as the step's receipt
+    hx, hs = x.cpu().pin_memory(), slots.cpu().pin_memory()
+    dx, ds = torch.empty_like(x), torch.empty_like(slots)
+    receipt = torch.empty(cache.shape[2], dtype=torch.uint8).pin_memory()
+    first = int(slots[0])
+
+    def e2e_step():
+        dx.copy_(hx, non_blocking=True)
+        ds.copy_(hs, non_blocking=True)
+        write(dx, ds, cache)
+        if kind == "write_quantize":
+            receipt[:512].copy_(last["q"][0].view(torch.uint8), non_blocking=True)
+        else:
+            receipt.copy_(cache.view(-1, cache.shape[2])[first], non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    e2e_steps = max(3, min(a.steps, 10))
+    ms_e2e = timed(e2e_step, e2e_steps)
+
+    if rank == 0:
+        hbm_gbs, _, peak_kind = measured_peaks()
+        dur_s = ms / a.steps / 1e3
+        roof = {"bound": "hbm", "achieved": alg_bytes / dur_s / 1e9, "peak": hbm_gbs, "unit": "GB/s",
+                "traffic": NCU_DRAM_TRAFFIC_BYTES.get(a.workload), "peak_kind": peak_kind,
+                "kernel": WRITER_KERNEL[kind],
+                "algorithmic_bytes_per_launch": alg_bytes}
+        roof["frac"] = roof["achieved"] / roof["peak"]
+        line = {
+            "metric": "rows quantized/s" if kind == "write_quantize" else "cache rows written/s",
+            "value": world * n * a.steps / (ms / 1e3), "unit": "rows/s",
+            "n_gpus": world, "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms / a.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f8e4m3" if kind == "write_fp8" else "i8", "data": "synthetic",
+            "config": {"workload": a.workload, "rows_per_gpu_per_step": n, "block_size": kw["block_size"],
+                       "l2": f"{alg_bytes / 2**20:.0f} MiB read + written per step > 126 MiB L2",
+                       "sharding": "rows sharded across GPUs, no collective"},
+            "roofline": roof,
+            "e2e": {"value": world * n * e2e_steps / (ms_e2e / 1e3), "unit": "rows/s",
+                    "h2d_bytes_per_step": hx.numel() * 2 + hs.numel() * 8, "d2h_bytes_per_step": tb,
+                    "ms_per_step": ms_e2e / e2e_steps, "steps": e2e_steps,
+                    "note": "latent rows and slots from pinned host memory each step; the cache stays in HBM, one token read back"},
+            "gpu_launches": a.steps,
+        }
+        if clocks:
+            line["clocks"] = clocks
+        if world == 1 and not a.no_cpu_baseline:
+            m = 1 << 15                      # bounded sample: the first 32768 rows of the same step
+            ref, dt = writer_oracle(kind, x[:m].float().cpu().numpy(), slots[:m].cpu().numpy(), cache.shape[0], cache.shape[1])
+            line["cpu_baseline"] = {"value": m / dt, "unit": "rows/s", "cores": 1, "kind": "port",
+                                    "sample": f"first {m} of {n} rows of the same step (numpy oracle writer)"}
+            # the same rows written by the kernel into an empty cache: the whole cache, byte for byte
+            if kind == "write_quantize":
+                write(x[:m], None, None)
+                exact = bool(np.array_equal(last["q"].cpu().numpy(), ref[0]) and np.array_equal(last["s"].cpu().numpy(), ref[1]))
+            else:
+                fresh = torch.zeros_like(cache)
+                write(x[:m], slots[:m], fresh)
+                exact = bool(np.array_equal(fresh.cpu().numpy(), ref))
+            line["parity"] = {"rows_checked": m, "bit_exact": exact}
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def run_reference(args_ns):
     """Reference arm: the fp32 CPU oracle (a port of the reference's own torch oracle; the Python
     reference cannot travel to the GPU box) on the host cores, same workload, bounded sample per step."""
@@ -207,6 +374,9 @@ def run_reference(args_ns):
         torch.set_num_threads(max(1, os.cpu_count() or 1))
     name = args_ns.workload
     kind, kw = WORKLOADS[name]
+    if kind.startswith("write"):
+        run_writer_reference(args_ns, kind, kw)
+        return
     if "int8" in kind:   # the int8 caches come from the product quantizer; use its CPU oracle twin here
         dev = "cuda" if torch.cuda.is_available() else None
         if dev is None:
@@ -280,6 +450,10 @@ def main():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    if WORKLOADS[a.workload][0].startswith("write"):
+        run_writer(a, *WORKLOADS[a.workload], world, rank, local, dev, barrier)
+        return
 
     kind, wargs, meta = build_workload(a.workload, dev, seed=rank)
     op = op_for(kind)

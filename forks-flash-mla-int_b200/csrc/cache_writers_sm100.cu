@@ -16,99 +16,26 @@
 //
 // HBM-bound: one warp per row, each lane owns 16 consecutive elements (one 256-bit load for 16-bit
 // inputs, two for fp32) and stores its 16 output bytes with one 16-byte store; per bf16 row the
-// kernel moves 1024 + 528 (int8) or 1024 + 584 (fp8) bytes plus the slot index.
+// kernel moves 1024 + 528 (int8) or 1024 + 584 (fp8) bytes plus the slot index.  The grid is sized
+// to the SMs; a warp walks rows with the next row's loads (and slot) in flight while it encodes the
+// current one.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <cstdint>
 
+#include "row_codec.cuh"
 #include "smla_internal.h"
 
 namespace smla {
+
+int row_kernel_blocks(const void *kernel, int64_t rows, unsigned *blocks);   // quantize_int8_sm100.cu
+
 namespace {
 
+using rowcodec::Lane16;
 constexpr int kWarpsPerBlock = 8;
-
-__device__ __forceinline__ void ldg_nc_v8(const void *p, uint4 &lo, uint4 &hi) {
-    asm volatile("ld.global.nc.L1::no_allocate.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                 : "=r"(lo.x), "=r"(lo.y), "=r"(lo.z), "=r"(lo.w), "=r"(hi.x), "=r"(hi.y), "=r"(hi.z), "=r"(hi.w)
-                 : "l"(p));
-}
-__device__ __forceinline__ uint4 ldg_nc_v4(const void *p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(p));
-    return v;
-}
-// 32 bytes at p: one 256-bit request when p is 32-byte aligned (warp-uniform), else two of 128 bits.
-__device__ __forceinline__ void load32(const uint8_t *p, bool wide, uint4 &lo, uint4 &hi) {
-    if (wide) {
-        ldg_nc_v8(p, lo, hi);
-    } else {
-        lo = ldg_nc_v4(p);
-        hi = ldg_nc_v4(p + 16);
-    }
-}
-
-// The 16 consecutive elements [16 * lane, 16 * lane + 16) of a row as floats; `bits` keeps the raw
-// 16-bit patterns of a 16-bit input (the fp8 writer copies bf16 RoPE values through unchanged).
-template <typename T> struct Lane16;
-template <> struct Lane16<__nv_bfloat16> {
-    static __device__ __forceinline__ void load(const uint8_t *row, int lane, bool wide, float *f, uint4 *bits) {
-        load32(row + lane * 32, wide, bits[0], bits[1]);
-        const uint32_t w[8] = {bits[0].x, bits[0].y, bits[0].z, bits[0].w, bits[1].x, bits[1].y, bits[1].z, bits[1].w};
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            f[2 * i] = __uint_as_float(w[i] << 16);
-            f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
-        }
-    }
-    // bf16 patterns of the 16 elements: unchanged.
-    static __device__ __forceinline__ void to_bf16(const float *, const uint4 *bits, uint4 *out) {
-        out[0] = bits[0];
-        out[1] = bits[1];
-    }
-};
-__device__ __forceinline__ uint32_t pack_bf16_rn(float a, float b) {
-    const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);   // .x = a in the low half
-    return *reinterpret_cast<const uint32_t *>(&v);
-}
-__device__ __forceinline__ void floats_to_bf16(const float *f, uint4 *out) {
-    out[0] = make_uint4(pack_bf16_rn(f[0], f[1]), pack_bf16_rn(f[2], f[3]), pack_bf16_rn(f[4], f[5]),
-                        pack_bf16_rn(f[6], f[7]));
-    out[1] = make_uint4(pack_bf16_rn(f[8], f[9]), pack_bf16_rn(f[10], f[11]), pack_bf16_rn(f[12], f[13]),
-                        pack_bf16_rn(f[14], f[15]));
-}
-template <> struct Lane16<__half> {
-    static __device__ __forceinline__ void load(const uint8_t *row, int lane, bool wide, float *f, uint4 *bits) {
-        load32(row + lane * 32, wide, bits[0], bits[1]);
-        const uint32_t w[8] = {bits[0].x, bits[0].y, bits[0].z, bits[0].w, bits[1].x, bits[1].y, bits[1].z, bits[1].w};
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const float2 p = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
-            f[2 * i] = p.x;
-            f[2 * i + 1] = p.y;
-        }
-    }
-    static __device__ __forceinline__ void to_bf16(const float *f, const uint4 *, uint4 *out) { floats_to_bf16(f, out); }
-};
-template <> struct Lane16<float> {
-    static __device__ __forceinline__ void load(const uint8_t *row, int lane, bool wide, float *f, uint4 *) {
-        uint4 v[4];
-        load32(row + lane * 64, wide, v[0], v[1]);
-        load32(row + lane * 64 + 32, wide, v[2], v[3]);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            f[4 * i] = __uint_as_float(v[i].x);
-            f[4 * i + 1] = __uint_as_float(v[i].y);
-            f[4 * i + 2] = __uint_as_float(v[i].z);
-            f[4 * i + 3] = __uint_as_float(v[i].w);
-        }
-    }
-    static __device__ __forceinline__ void to_bf16(const float *f, const uint4 *, uint4 *out) { floats_to_bf16(f, out); }
-};
 
 struct WriterArgs {
     const uint8_t *x;          // rows of 512 elements
@@ -136,41 +63,20 @@ __device__ __forceinline__ void store16(uint8_t *p, const uint4 &v, bool st16) {
 }
 
 __device__ __forceinline__ int64_t slot_of(const WriterArgs &a, int64_t row) {
-    return a.slots_i64 ? static_cast<const int64_t *>(a.slots)[row]
-                       : static_cast<int64_t>(static_cast<const int32_t *>(a.slots)[row]);
+    return a.slots_i64 ? __ldg(static_cast<const int64_t *>(a.slots) + row)
+                       : static_cast<int64_t>(__ldg(static_cast<const int32_t *>(a.slots) + row));
 }
 
-template <typename T>
-__global__ void __launch_bounds__(kWarpsPerBlock * 32) write_int8_ds_mla_kernel(const WriterArgs a) {
-    const int lane = threadIdx.x & 31;
-    const int64_t row = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
-    if (row >= a.rows) return;
-    const int64_t slot = slot_of(a, row);
-    if (slot < 0 || slot >= a.num_slots) return;          // padding rows of a batch carry slot -1
-
-    float f[16];
-    uint4 bits[2];
-    Lane16<T>::load(a.x + row * a.x_row_bytes, lane, a.wide != 0, f, bits);
+// One row, already in registers as fp32, to its int8_ds_mla token.
+__device__ __forceinline__ void encode_int8(const WriterArgs &a, const float *f, int64_t slot, int lane) {
     float amax = 0.0f;
 #pragma unroll
     for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(f[i]));
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    amax = rowcodec::warp_max(amax);
     const float s = a.scale_rule == 0 ? __fdiv_rn(fmaxf(amax, 1e-12f), 127.0f)
                                       : fmaxf(__fdiv_rn(amax, 127.0f), 1e-12f);
-
     uint32_t w[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        uint32_t word = 0;
-#pragma unroll
-        for (int b = 0; b < 4; ++b) {
-            float r = rintf(__fdiv_rn(f[4 * j + b], s));
-            r = fminf(fmaxf(r, -127.0f), 127.0f);
-            word |= (static_cast<uint32_t>(static_cast<int>(r)) & 0xFFu) << (8 * b);
-        }
-        w[j] = word;
-    }
+    rowcodec::int8_codes16(f, s, w);
     uint8_t *tok = a.cache + (slot / a.block_size) * a.block_stride + (slot % a.block_size) * a.pos_stride;
     *reinterpret_cast<uint4 *>(tok + lane * 16) = make_uint4(w[0], w[1], w[2], w[3]);
     if (lane == 0) *reinterpret_cast<uint4 *>(tok + 512) = make_uint4(__float_as_uint(s), 0u, 0u, 0u);
@@ -185,59 +91,86 @@ __device__ __forceinline__ int ue8m0_exponent(float amax) {
     return max(-120, min(120, e));
 }
 
-template <typename T>
-__global__ void __launch_bounds__(kWarpsPerBlock * 32) write_fp8_ds_mla_kernel(const WriterArgs a) {
-    const int lane = threadIdx.x & 31;
-    const int64_t row = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
-    if (row >= a.rows) return;
-    const int64_t slot = slot_of(a, row);
-    if (slot < 0 || slot >= a.num_slots) return;
+__device__ __forceinline__ uint32_t pack_bf16_rn(float a, float b) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);   // .x = a in the low half
+    return *reinterpret_cast<const uint32_t *>(&v);
+}
+__device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
+    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);   // a in the low byte
+    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+    return lo | (hi << 16);
+}
 
-    float f[16];
-    uint4 bits[2];
-    Lane16<T>::load(a.x + row * a.x_row_bytes, lane, a.wide != 0, f, bits);
-    // Four lanes share a group of 64 dims: groups 0..6 are NoPE, lanes 28..31 hold the RoPE tail.
+// One row to its fp8_ds_mla token: four lanes share a group of 64 dims; groups 0..6 are NoPE, lanes
+// 28..31 hold the RoPE tail (bf16 inputs round to themselves).
+__device__ __forceinline__ void encode_fp8(const WriterArgs &a, const float *f, int64_t slot, int lane) {
     float amax = 0.0f;
 #pragma unroll
     for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(f[i]));
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
     const int e = ue8m0_exponent(amax);
-    uint32_t sc_lo = 0, sc_hi = 0;                         // the 8 scale bytes, assembled in every lane
+    uint32_t sc_lo = 0, sc_hi = 127u << 24;                // the 8 scale bytes, assembled in every lane
 #pragma unroll
     for (int g = 0; g < 7; ++g) {
         const uint32_t byte = static_cast<uint32_t>(__shfl_sync(0xffffffffu, e, 4 * g) + 127);
         if (g < 4) sc_lo |= byte << (8 * g);
         else sc_hi |= byte << (8 * (g - 4));
     }
-    sc_hi |= 127u << 24;
-
     const int64_t blk = slot / a.block_size;
     const int pos = static_cast<int>(slot % a.block_size);
     uint8_t *block = a.cache + blk * a.block_stride;
     uint8_t *tok = block + static_cast<int64_t>(pos) * 576;
     if (lane < 28) {
         const float inv = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);     // 2^-e, exact
-        uint32_t w[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            uint32_t word = 0;
-#pragma unroll
-            for (int b = 0; b < 4; ++b) {
-                const uint32_t code = __nv_cvt_float_to_fp8(f[4 * j + b] * inv, __NV_SATFINITE, __NV_E4M3);
-                word |= code << (8 * b);
-            }
-            w[j] = word;
-        }
-        store16(tok + lane * 16, make_uint4(w[0], w[1], w[2], w[3]), a.st16 != 0);
+        uint4 w;
+        w.x = pack_e4m3x4(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv);
+        w.y = pack_e4m3x4(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv);
+        w.z = pack_e4m3x4(f[8] * inv, f[9] * inv, f[10] * inv, f[11] * inv);
+        w.w = pack_e4m3x4(f[12] * inv, f[13] * inv, f[14] * inv, f[15] * inv);
+        store16(tok + lane * 16, w, a.st16 != 0);
     } else {
-        uint4 r[2];
-        Lane16<T>::to_bf16(f, bits, r);
-        store16(tok + 448 + (lane - 28) * 32, r[0], a.st16 != 0);
-        store16(tok + 448 + (lane - 28) * 32 + 16, r[1], a.st16 != 0);
+        const uint4 r0 = make_uint4(pack_bf16_rn(f[0], f[1]), pack_bf16_rn(f[2], f[3]), pack_bf16_rn(f[4], f[5]),
+                                    pack_bf16_rn(f[6], f[7]));
+        const uint4 r1 = make_uint4(pack_bf16_rn(f[8], f[9]), pack_bf16_rn(f[10], f[11]), pack_bf16_rn(f[12], f[13]),
+                                    pack_bf16_rn(f[14], f[15]));
+        store16(tok + 448 + (lane - 28) * 32, r0, a.st16 != 0);
+        store16(tok + 448 + (lane - 28) * 32 + 16, r1, a.st16 != 0);
     }
     if (lane == 0)
         *reinterpret_cast<uint2 *>(block + static_cast<int64_t>(a.block_size) * 576 + pos * 8) = make_uint2(sc_lo, sc_hi);
+}
+
+template <typename T, bool FP8>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32) write_ds_mla_cache_kernel(const WriterArgs a) {
+    constexpr int V = Lane16<T>::kVecs;
+    const int lane = threadIdx.x & 31;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * kWarpsPerBlock;
+    int64_t row = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
+    if (row >= a.rows) return;
+    uint4 raw[V];
+    int64_t slot = slot_of(a, row);
+    Lane16<T>::load(a.x + row * a.x_row_bytes, lane, a.wide != 0, raw);
+    while (true) {
+        const int64_t next = row + stride;
+        uint4 raw_next[V];
+        int64_t slot_next = -1;
+        if (next < a.rows) {
+            slot_next = slot_of(a, next);
+            Lane16<T>::load(a.x + next * a.x_row_bytes, lane, a.wide != 0, raw_next);
+        }
+        if (slot >= 0 && slot < a.num_slots) {             // padding rows of a batch carry slot -1
+            float f[16];
+            Lane16<T>::unpack(raw, f);
+            if constexpr (FP8) encode_fp8(a, f, slot, lane);
+            else encode_int8(a, f, slot, lane);
+        }
+        if (next >= a.rows) break;
+#pragma unroll
+        for (int v = 0; v < V; ++v) raw[v] = raw_next[v];
+        slot = slot_next;
+        row = next;
+    }
 }
 
 int check_common(const void *x, int x_dtype, int64_t rows, int64_t x_row_stride, const void *slots, void *cache,
@@ -259,24 +192,17 @@ int check_common(const void *x, int x_dtype, int64_t rows, int64_t x_row_stride,
     return SMLA_OK;
 }
 
-template <template <typename> class Launcher>
+template <bool FP8>
 int dispatch(int x_dtype, const WriterArgs &a, cudaStream_t stream) {
-    const int64_t blocks64 = (a.rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
-    if (blocks64 > 0x7FFFFFFFLL) return SMLA_ETOOBIG;
-    const dim3 grid(static_cast<unsigned>(blocks64)), block(kWarpsPerBlock * 32);
-    switch (x_dtype) {
-        case 0: Launcher<__nv_bfloat16>::run(grid, block, stream, a); break;
-        case 1: Launcher<__half>::run(grid, block, stream, a); break;
-        default: Launcher<float>::run(grid, block, stream, a); break;
-    }
-    return static_cast<int>(cudaGetLastError());
+    const void *kernel =
+        x_dtype == 0   ? reinterpret_cast<const void *>(&write_ds_mla_cache_kernel<__nv_bfloat16, FP8>)
+        : x_dtype == 1 ? reinterpret_cast<const void *>(&write_ds_mla_cache_kernel<__half, FP8>)
+                       : reinterpret_cast<const void *>(&write_ds_mla_cache_kernel<float, FP8>);
+    unsigned blocks = 0;
+    if (const int rc = row_kernel_blocks(kernel, a.rows, &blocks)) return rc;
+    void *args[] = {const_cast<WriterArgs *>(&a)};
+    return static_cast<int>(cudaLaunchKernel(kernel, dim3(blocks), dim3(kWarpsPerBlock * 32), args, 0, stream));
 }
-template <typename T> struct LaunchInt8 {
-    static void run(dim3 g, dim3 b, cudaStream_t s, const WriterArgs &a) { write_int8_ds_mla_kernel<T><<<g, b, 0, s>>>(a); }
-};
-template <typename T> struct LaunchFp8 {
-    static void run(dim3 g, dim3 b, cudaStream_t s, const WriterArgs &a) { write_fp8_ds_mla_kernel<T><<<g, b, 0, s>>>(a); }
-};
 
 }  // namespace
 
@@ -293,7 +219,7 @@ int launch_write_int8_ds_mla(const void *x, int x_dtype, int64_t rows, int64_t x
     a.block_stride = block_stride;
     a.pos_stride = pos_stride;
     a.scale_rule = scale_rule;
-    return dispatch<LaunchInt8>(x_dtype, a, stream);
+    return dispatch<false>(x_dtype, a, stream);
 }
 
 int launch_write_fp8_ds_mla(const void *x, int x_dtype, int64_t rows, int64_t x_row_stride, const void *slots,
@@ -310,7 +236,7 @@ int launch_write_fp8_ds_mla(const void *x, int x_dtype, int64_t rows, int64_t x_
     a.slots_i64 = slots_i64;
     a.block_stride = block_stride;
     a.pos_stride = 576;
-    return dispatch<LaunchFp8>(x_dtype, a, stream);
+    return dispatch<true>(x_dtype, a, stream);
 }
 
 }  // namespace smla

@@ -1,0 +1,141 @@
+// Row loaders and the int8_ds_mla code computation shared by the row quantizer and the cache writers.
+//
+// A warp owns a 512-element row; lane l owns the 16 consecutive elements [16 l, 16 l + 16): one
+// 256-bit load for 16-bit inputs (two for fp32) and one 16-byte store of the 16 output bytes.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+
+namespace smla {
+namespace rowcodec {
+
+__device__ __forceinline__ void ldg_nc_v8(const void *p, uint4 &lo, uint4 &hi) {
+    asm volatile("ld.global.nc.L1::no_allocate.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(lo.x), "=r"(lo.y), "=r"(lo.z), "=r"(lo.w), "=r"(hi.x), "=r"(hi.y), "=r"(hi.z), "=r"(hi.w)
+                 : "l"(p));
+}
+__device__ __forceinline__ uint4 ldg_nc_v4(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+// 32 bytes at p: one 256-bit request when p is 32-byte aligned (warp-uniform choice), else two of 128 bits.
+__device__ __forceinline__ void load32(const uint8_t *p, bool wide, uint4 &lo, uint4 &hi) {
+    if (wide) {
+        ldg_nc_v8(p, lo, hi);
+    } else {
+        lo = ldg_nc_v4(p);
+        hi = ldg_nc_v4(p + 16);
+    }
+}
+
+// The raw bytes of a lane's 16 elements (kept in flight while the previous row is processed) and
+// their conversion to fp32.
+template <typename T> struct Lane16;
+template <> struct Lane16<__nv_bfloat16> {
+    static constexpr int kVecs = 2;
+    static __device__ __forceinline__ void load(const uint8_t *row, int lane, bool wide, uint4 *raw) {
+        load32(row + lane * 32, wide, raw[0], raw[1]);
+    }
+    static __device__ __forceinline__ void unpack(const uint4 *raw, float *f) {
+        const uint32_t w[8] = {raw[0].x, raw[0].y, raw[0].z, raw[0].w, raw[1].x, raw[1].y, raw[1].z, raw[1].w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            f[2 * i] = __uint_as_float(w[i] << 16);
+            f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+        }
+    }
+};
+template <> struct Lane16<__half> {
+    static constexpr int kVecs = 2;
+    static __device__ __forceinline__ void load(const uint8_t *row, int lane, bool wide, uint4 *raw) {
+        load32(row + lane * 32, wide, raw[0], raw[1]);
+    }
+    static __device__ __forceinline__ void unpack(const uint4 *raw, float *f) {
+        const uint32_t w[8] = {raw[0].x, raw[0].y, raw[0].z, raw[0].w, raw[1].x, raw[1].y, raw[1].z, raw[1].w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float2 p = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
+            f[2 * i] = p.x;
+            f[2 * i + 1] = p.y;
+        }
+    }
+};
+template <> struct Lane16<float> {
+    static constexpr int kVecs = 4;
+    static __device__ __forceinline__ void load(const uint8_t *row, int lane, bool wide, uint4 *raw) {
+        load32(row + lane * 64, wide, raw[0], raw[1]);
+        load32(row + lane * 64 + 32, wide, raw[2], raw[3]);
+    }
+    static __device__ __forceinline__ void unpack(const uint4 *raw, float *f) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            f[4 * i] = __uint_as_float(raw[i].x);
+            f[4 * i + 1] = __uint_as_float(raw[i].y);
+            f[4 * i + 2] = __uint_as_float(raw[i].z);
+            f[4 * i + 3] = __uint_as_float(raw[i].w);
+        }
+    }
+};
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+__device__ __forceinline__ uint32_t pack_low_bytes(const uint32_t *y) {   // byte i of the result = low byte of y[i]
+    const uint32_t lo = __byte_perm(y[0], y[1], 0x0040);
+    const uint32_t hi = __byte_perm(y[2], y[3], 0x0040);
+    return __byte_perm(lo, hi, 0x5410);
+}
+
+// The 16 codes clamp(rint(f[i] / s), -127, 127) of a lane, packed four to a word, BIT-EXACT with IEEE
+// fp32 division followed by round-half-even -- without dividing, except near a rounding tie.
+//
+// For |f / s| <= 127.0001 (s is the row scale, about amax / 127) the product q0 = f * RN(1 / s) is
+// within |f / s| * (2^-23 + 2^-48) < 2^-16 of the true quotient t, and the correctly rounded quotient
+// RN(t) within half an ulp (<= 2^-18 below 128) of it.  When q0 lies at least 2^-15 away from every
+// half-integer, t, RN(t) and q0 therefore sit strictly between the same two half-integers and round to
+// the same integer; a lane with an element closer than that (six in 10^5) recomputes its 16 codes with
+// true divisions.  Clamping first is the same as clamping last, both bounds being integers, and the
+// rounding is one addition of 1.5 * 2^23 (round-half-even by the adder), which also leaves the code in
+// the low byte of the sum.
+__device__ __forceinline__ void int8_codes16(const float *f, float s, uint32_t *w) {
+    constexpr float kMagic = 12582912.0f;                     // 1.5 * 2^23
+    constexpr float kTie = 0.5f - 0x1p-15f;
+    const float r = __frcp_rn(s);
+    bool near_tie = false;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        uint32_t y[4];
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const float c = fminf(fmaxf(f[4 * j + b] * r, -127.0f), 127.0f);
+            const float sum = __fadd_rn(c, kMagic);
+            const float back = __fsub_rn(sum, kMagic);        // rint(c)
+            near_tie |= fabsf(__fsub_rn(c, back)) > kTie;
+            y[b] = __float_as_uint(sum);
+        }
+        w[j] = pack_low_bytes(y);
+    }
+    if (near_tie) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            uint32_t y[4];
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                const float c = fminf(fmaxf(__fdiv_rn(f[4 * j + b], s), -127.0f), 127.0f);
+                y[b] = __float_as_uint(__fadd_rn(c, kMagic));
+            }
+            w[j] = pack_low_bytes(y);
+        }
+    }
+}
+
+}  // namespace rowcodec
+}  // namespace smla

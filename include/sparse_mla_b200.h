@@ -145,7 +145,7 @@ SMLA_API int smla_sparse_mla_prefill(const smla_attn_params_t *params, void *str
  * (flash_mla/int8_sparse_mla.py:15-26): scale = max(amax|x|, 1e-12) / 127 and
  * q = clamp(rint(x / scale), -127, 127) in IEEE fp32.
  *   x: [rows, 512] of `x_dtype` (0 = bf16, 1 = fp16, 2 = fp32), `x_row_stride` elements apart;
- *   q: int8 [rows, 512] contiguous; scale: fp32 [rows]. */
+ *   q: int8 [rows, 512] contiguous, 16-byte aligned; scale: fp32 [rows]. */
 SMLA_API int smla_quantize_int8_ds_mla_rows(const void *x, int x_dtype, int64_t rows, int64_t x_row_stride,
                                    int8_t *q, float *scale, void *stream);
 

@@ -51,6 +51,12 @@ def _rows(n, seed, dtype):
         x[10, 128] = -448.0 * 2.0 ** -20
         x[11] = (6.0e3 if dtype == torch.float16 else 1e30) * torch.randn(512, generator=g).clamp(-3, 3)
         x[12] = 1e-38 * torch.randn(512, generator=g)        # subnormal-range values
+        x[13] = torch.arange(512) % 251 - 125.5               # scale 1: every quotient an exact tie
+        x[13, 0] = 127.0
+        x[14] = x[13] + (torch.arange(512) % 3 - 1.0) * 2.0 ** -17   # ... and just off the tie
+        x[14, 0] = 127.0
+        x[15] = (torch.arange(512) % 251 - 125.5) * 3.0       # scale 3: ties after an inexact division
+        x[15, 0] = 381.0
     return x.to(dtype)
 
 
@@ -92,6 +98,33 @@ def test_fp8_writer_matches_oracle(fm, dtype, block_size, slot_dtype):
     oracle.write_fp8_ds_mla(ref, x.float().numpy(), slots.cpu().numpy())
     got = cache.cpu().numpy()
     assert np.array_equal(got, ref), f"{np.argwhere(got != ref)[:8]}"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_int8_codes_bit_exact_at_scale(fm, dtype):
+    """2^16 rows (33 M codes) of mixed magnitude against IEEE division + round-half-even on the CPU:
+    the kernels get their codes from a reciprocal multiply and divide only near a rounding tie, so
+    this is the check that the short cut never shows.  Rows are scaled so that many quotients land on
+    or next to half-integers."""
+    n = 1 << 16
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn(n, 512, generator=g, device="cuda") * torch.exp2(torch.randint(-20, 21, (n, 1), generator=g, device="cuda").float())
+    # every fourth row: multiples of half the scale -> exact ties wherever the multiple is odd
+    k = torch.randint(-254, 255, (n // 4, 512), generator=g, device="cuda").float()
+    k[:, 0] = 254.0
+    step = torch.rand(n // 4, 1, generator=g, device="cuda") + 0.5
+    x[::4] = k * step * 0.5
+    x = x.to(dtype)
+    qo, so = oracle.quantize_int8_rows(x.float().cpu().numpy())
+    q, s = fm.quantize_int8_ds_mla_rows(x)
+    assert np.array_equal(s.cpu().numpy(), so)
+    assert np.array_equal(q.cpu().numpy(), qo)
+    cache = torch.zeros(n // 64, 64, 528, dtype=torch.uint8, device="cuda")
+    slots = torch.randperm(n, generator=g, device="cuda")
+    fm.write_int8_ds_mla_cache(x, slots, cache)
+    data, scale = fm.int8_ds_mla_cache_views(cache)
+    assert np.array_equal(data.reshape(-1, 512)[slots].cpu().numpy(), qo)
+    assert np.array_equal(scale.reshape(-1)[slots].cpu().numpy(), so)
 
 
 def test_writers_strided_rows_and_alignment_paths(fm):
