@@ -46,8 +46,9 @@ struct WriterArgs {
     uint8_t *cache;
     int64_t block_stride;      // bytes
     int64_t pos_stride;        // bytes between the tokens of a block (int8 format)
-    int block_size;
-    int64_t num_slots;         // num_blocks * block_size
+    uint32_t block_size;
+    int block_shift;           // log2(block_size) when it is a power of two, else -1
+    int64_t num_slots;         // num_blocks * block_size, below 2^31
     int scale_rule;            // int8 format: 0 = max(amax, 1e-12) / 127, 1 = max(amax / 127, 1e-12)
     int wide;                  // rows are 32-byte aligned: 256-bit loads
     int st16;                  // fp8 format: blocks are 16-byte aligned (else 8-byte stores)
@@ -59,6 +60,18 @@ __device__ __forceinline__ void store16(uint8_t *p, const uint4 &v, bool st16) {
     } else {
         *reinterpret_cast<uint2 *>(p) = make_uint2(v.x, v.y);
         *reinterpret_cast<uint2 *>(p + 8) = make_uint2(v.z, v.w);
+    }
+}
+
+// slot -> (block, position); 32-bit arithmetic (a 64-bit division costs as much as encoding the row).
+__device__ __forceinline__ void split_slot(const WriterArgs &a, int64_t slot, uint32_t &blk, uint32_t &pos) {
+    const uint32_t s32 = static_cast<uint32_t>(slot);
+    if (a.block_shift >= 0) {
+        blk = s32 >> a.block_shift;
+        pos = s32 & (a.block_size - 1u);
+    } else {
+        blk = s32 / a.block_size;
+        pos = s32 - blk * a.block_size;
     }
 }
 
@@ -77,7 +90,9 @@ __device__ __forceinline__ void encode_int8(const WriterArgs &a, const float *f,
                                       : fmaxf(__fdiv_rn(amax, 127.0f), 1e-12f);
     uint32_t w[4];
     rowcodec::int8_codes16(f, s, w);
-    uint8_t *tok = a.cache + (slot / a.block_size) * a.block_stride + (slot % a.block_size) * a.pos_stride;
+    uint32_t blk, pos;
+    split_slot(a, slot, blk, pos);
+    uint8_t *tok = a.cache + blk * a.block_stride + pos * a.pos_stride;
     *reinterpret_cast<uint4 *>(tok + lane * 16) = make_uint4(w[0], w[1], w[2], w[3]);
     if (lane == 0) *reinterpret_cast<uint4 *>(tok + 512) = make_uint4(__float_as_uint(s), 0u, 0u, 0u);
 }
@@ -117,10 +132,10 @@ __device__ __forceinline__ void encode_fp8(const WriterArgs &a, const float *f, 
         if (g < 4) sc_lo |= byte << (8 * g);
         else sc_hi |= byte << (8 * (g - 4));
     }
-    const int64_t blk = slot / a.block_size;
-    const int pos = static_cast<int>(slot % a.block_size);
+    uint32_t blk, pos;
+    split_slot(a, slot, blk, pos);
     uint8_t *block = a.cache + blk * a.block_stride;
-    uint8_t *tok = block + static_cast<int64_t>(pos) * 576;
+    uint8_t *tok = block + pos * 576u;
     if (lane < 28) {
         const float inv = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);     // 2^-e, exact
         uint4 w;
@@ -186,7 +201,9 @@ int check_common(const void *x, int x_dtype, int64_t rows, int64_t x_row_stride,
     a.x_row_bytes = x_row_stride * elem;
     a.slots = slots;
     a.cache = static_cast<uint8_t *>(cache);
-    a.block_size = block_size;
+    if (num_blocks * block_size > 0x7FFFFFFFll) return SMLA_ETOOBIG;     // more tokens than any device holds
+    a.block_size = static_cast<uint32_t>(block_size);
+    a.block_shift = (block_size & (block_size - 1)) ? -1 : __builtin_ctz(static_cast<unsigned>(block_size));
     a.num_slots = num_blocks * block_size;
     a.wide = !(reinterpret_cast<uintptr_t>(x) & 31u) && !(a.x_row_bytes & 31);
     return SMLA_OK;

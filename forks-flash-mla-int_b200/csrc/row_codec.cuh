@@ -95,35 +95,52 @@ __device__ __forceinline__ uint32_t pack_low_bytes(const uint32_t *y) {   // byt
 }
 
 // The 16 codes clamp(rint(f[i] / s), -127, 127) of a lane, packed four to a word, BIT-EXACT with IEEE
-// fp32 division followed by round-half-even -- without dividing, except near a rounding tie.
+// fp32 division followed by round-half-even -- without a division instruction sequence per element.
 //
-// For |f / s| <= 127.0001 (s is the row scale, about amax / 127) the product q0 = f * RN(1 / s) is
-// within |f / s| * (2^-23 + 2^-48) < 2^-16 of the true quotient t, and the correctly rounded quotient
-// RN(t) within half an ulp (<= 2^-18 below 128) of it.  When q0 lies at least 2^-15 away from every
-// half-integer, t, RN(t) and q0 therefore sit strictly between the same two half-integers and round to
-// the same integer; a lane with an element closer than that (six in 10^5) recomputes its 16 codes with
-// true divisions.  Clamping first is the same as clamping last, both bounds being integers, and the
-// rounding is one addition of 1.5 * 2^23 (round-half-even by the adder), which also leaves the code in
-// the low byte of the sum.
+// s is the row scale (amax / 127 up to rounding, at least 7.8e-15), so |f / s| <= 127 (1 + 2^-23) and
+// the clamp never acts: rint alone gives +-127 at the ends.  Rounding is one addition of 1.5 * 2^23
+// (round-half-even by the adder), which leaves the code in the low byte of the sum.
+//
+// Far from a tie.  q0 = f * RN(1 / s) is within |f / s| (2^-23 + 2^-48) < 2^-16 of the true quotient
+// t, and RN(t) within half an ulp (<= 2^-18 below 128).  When q0 lies at least 2^-15 away from every
+// half-integer, t, RN(t) and q0 sit strictly between the same two half-integers: rint(q0) is the code.
+//
+// Near a tie (about 1 % of the elements of bf16 rows, whose quotients are ratios of 8-bit
+// significands) the correctly rounded quotient itself is needed.  One Newton step
+// q1 = q0 + (f - q0 s) / s lands on it or next to it, and the residual e = f - q1 s, which one FMA
+// delivers EXACTLY when q1 is within an ulp of t, proves which: t - q1 = e / s, so RN(t) = q1 if and
+// only if |e| < (ulp(q1) / 2) s (q1 not a power of two; a quotient is never a midpoint).  Anything
+// else -- the proof failing, |q1| = 0.5 -- sends the lane to true divisions; that path is there for
+// rigour and practically never runs.
 __device__ __forceinline__ void int8_codes16(const float *f, float s, uint32_t *w) {
     constexpr float kMagic = 12582912.0f;                     // 1.5 * 2^23
     constexpr float kTie = 0.5f - 0x1p-15f;
     const float r = __frcp_rn(s);
-    bool near_tie = false;
+    bool unsure = false;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         uint32_t y[4];
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
-            const float c = fminf(fmaxf(f[4 * j + b] * r, -127.0f), 127.0f);
-            const float sum = __fadd_rn(c, kMagic);
-            const float back = __fsub_rn(sum, kMagic);        // rint(c)
-            near_tie |= fabsf(__fsub_rn(c, back)) > kTie;
+            const float x = f[4 * j + b];
+            const float q0 = x * r;
+            float sum = __fadd_rn(q0, kMagic);
+            const float back = __fsub_rn(sum, kMagic);        // rint(q0)
+            const bool near_tie = fabsf(__fsub_rn(q0, back)) > kTie;
+            if (__any_sync(0xffffffffu, near_tie)) {          // warp-uniform: skipped for most elements
+                if (near_tie) {
+                    const float q1 = __fmaf_rn(__fmaf_rn(-q0, s, x), r, q0);
+                    const float e = __fmaf_rn(-q1, s, x);
+                    const float half_ulp_s = s * __uint_as_float((__float_as_uint(q1) & 0x7F800000u) - (24u << 23));
+                    unsure |= !(fabsf(e) < half_ulp_s) || fabsf(q1) == 0.5f;
+                    sum = __fadd_rn(q1, kMagic);
+                }
+            }
             y[b] = __float_as_uint(sum);
         }
         w[j] = pack_low_bytes(y);
     }
-    if (near_tie) {
+    if (unsure) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             uint32_t y[4];
