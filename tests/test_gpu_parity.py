@@ -684,3 +684,35 @@ def test_prefill_int8_causal_config4_reduced(fm):
     ref = oracle_out(kw["q"], swa_K, kw["swa_indices"], kw["swa_lens"], extra_K, kw["extra_indices"], kw["extra_lens"],
                      sink=kw["attn_sink"], tokens=toks)
     assert_attention_close(out, ref, "config 4 reduced", tokens=toks)
+
+
+def test_host_pipeline_matches_plain_calls(fm):
+    """Steps staggered over three streams (copy in / kernel / copy out) with buffers reused every
+    third step give, for every step, the output of the plain call on that step's inputs."""
+    from flash_mla.host_pipeline import HostPipeline
+    T, H, n, topk = 16, 64, 2048, 512
+    g = torch.Generator().manual_seed(77)
+    cache, _ = fp8_cache_from_latent(torch.randn(n, 512, generator=g).numpy(), 64)
+    lens = torch.randint(1, topk + 1, (T,), generator=g, dtype=torch.int32)
+    steps = []
+    for _ in range(8):
+        steps.append({"q": torch.randn(T, H, 512, generator=g).to(torch.bfloat16).pin_memory(),
+                      "swa_indices": torch.randint(0, n, (T, topk), generator=g, dtype=torch.int32).pin_memory(),
+                      "swa_lens": lens.clone().pin_memory()})
+
+    def run(dev, i):
+        return fm.sparse_mla_decode_fp8(dev["q"], cache, dev["swa_indices"], dev["swa_lens"], scale=SCALE)
+
+    example = {k: v.cuda() for k, v in steps[0].items()}
+    want = [run({k: v.cuda() for k, v in st.items()}, 0).cpu() for st in steps]
+    pipe = HostPipeline(run, example, want[0].cuda(), depth=3)
+    got = []
+    for i, st in enumerate(steps):
+        t = pipe.submit(i, st)
+        if i >= 2:                                     # read step i-2 before its slot comes round again
+            got.append(pipe.result((i - 2) % 3).clone())
+    pipe.drain()
+    got += [pipe.result(6 % 3).clone(), pipe.result(7 % 3).clone()]
+    assert len(got) == len(want)
+    for i, (a, b) in enumerate(zip(got, want)):
+        assert torch.equal(a, b), f"step {i}"
