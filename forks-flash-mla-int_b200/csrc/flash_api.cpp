@@ -104,7 +104,8 @@ Tensor sparse_mla_forward(const char *what, bool int8, bool prefill, const Tenso
                           const std::optional<Tensor> &swa_scale, const Tensor &swa_indices,
                           const Tensor &swa_lens, double scale, const std::optional<Tensor> &attn_sink,
                           const std::optional<Tensor> &extra_cache, const std::optional<Tensor> &extra_scale,
-                          const std::optional<Tensor> &extra_indices, const std::optional<Tensor> &extra_lens) {
+                          const std::optional<Tensor> &extra_indices, const std::optional<Tensor> &extra_lens,
+                          const Tensor *out_given = nullptr, const std::optional<Tensor> *ws_given = nullptr) {
     STD_TORCH_CHECK(q_in.is_cuda(), "q must be on CUDA");
     STD_TORCH_CHECK(q_in.dim() == 3, "q must have shape (num_tokens, num_heads, 512)");
     STD_TORCH_CHECK(q_in.size(2) == 512, "head_dim must be 512");
@@ -115,7 +116,15 @@ Tensor sparse_mla_forward(const char *what, bool int8, bool prefill, const Tenso
     const Tensor q = as_kernel_q(q_in);
     const int64_t T = q.size(0), H = q.size(1);
     STD_TORCH_CHECK(H >= 1, "q must have at least one head");
-    Tensor out = torch::stable::new_empty(q, {T, H, 512});
+    if (out_given) {
+        const Tensor &o = *out_given;
+        STD_TORCH_CHECK(o.is_cuda() && o.get_device_index() == device && o.scalar_type() == ScalarType::BFloat16 &&
+                            o.dim() == 3 && o.size(0) == T && o.size(1) == H && o.size(2) == 512,
+                        "out must be a bfloat16 (num_tokens, num_heads, 512) tensor on q's device");
+        STD_TORCH_CHECK(o.stride(2) == 1 && o.stride(0) % 8 == 0 && o.stride(1) % 8 == 0 && aligned16(o),
+                        "out must have contiguous 16-byte aligned rows");
+    }
+    Tensor out = out_given ? *out_given : torch::stable::new_empty(q, {T, H, 512});
     if (T == 0) return out;
 
     smla_attn_params_t p = {};
@@ -159,7 +168,19 @@ Tensor sparse_mla_forward(const char *what, bool int8, bool prefill, const Tenso
         int splits = 1;
         size_t ws_bytes = 0;
         check_rc(smla_decode_plan(p.num_tokens, p.num_heads, width, &splits, &ws_bytes), "sparse-MLA decode plan");
-        if (splits > 1) {
+        if (ws_given) {            // planned call: the caller's scratch or none at all, nothing is allocated here
+            if (splits > 1 && ws_given->has_value()) {
+                const Tensor &w = ws_given->value();
+                STD_TORCH_CHECK(w.is_cuda() && w.get_device_index() == device && w.is_contiguous() && aligned16(w),
+                                "workspace must be a contiguous 16-byte aligned tensor on q's device");
+                STD_TORCH_CHECK(static_cast<size_t>(w.numel()) * w.element_size() >= ws_bytes,
+                                "workspace is smaller than the plan for this shape needs");
+                p.workspace = w.data_ptr();
+                p.workspace_bytes = static_cast<size_t>(w.numel()) * w.element_size();
+            } else {
+                splits = 1;
+            }
+        } else if (splits > 1) {
             workspace = torch::stable::new_empty(q, {static_cast<int64_t>((ws_bytes + 3) / 4)}, ScalarType::Float);
             p.workspace = workspace->data_ptr();
             p.workspace_bytes = ws_bytes;
@@ -196,6 +217,19 @@ Tensor fwd_sparse_int8_prefill_mla(Tensor q, Tensor swa_cache, Tensor swa_scale,
                                    std::optional<Tensor> extra_indices, std::optional<Tensor> extra_lens) {
     return sparse_mla_forward("sparse-MLA int8 prefill", true, true, q, swa_cache, swa_scale, swa_indices, swa_lens,
                               scale, attn_sink, extra_cache, extra_scale, extra_indices, extra_lens);
+}
+
+// Decode into caller-owned `out` with caller-owned split scratch (or none): no allocation in the call.
+// The cache format follows the cache dtype (int8 rows + scales, or uint8 fp8_ds_mla blocks).
+void fwd_sparse_decode_mla_planned(Tensor q, Tensor swa_cache, std::optional<Tensor> swa_scale, Tensor swa_indices,
+                                   Tensor swa_lens, double scale, std::optional<Tensor> attn_sink,
+                                   std::optional<Tensor> extra_cache, std::optional<Tensor> extra_scale,
+                                   std::optional<Tensor> extra_indices, std::optional<Tensor> extra_lens, Tensor out,
+                                   std::optional<Tensor> workspace) {
+    const bool int8 = swa_cache.scalar_type() == ScalarType::Char;
+    sparse_mla_forward(int8 ? "sparse-MLA int8 decode (planned)" : "sparse-MLA fp8 decode (planned)", int8, false, q,
+                       swa_cache, swa_scale, swa_indices, swa_lens, scale, attn_sink, extra_cache, extra_scale,
+                       extra_indices, extra_lens, &out, &workspace);
 }
 
 // k: [..., 512] bf16 / fp16 / fp32 on CUDA -> (int8 [..., 512], fp32 [...]).
@@ -320,6 +354,15 @@ void boxed_quantize(StableIValue *stack, uint64_t, uint64_t) {
     stack[1] = from(s);
 }
 
+void boxed_decode_planned(StableIValue *stack, uint64_t, uint64_t) {
+    fwd_sparse_decode_mla_planned(to<Tensor>(stack[0]), to<Tensor>(stack[1]), to<std::optional<Tensor>>(stack[2]),
+                                  to<Tensor>(stack[3]), to<Tensor>(stack[4]), to<double>(stack[5]),
+                                  to<std::optional<Tensor>>(stack[6]), to<std::optional<Tensor>>(stack[7]),
+                                  to<std::optional<Tensor>>(stack[8]), to<std::optional<Tensor>>(stack[9]),
+                                  to<std::optional<Tensor>>(stack[10]), to<Tensor>(stack[11]),
+                                  to<std::optional<Tensor>>(stack[12]));
+}
+
 void boxed_write_int8(StableIValue *stack, uint64_t, uint64_t) {
     write_ds_mla_cache("int8_ds_mla cache writer", false, to<Tensor>(stack[0]), to<Tensor>(stack[1]),
                        to<Tensor>(stack[2]), to<int64_t>(stack[3]));
@@ -346,6 +389,9 @@ STABLE_TORCH_LIBRARY(flash_mla, m) {
           "Tensor swa_indices, Tensor swa_lens, float scale, Tensor? attn_sink, "
           "Tensor? extra_cache, Tensor? extra_scale, Tensor? extra_indices, Tensor? extra_lens) -> Tensor");
     m.def("quantize_int8_ds_mla_rows(Tensor k) -> (Tensor, Tensor)");
+    m.def("fwd_sparse_decode_mla_planned(Tensor q, Tensor swa_cache, Tensor? swa_scale, Tensor swa_indices, "
+          "Tensor swa_lens, float scale, Tensor? attn_sink, Tensor? extra_cache, Tensor? extra_scale, "
+          "Tensor? extra_indices, Tensor? extra_lens, Tensor(a!) out, Tensor? workspace) -> ()");
     m.def("write_int8_ds_mla_cache(Tensor latent, Tensor slot_mapping, Tensor(a!) cache, int scale_rule) -> ()");
     m.def("write_fp8_ds_mla_cache(Tensor latent, Tensor slot_mapping, Tensor(a!) cache) -> ()");
 }
@@ -356,6 +402,7 @@ STABLE_TORCH_LIBRARY_IMPL(flash_mla, CUDA, m) {
     m.impl("fwd_sparse_int8_prefill_mla", &boxed_int8<true>);
     m.impl("fwd_sparse_int8_decode_mla", &boxed_int8<false>);
     m.impl("quantize_int8_ds_mla_rows", &boxed_quantize);
+    m.impl("fwd_sparse_decode_mla_planned", &boxed_decode_planned);
     m.impl("write_int8_ds_mla_cache", &boxed_write_int8);
     m.impl("write_fp8_ds_mla_cache", &boxed_write_fp8);
 }

@@ -20,6 +20,11 @@ from .cache_formats import (  # noqa: F401
     write_fp8_ds_mla_cache,
     write_int8_ds_mla_cache,
 )
+from .decode_plan import (  # noqa: F401
+    SparseMlaDecodePlan,
+    get_sparse_mla_decode_plan,
+    sparse_mla_decode_planned,
+)
 from .int8_sparse_mla import (  # noqa: F401
     quantize_int8_ds_mla_rows,
     sparse_mla_decode_int8,
@@ -35,4 +40,7 @@ __all__ = [
     "write_fp8_ds_mla_cache",
     "write_int8_ds_mla_cache",
     "int8_ds_mla_cache_views",
+    "get_sparse_mla_decode_plan",
+    "sparse_mla_decode_planned",
+    "SparseMlaDecodePlan",
 ]

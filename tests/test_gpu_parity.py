@@ -716,3 +716,60 @@ def test_host_pipeline_matches_plain_calls(fm):
     assert len(got) == len(want)
     for i, (a, b) in enumerate(zip(got, want)):
         assert torch.equal(a, b), f"step {i}"
+
+
+@pytest.mark.parametrize("fmt", ["fp8", "int8"])
+@pytest.mark.parametrize("T", [1, 8, 48, 200])
+def test_planned_decode_allocates_nothing_and_replays(fm, fmt, T):
+    """Decode through a plan made once per shape (the counterpart of the split planning the reference
+    does inside each call, csrc/flash_api.cpp:75-102,381-405): same results as the plain op for both
+    cache formats and every merge form, no allocation inside the call, and a captured CUDA graph that
+    follows new contents of the same input buffers."""
+    H, n, topk, etopk = 64, 4096, 256, 128
+    g = torch.Generator().manual_seed(100 + T)
+    lat = torch.randn(n, 512, generator=g).numpy()
+    if fmt == "fp8":
+        cache, _ = fp8_cache_from_latent(lat, 64)
+        caches = dict(swa_cache=cache, extra_cache=cache)
+        plain = fm.sparse_mla_decode_fp8
+    else:
+        data, scale, _, _ = int8_cache_from_latent(lat, 64, "inline528")
+        caches = dict(swa_cache=data, swa_scale=scale, extra_cache=data, extra_scale=scale)
+        plain = fm.sparse_mla_decode_int8
+
+    def inputs():
+        return dict(q=torch.randn(T, H, 512, generator=g).to(torch.bfloat16).cuda(),
+                    swa_indices=torch.randint(0, n, (T, topk), generator=g, dtype=torch.int32).cuda(),
+                    swa_lens=torch.randint(1, topk + 1, (T,), generator=g, dtype=torch.int32).cuda(),
+                    extra_indices=torch.randint(-1, n, (T, etopk), generator=g, dtype=torch.int32).cuda(),
+                    extra_lens=torch.randint(0, etopk + 1, (T,), generator=g, dtype=torch.int32).cuda())
+
+    sink = torch.randn(H, generator=g).cuda()
+    plan = fm.get_sparse_mla_decode_plan(T, H, topk + etopk)
+    assert plan.out.shape == (T, H, 512) and (plan.workspace is None) == (plan.num_splits == 1)
+    a = inputs()
+    want = plain(a["q"], scale=SCALE, attn_sink=sink, **{k: v for k, v in a.items() if k != "q"}, **caches)
+    torch.cuda.synchronize()
+    before = torch.cuda.memory_allocated()
+    got = fm.sparse_mla_decode_planned(plan, scale=SCALE, attn_sink=sink, **a, **caches)
+    assert torch.cuda.memory_allocated() == before
+    assert got.data_ptr() == plan.out.data_ptr() and torch.equal(got, want)
+
+    # capture once, replay on new contents of the same buffers
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        fm.sparse_mla_decode_planned(plan, scale=SCALE, attn_sink=sink, **a, **caches)
+    torch.cuda.current_stream().wait_stream(side)
+    with torch.cuda.graph(graph):
+        fm.sparse_mla_decode_planned(plan, scale=SCALE, attn_sink=sink, **a, **caches)
+    for _ in range(3):
+        b = inputs()
+        for k in a:
+            a[k].copy_(b[k])
+        graph.replay()
+        want = plain(b["q"], scale=SCALE, attn_sink=sink, **{k: v for k, v in b.items() if k != "q"}, **caches)
+        assert torch.equal(plan.out, want)
+    with pytest.raises(ValueError):
+        fm.sparse_mla_decode_planned(plan, **{**a, "q": a["q"][:, :32]}, **caches)
