@@ -215,6 +215,39 @@ def test_writers_through_c_abi(fm):
         fm.write_int8_ds_mla_cache(x, slots, cf)
 
 
+def test_writers_edge_shapes(fm):
+    """No rows, only skipped rows, blocks with padding between them (block stride larger than the
+    tokens need), and a slot count no device could hold."""
+    from flash_mla import c_abi
+    lib = c_abi.load()
+    st = torch.cuda.current_stream().cuda_stream
+    bs, nb = 8, 6
+    for tb, write, owrite in ((528, fm.write_int8_ds_mla_cache, oracle.write_int8_inline528),
+                              (584, fm.write_fp8_ds_mla_cache, oracle.write_fp8_ds_mla)):
+        cache = torch.full((nb, bs, tb), FILL, dtype=torch.uint8, device="cuda")
+        write(torch.empty(0, 512, dtype=torch.bfloat16, device="cuda"), torch.empty(0, dtype=torch.int64, device="cuda"), cache)
+        x = _rows(40, 9, torch.bfloat16).cuda()
+        write(x, torch.full((40,), -1, dtype=torch.int64, device="cuda"), cache)
+        write(x, torch.full((40,), nb * bs, dtype=torch.int32, device="cuda"), cache)
+        assert bool((cache == FILL).all())
+        # every second block of a larger allocation: block stride = 2 * bs * tb
+        big = torch.full((2 * nb, bs, tb), FILL, dtype=torch.uint8, device="cuda")
+        view = big[::2]
+        slots = _slots(40, nb * bs, 10, torch.int64)
+        write(x, slots, view)
+        ref = np.full((nb, bs, tb), FILL, np.uint8)
+        owrite(ref, x.float().cpu().numpy(), slots.cpu().numpy())
+        assert np.array_equal(view.cpu().numpy(), ref)
+        assert bool((big[1::2] == FILL).all())
+    x = _rows(40, 9, torch.bfloat16).cuda()
+    slots = _slots(40, 48, 10, torch.int64)
+    ETOOBIG = -5
+    assert lib.smla_write_int8_ds_mla_cache(x.data_ptr(), 0, 40, 512, slots.data_ptr(), 1, big.data_ptr(), 1 << 26, 64,
+                                            64 * 528, 528, 0, st) == ETOOBIG
+    assert lib.smla_write_fp8_ds_mla_cache(x.data_ptr(), 0, 40, 512, slots.data_ptr(), 1, big.data_ptr(), 1 << 26, 64,
+                                           64 * 584, st) == ETOOBIG
+
+
 def _dequant_fp8_torch(cache):
     nb, bs, _ = cache.shape
     flat = cache.view(nb, bs * 584)
