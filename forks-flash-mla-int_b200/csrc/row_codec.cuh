@@ -82,10 +82,10 @@ template <> struct Lane16<float> {
     }
 };
 
+// Maximum over the warp of a NON-NEGATIVE float: the bit patterns order like the values, so one
+// integer warp reduction does it.
 __device__ __forceinline__ float warp_max(float v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-    return v;
+    return __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(v)));
 }
 
 __device__ __forceinline__ uint32_t pack_low_bytes(const uint32_t *y) {   // byte i of the result = low byte of y[i]
@@ -112,31 +112,66 @@ __device__ __forceinline__ uint32_t pack_low_bytes(const uint32_t *y) {   // byt
 // only if |e| < (ulp(q1) / 2) s (q1 not a power of two; a quotient is never a midpoint).  Anything
 // else -- the proof failing, |q1| = 0.5 -- sends the lane to true divisions; that path is there for
 // rigour and practically never runs.
+// Packed fp32 pairs (sm_100 has two-wide fp32 add / mul / fma on 64-bit register pairs).
+__device__ __forceinline__ uint64_t f32x2(float lo, float hi) {
+    uint64_t v;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "f"(lo), "f"(hi));
+    return v;
+}
+__device__ __forceinline__ void split_f32x2(uint64_t v, float &lo, float &hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t mul_f32x2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+
 __device__ __forceinline__ void int8_codes16(const float *f, float s, uint32_t *w) {
     constexpr float kMagic = 12582912.0f;                     // 1.5 * 2^23
     constexpr float kTie = 0.5f - 0x1p-15f;
     const float r = __frcp_rn(s);
+    const uint64_t rr = f32x2(r, r), magic2 = f32x2(kMagic, kMagic), neg_magic2 = f32x2(-kMagic, -kMagic),
+                   neg_one2 = f32x2(-1.0f, -1.0f);
     bool unsure = false;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         uint32_t y[4];
 #pragma unroll
-        for (int b = 0; b < 4; ++b) {
-            const float x = f[4 * j + b];
-            const float q0 = x * r;
-            float sum = __fadd_rn(q0, kMagic);
-            const float back = __fsub_rn(sum, kMagic);        // rint(q0)
-            const bool near_tie = fabsf(__fsub_rn(q0, back)) > kTie;
-            if (__any_sync(0xffffffffu, near_tie)) {          // warp-uniform: skipped for most elements
-                if (near_tie) {
-                    const float q1 = __fmaf_rn(__fmaf_rn(-q0, s, x), r, q0);
-                    const float e = __fmaf_rn(-q1, s, x);
-                    const float half_ulp_s = s * __uint_as_float((__float_as_uint(q1) & 0x7F800000u) - (24u << 23));
-                    unsure |= !(fabsf(e) < half_ulp_s) || fabsf(q1) == 0.5f;
-                    sum = __fadd_rn(q1, kMagic);
+        for (int h = 0; h < 2; ++h) {
+            // two elements at a time: q0 = x r, sum = q0 + magic, back = sum - magic = rint(q0), d = q0 - back
+            const uint64_t q2 = mul_f32x2(f32x2(f[4 * j + 2 * h], f[4 * j + 2 * h + 1]), rr);
+            const uint64_t sum2 = add_f32x2(q2, magic2);
+            const uint64_t d2 = fma_f32x2(add_f32x2(sum2, neg_magic2), neg_one2, q2);
+            float q0[2], sum[2], d[2];
+            split_f32x2(q2, q0[0], q0[1]);
+            split_f32x2(sum2, sum[0], sum[1]);
+            split_f32x2(d2, d[0], d[1]);
+#pragma unroll
+            for (int b = 0; b < 2; ++b) {
+                const bool near_tie = fabsf(d[b]) > kTie;
+                if (__any_sync(0xffffffffu, near_tie)) {      // warp-uniform: skipped for most elements
+                    if (near_tie) {
+                        const float x = f[4 * j + 2 * h + b];
+                        const float q1 = __fmaf_rn(__fmaf_rn(-q0[b], s, x), r, q0[b]);
+                        const float e = __fmaf_rn(-q1, s, x);
+                        const float half_ulp_s = s * __uint_as_float((__float_as_uint(q1) & 0x7F800000u) - (24u << 23));
+                        unsure |= !(fabsf(e) < half_ulp_s) || fabsf(q1) == 0.5f;
+                        sum[b] = __fadd_rn(q1, kMagic);
+                    }
                 }
+                y[2 * h + b] = __float_as_uint(sum[b]);
             }
-            y[b] = __float_as_uint(sum);
         }
         w[j] = pack_low_bytes(y);
     }
