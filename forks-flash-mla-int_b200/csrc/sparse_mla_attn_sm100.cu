@@ -210,14 +210,36 @@ __device__ __forceinline__ uint4 load16(const uint8_t *p, bool vec16) {
 }
 
 // 4 int8 -> 4 x bf16_rn(float(v) * scale).  float(v) is built exactly with the 2^23 magic.
+// Two-wide fp32 arithmetic on 64-bit register pairs (sm_100): half the issue slots of the scalar form.
+__device__ __forceinline__ uint64_t f32x2(float lo, float hi) {
+    uint64_t v;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "f"(lo), "f"(hi));
+    return v;
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(uint64_t v) {
+    float lo, hi;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+    return pack_bf16x2(lo, hi);
+}
+__device__ __forceinline__ uint64_t mul_f32x2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
 __device__ __forceinline__ void cvt_i8x4(uint32_t w, float s, uint32_t &lo, uint32_t &hi) {
     const uint32_t x = w ^ 0x80808080u;
-    const float f0 = (__uint_as_float(__byte_perm(x, 0x4B000000u, 0x7540)) - 8388736.0f) * s;
-    const float f1 = (__uint_as_float(__byte_perm(x, 0x4B000000u, 0x7541)) - 8388736.0f) * s;
-    const float f2 = (__uint_as_float(__byte_perm(x, 0x4B000000u, 0x7542)) - 8388736.0f) * s;
-    const float f3 = (__uint_as_float(__byte_perm(x, 0x4B000000u, 0x7543)) - 8388736.0f) * s;
-    lo = pack_bf16x2(f0, f1);
-    hi = pack_bf16x2(f2, f3);
+    const uint64_t ss = f32x2(s, s), bias = f32x2(-8388736.0f, -8388736.0f);
+    const uint64_t a = f32x2(__uint_as_float(__byte_perm(x, 0x4B000000u, 0x7540)),
+                             __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7541)));
+    const uint64_t b = f32x2(__uint_as_float(__byte_perm(x, 0x4B000000u, 0x7542)),
+                             __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7543)));
+    lo = pack_bf16x2(mul_f32x2(add_f32x2(a, bias), ss));
+    hi = pack_bf16x2(mul_f32x2(add_f32x2(b, bias), ss));
 }
 // 4 e4m3 -> 4 x bf16(e4m3 * 2^(ue8m0 - 127)); exact (power-of-two scaling of a 4-bit significand).
 __device__ __forceinline__ void cvt_e4m3x4(uint32_t w, float mult, uint32_t &lo, uint32_t &hi) {
@@ -225,8 +247,9 @@ __device__ __forceinline__ void cvt_e4m3x4(uint32_t w, float mult, uint32_t &lo,
     const __half2_raw b = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(w >> 16), __NV_E4M3);
     const float2 fa = __half22float2(*reinterpret_cast<const __half2 *>(&a));
     const float2 fb = __half22float2(*reinterpret_cast<const __half2 *>(&b));
-    lo = pack_bf16x2(fa.x * mult, fa.y * mult);
-    hi = pack_bf16x2(fb.x * mult, fb.y * mult);
+    const uint64_t mm = f32x2(mult, mult);
+    lo = pack_bf16x2(mul_f32x2(f32x2(fa.x, fa.y), mm));
+    hi = pack_bf16x2(mul_f32x2(f32x2(fb.x, fb.y), mm));
 }
 
 // Column reduction across the 32 lanes of a warp: every lane holds L values (one per column);
