@@ -12,6 +12,13 @@ tests/test_sparse_mla_prefill_int8_adversarial.py:44-74): 512 int8 per token plu
 fp32 scale; ``K[d] = bf16_rn(float(int8[d]) * scale)``.  The production container is a
 528-byte token (512 payload, fp32 scale at +512, 12 pad bytes).
 
+Cache writers (``write_fp8_ds_mla``, ``write_int8_inline528``): the reference has no writer, only
+test-side packers that take the fp8 exponents as given, so the exponent rule here
+(``ue8m0_exponents``: the smallest power of two that keeps the group within +-448) is this project's
+own and is pinned only through the format: rows the reference's packers produced re-encode to caches
+that dequantise to the same rows (tests/test_gpu_cache_writers.py), and the int8 tokens are the
+reference quantizer's known answers laid out as its tests describe the serving engine's token.
+
 Row quantizer (reference: flash_mla/int8_sparse_mla.py:15-26):
 ``scale = max(amax|x|, 1e-12) / 127`` and ``q = clamp(rint(x / scale), -127, 127)``, all in
 IEEE fp32 with true division and round-half-even.
