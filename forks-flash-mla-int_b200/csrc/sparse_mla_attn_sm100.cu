@@ -121,6 +121,7 @@ struct StreamDev {
     const int *lens;
     long long idx_stride, block_stride, pos_stride, scale_block_stride, scale_pos_stride;
     int topk, num_slots, block_size;
+    int block_shift;   // log2(block_size) when it is a power of two, else -1
     int vec;   // widest aligned load of a row piece: 2 = 32 bytes, 1 = 16 bytes, 0 = 8 (fp8) / 4 (int8) bytes
 };
 
@@ -334,7 +335,8 @@ __device__ __forceinline__ RowRef<FMT> make_row_ref(const KernelArgs &a, int ns,
     if (g >= n) return r;
     const StreamDev &s = (g < ns) ? a.swa : a.extra;
     if (static_cast<unsigned>(id) >= static_cast<unsigned>(s.num_slots)) return r;
-    const int b = id / s.block_size;
+    // id is a valid slot here (0 <= id < num_slots); paged caches use power-of-two blocks as a rule
+    const int b = s.block_shift >= 0 ? (id >> s.block_shift) : id / s.block_size;
     const int i = id - b * s.block_size;
     const uint8_t *blk = s.cache + static_cast<long long>(b) * s.block_stride;
     r.ok = true;
@@ -1603,6 +1605,7 @@ int fill_stream(const smla_stream_t &s, int fmt, StreamDev &d) {
     if (slots > 0x7FFFFFFFLL) return SMLA_ETOOBIG;
     d.num_slots = static_cast<int>(slots);
     d.block_size = s.block_size;
+    d.block_shift = (s.block_size & (s.block_size - 1)) ? -1 : __builtin_ctz(static_cast<unsigned>(s.block_size));
     const uintptr_t base = reinterpret_cast<uintptr_t>(s.cache);
     if (fmt == SMLA_FP8_DS_MLA) {
         if ((base & 7u) || (s.block_stride & 7)) return SMLA_EALIGN;
