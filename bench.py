@@ -415,7 +415,7 @@ def run_reference(args_ns):
 
 
 # attention-kernel DRAM traffic per launch measured with ncu (profiles/sparse_mla_fwd_kernel_fp8_decode_T128_H64.md)
-NCU_DRAM_TRAFFIC_BYTES = {"dsv4_fp8_decode_T128_H64": 43.2e6,
+NCU_DRAM_TRAFFIC_BYTES = {"dsv4_fp8_decode_T128_H64": 42.5e6, "dsv4_int8_decode_T128_H64": 40.0e6,
                           # row kernels: captured on 2^18 rows, scaled by 4 (profiles/write_ds_mla_cache_kernel_262144_rows.md,
                           # profiles/quantize_int8_rows_kernel_262144_rows.md)
                           "write_int8_cache_rows1M": 1543.6e6, "write_fp8_cache_rows1M": 1567.9e6,
