@@ -101,7 +101,20 @@ constexpr int kKBytes = 16 * kRowGroupBytes;     // 128 rows
 constexpr int kTmemCols = 512;
 constexpr int kTmemOCol = 64;                    // O^T chunks start here; S^T at column 0
 constexpr float kLog2e = 1.4426950408889634f;
-constexpr float kRescaleThreshold = 8.0f;        // log2 units: the reference max may lag by up to 2^8
+// The softmax reference m (log2 units, integer-valued) only has to keep 2^(s - m) inside the range of
+// bf16 / fp32, not near 1: a power-of-two offset changes no mantissa anywhere (P, the fp32 accumulators,
+// the denominators and the final quotient all scale exactly).  So m is set kRefHeadroom ABOVE the
+// maximum seen and is left alone until a score exceeds it by kRescaleThreshold: scores may grow by 2^100
+// after a segment's first tile (a few outlier rows among ordinary ones) before the accumulators are
+// rescaled, which stalls the tile pipeline (measured: 5 % outlier rows x50 cost 11 % with m kept at the
+// running maximum and an 8-unit threshold, 6 % now).  The bound on the sum: a rescale factor
+// 2^(m_old - m_new), or a merge weight 2^(m_i - M), multiplies terms that still matter (within 2^-24 of
+// the largest) only when its exponent is above -(kRescaleThreshold + kRefHeadroom + 24), which has to
+// stay a normal fp32 number (2^-126); with both at 80 the factor flushed to zero and took live
+// accumulators with it.
+constexpr float kRescaleThreshold = 60.0f;
+constexpr float kRefHeadroom = 40.0f;
+static_assert(kRescaleThreshold + kRefHeadroom + 24.0f <= 126.0f, "rescale factors must stay normal fp32 numbers");
 constexpr int kAllWorkersBar = 5;                // named barriers 1..4: the four column-slice groups
 // mbarrier slots
 constexpr int kBarReady = 0;   // [4] K chunk c holds this tile (16 arrivals: one per worker warp)
@@ -1416,7 +1429,7 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
                     // nothing has been accumulated yet, so there is nothing to rescale.
                     const bool sink_here = (sg[7] & kSegComplete) != 0 && a.sink != nullptr;
                     const bool up = first_tile ? (!sink_here || ceilf(tm) > m_old) : tm > m_old + kRescaleThreshold;
-                    const float m_new = up ? ceilf(tm) : m_old;
+                    const float m_new = up ? ceilf(tm) + kRefHeadroom : m_old;
                     alpha_s[col] = (up && !first_tile) ? fast_exp2(m_old - m_new) : 1.0f;
                     shift_s[col] = m_old - m_new;
                     m_s[col] = m_new;

@@ -399,6 +399,35 @@ def test_scores_jump_far_above_the_first_tile(fm):
             assert_attention_close(out, ref, f"score jump {op.__name__}")
 
 
+@pytest.mark.parametrize("plateau", [20.0, 39.0, 59.0, 79.0, 99.0, 119.0, 139.0, 159.0, 199.0])
+def test_score_staircase_keeps_terms_that_matter(fm, plateau):
+    """Five 128-row tiles whose scores sit at 0, `plateau`, `plateau` + 2.5, `plateau` + 2.5 and 0 log2
+    units (each row up to 3 units lower).  The kernel keeps its softmax reference far from the running
+    maximum and rescales its accumulators rarely, so for some plateau the second tile lands just inside
+    the window that needs no rescale and the third just outside it: the rescale factor is then tiny, but
+    the second tile's rows are only a few units below the final maximum and must keep their weight
+    (a factor that underflows loses them).  Same for the weights that merge partial segments.  q is
+    one-hot and the softmax scale is ln 2, so a row's score in log2 units is simply its first element."""
+    H, n = 64, 5 * 128
+    rng = np.random.default_rng(int(plateau))
+    k = (rng.standard_normal((n, 512)) * 4.0).astype(np.float32)
+    level = np.array([0.0, plateau, plateau + 2.5, plateau + 2.5, 0.0])[np.arange(n) // 128]
+    k[:, 0] = (level + rng.choice([0.0, -0.25, -0.5, -3.0], size=n)) / 8.0          # first element = score / 8
+    data, scale, K, _ = int8_cache_from_latent(k, 64, "inline528")
+    q = torch.zeros(3, H, 512, dtype=torch.bfloat16, device="cuda")
+    q[:, :, 0] = 8.0
+    idx = torch.arange(n, dtype=torch.int32, device="cuda").repeat(3, 1)
+    idx[1] = torch.flip(idx[1], dims=[0])
+    idx[2, 128:384] = idx[2, 128:384][torch.randperm(256, device="cuda")]      # the two upper plateaus mixed
+    lens = torch.full((3,), n, dtype=torch.int32, device="cuda")
+    ln2 = math.log(2.0)
+    for sink in (None, torch.full((H,), (plateau + 1.0) * ln2, device="cuda")):
+        ref = oracle_out(q, K, idx, lens, scale=ln2, sink=sink)
+        for op in (fm.sparse_mla_decode_int8, fm.sparse_mla_prefill_int8):
+            out = op(q, data, scale, idx, lens, scale=ln2, attn_sink=sink)
+            assert_attention_close(out, ref, f"plateau {plateau} {op.__name__}")
+
+
 @pytest.mark.parametrize("T", [96, 4])
 def test_decode_replays_from_a_cuda_graph(fm, T):
     """The serving engine captures decode in a CUDA graph and replays it with new contents in the same
