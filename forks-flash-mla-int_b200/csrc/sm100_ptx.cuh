@@ -216,6 +216,47 @@ __device__ __forceinline__ void umma_bf16_ss_lohi(uint32_t d_tmem, uint32_t a_lo
         : "r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// One lane of a converged warp (1 in that lane, 0 in the others).
+__device__ __forceinline__ uint32_t elect_one() {
+    uint32_t r;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(r));
+    return r;
+}
+// tcgen05.mma issued from warp-uniform code: every lane runs the surrounding loop and its descriptor
+// arithmetic (so the compiler keeps it on the uniform datapath), only the lane with `go` != 0 issues.
+// Measured with the other four warps of the scheduler busy with arithmetic: 90 cycles per MMA against
+// 500 for the same loop run by one lane inside a divergent branch.
+__device__ __forceinline__ void umma_bf16_ss_pred(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                  uint32_t accumulate, uint32_t go) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, g;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "setp.ne.b32 g, %5, 0;\n\t"
+        "@g tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}"
+        :
+        : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(go)
+        : "memory");
+}
+// umma_commit by the lane with `go` != 0 (same use as umma_bf16_ss_pred).
+__device__ __forceinline__ void umma_commit_pred(uint32_t bar, uint32_t go) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred g;\n\t"
+        "setp.ne.b32 g, %1, 0;\n\t"
+        "@g tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t"
+        "}"
+        :
+        : "r"(bar), "r"(go)
+        : "memory");
+}
 // Arrive on an mbarrier once every tcgen05 operation this thread issued so far has completed.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)

@@ -819,9 +819,19 @@ __device__ __forceinline__ bool wait_published(const int *sched, int k, volatile
     }
 }
 
-// ------------------------------------------------------------------ MMA issue (lane 0 of the MMA warp)
-// Walks the segments the workers publish.  Barrier phases are counted over the CTA's whole life:
-// `gt` tiles for the per-tile barriers, `so` segments for the two accumulator barriers.
+// ------------------------------------------------------------------ MMA issue (the MMA warp, all lanes)
+// Walks the segments the scheduler warp publishes.  Barrier phases are counted over the CTA's whole
+// life: `gt` tiles for the per-tile barriers, `so` segments for the two accumulator barriers.
+//
+// The whole warp runs this code and only the tcgen05 instructions themselves are predicated on one
+// elected lane.  A tcgen05.mma has to be ISSUED, and this warp shares its scheduler with four worker
+// warps that are busy with conversion arithmetic for most of a tile.  Measured on the GPU with the
+// scheduler's other warps always ready to issue: one lane inside a divergent branch, building each
+// descriptor from two 32-bit halves, got one MMA out per 500 cycles; the same loop run warp-uniformly
+// (the compiler keeps the descriptor arithmetic on the uniform datapath) one per 90, against 48 for the
+// tensor pipe alone (M128 x N64 x K16 with both operands fetched from shared memory).  In this kernel the
+// one-lane form issued one MMA per ~75 cycles, so every PV chunk released its part of the K buffer late
+// and the conversion of the next tile, which follows those releases, was paced by MMA issue.
 template <int NPAD>
 __device__ __forceinline__ void mma_role(uint8_t *smem, uint32_t tmem_base) {
     using L = Smem<NPAD>;
@@ -830,21 +840,18 @@ __device__ __forceinline__ void mma_role(uint8_t *smem, uint32_t tmem_base) {
     const volatile int *ring = reinterpret_cast<const volatile int *>(smem + L::kSched) + kSchedRec;
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::kAbort);
     const uint32_t bars = smem_u32(smem + L::kBars);
+    const int lane = threadIdx.x & 31;
+    const uint32_t go = elect_one();
     constexpr uint32_t idesc_qk = umma_idesc_bf16(128, NPAD, 0, 0);
     constexpr uint32_t idesc_pv = umma_idesc_bf16(128, NPAD, 1, 1);
     // QK^T: K-major A (rows x dims) and B (heads x dims): M/N step = one row group (8192 B), K step =
     // one core matrix (128 B).  PV: MN-major A = K^T chunk (dims x rows): M step = next dim group
     // (128 B), K step = next row group (8192 B); MN-major B = P^T: N step = next head group (2048 B),
-    // K step = next row group (128 B).  Only the 14-bit start-address field changes between MMAs, so
-    // stepping a descriptor is one 32-bit add: the thread must sustain one MMA per ~50 cycles.
+    // K step = next row group (128 B).  Only the 14-bit start-address field changes between MMAs.
     const uint64_t qa = umma_desc(smem_u32(smem + L::kK), kCoreBytes, kRowGroupBytes);
     const uint64_t qb = umma_desc(smem_u32(smem + L::kQ), kCoreBytes, kRowGroupBytes);
     const uint64_t pa = umma_desc(smem_u32(smem + L::kK), kRowGroupBytes, kCoreBytes);
     const uint64_t pb = umma_desc(smem_u32(smem + L::kP), kCoreBytes, 2048);
-    const uint32_t qa_lo = static_cast<uint32_t>(qa), qa_hi = static_cast<uint32_t>(qa >> 32);
-    const uint32_t qb_lo = static_cast<uint32_t>(qb), qb_hi = static_cast<uint32_t>(qb >> 32);
-    const uint32_t pa_lo = static_cast<uint32_t>(pa), pa_hi = static_cast<uint32_t>(pa >> 32);
-    const uint32_t pb_lo = static_cast<uint32_t>(pb), pb_hi = static_cast<uint32_t>(pb >> 32);
 
     int gt = 0;
     for (int so = 0;; ++so) {
@@ -855,35 +862,34 @@ __device__ __forceinline__ void mma_role(uint8_t *smem, uint32_t tmem_base) {
         for (int it = 0; it < ntl; ++it, ++gt) {
             SMLA_MARK(gt, 0);
             if (it == 0 && !mbar_wait(bars + kBarQ * 8, so & 1, abort_flag)) {   // this item's Q tile
-                give_up(abort_flag, kStatusMmaWait);
+                if (lane == 0) give_up(abort_flag, kStatusMmaWait);
                 return;
             }
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 if (!mbar_wait(bars + (kBarReady + c) * 8, gt & 1, abort_flag)) {
-                    give_up(abort_flag, kStatusMmaWait);
+                    if (lane == 0) give_up(abort_flag, kStatusMmaWait);
                     return;
                 }
                 tc_fence_after_sync();
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {
-                    const uint32_t off = static_cast<uint32_t>(((16 * c + 2 * k) * kCoreBytes) >> 4);
-                    umma_bf16_ss_lohi(tmem_base, qa_lo + off, qa_hi, qb_lo + off, qb_hi, idesc_qk,
-                                      (c | k) != 0 ? 1u : 0u);
+                    const uint64_t off = static_cast<uint64_t>(((16 * c + 2 * k) * kCoreBytes) >> 4);
+                    umma_bf16_ss_pred(tmem_base, qa + off, qb + off, idesc_qk, (c | k) != 0 ? 1u : 0u, go);
                 }
             }
-            umma_commit(bars + kBarS * 8);
+            umma_commit_pred(bars + kBarS * 8, go);
             SMLA_MARK(gt, 1);
             if (!mbar_wait(bars + kBarP * 8, gt & 1, abort_flag)) {
-                give_up(abort_flag, kStatusMmaWait);
+                if (lane == 0) give_up(abort_flag, kStatusMmaWait);
                 return;
             }
             // Progress for the warps that only follow (Q loader, scheduler): a count cannot be missed
             // the way an mbarrier phase can by a waiter that falls two phases behind.
-            reinterpret_cast<volatile int *>(smem + L::kSched)[kSchedTiles] = gt + 1;
+            if (lane == 0) reinterpret_cast<volatile int *>(smem + L::kSched)[kSchedTiles] = gt + 1;
             // The first PV of a segment overwrites O^T: the previous segment's epilogue must have read it.
             if (it == 0 && so > 0 && !mbar_wait(bars + kBarOFree * 8, (so - 1) & 1, abort_flag)) {
-                give_up(abort_flag, kStatusMmaWait);
+                if (lane == 0) give_up(abort_flag, kStatusMmaWait);
                 return;
             }
             tc_fence_after_sync();
@@ -893,14 +899,13 @@ __device__ __forceinline__ void mma_role(uint8_t *smem, uint32_t tmem_base) {
             for (int c = 0; c < 4; ++c) {
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {
-                    const uint32_t aoff = static_cast<uint32_t>((c * 16 * kCoreBytes + 2 * k * kRowGroupBytes) >> 4);
-                    const uint32_t boff = static_cast<uint32_t>((2 * k * kCoreBytes) >> 4);
-                    umma_bf16_ss_lohi(tmem_base + kTmemOCol + c * NPAD, pa_lo + aoff, pa_hi, pb_lo + boff, pb_hi,
-                                      idesc_pv, k > 0 ? 1u : acc0);
+                    const uint64_t aoff = static_cast<uint64_t>((c * 16 * kCoreBytes + 2 * k * kRowGroupBytes) >> 4);
+                    const uint64_t boff = static_cast<uint64_t>((2 * k * kCoreBytes) >> 4);
+                    umma_bf16_ss_pred(tmem_base + kTmemOCol + c * NPAD, pa + aoff, pb + boff, idesc_pv, k > 0 ? 1u : acc0, go);
                 }
-                umma_commit(bars + (kBarFree + c) * 8);   // chunk c of the K buffer may be refilled
+                umma_commit_pred(bars + (kBarFree + c) * 8, go);   // chunk c of the K buffer may be refilled
             }
-            if (it + 1 == ntl) umma_commit(bars + kBarO * 8);
+            if (it + 1 == ntl) umma_commit_pred(bars + kBarO * 8, go);
             SMLA_MARK(gt, 6);
         }
     }
@@ -1560,8 +1565,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const __gri
     if (warp < kWorkerWarps) {
         worker_role<FMT, NPAD>(a, smem, tmem_base, warp, lane);
     } else if (warp == kMmaWarp) {
-        if (lane == 0) mma_role<NPAD>(smem, tmem_base);
-        __syncwarp();
+        mma_role<NPAD>(smem, tmem_base);
     } else if (a.q_tma) {
         // one tensor copy per item needs one thread; the next warp publishes the schedule
         if (warp == kMmaWarp + 1) qload_role<NPAD>(a, smem, 0, lane);
