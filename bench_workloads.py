@@ -1,9 +1,14 @@
 """Seeded synthetic sparse-MLA workloads with the shapes, sizes and value distributions of the
 benchmark configurations (there is no public dataset for this path; the reference benchmarks
-synthetic tensors too, benchmarks/bench_sparse_mla_decode_16k.py:109-143).
+synthetic tensors too, benchmarks/bench_sparse_mla_decode_16k.py:109-143).  Used by ``bench.py`` and
+by the tests; not part of the product package.
 
 Every builder returns a dict of keyword arguments for the matching ``flash_mla`` op plus a
-``meta`` entry (row counts for roofline arithmetic).  All tensors live on ``device``.
+``meta`` entry (row counts for roofline arithmetic).  All tensors live on ``device``.  On a CUDA
+device the caches are packed with the library's own writers and quantizer (``flash_mla``); on the
+CPU -- the reference arm of the benchmark, which must not load the library -- with the numpy oracle
+(``oracle.pack_fp8_ds_mla``, ``oracle.quantize_int8_rows``, ``oracle.pack_int8_inline528``), whose
+bytes are the same formats.
 """
 from __future__ import annotations
 
@@ -11,7 +16,37 @@ from typing import Optional
 
 import torch
 
-from .cache_formats import pack_fp8_ds_mla, pack_int8_inline528
+
+def _is_cpu(device) -> bool:
+    return torch.device(device).type == "cpu"
+
+
+def pack_fp8_ds_mla(latent_bf16, block_size):
+    if _is_cpu(latent_bf16.device):
+        import oracle
+        cache, _ = oracle.pack_fp8_ds_mla(latent_bf16.float().numpy(), block_size)
+        return torch.from_numpy(cache)
+    from flash_mla.cache_formats import pack_fp8_ds_mla as pack
+    return pack(latent_bf16, block_size)
+
+
+def quantize_int8_ds_mla_rows(latent_bf16):
+    if _is_cpu(latent_bf16.device):
+        import oracle
+        q, s = oracle.quantize_int8_rows(latent_bf16.float().numpy())
+        return torch.from_numpy(q), torch.from_numpy(s)
+    from flash_mla import quantize_int8_ds_mla_rows as quant
+    return quant(latent_bf16)
+
+
+def pack_int8_inline528(q, scale, block_size):
+    """-> (backing uint8 buffer [nb, bs, 528], int8 data view [nb, bs, 512], fp32 scale view [nb, bs])."""
+    if _is_cpu(q.device):
+        import oracle
+        buf = torch.from_numpy(oracle.pack_int8_inline528(q.numpy(), scale.numpy(), block_size))
+        return buf, buf[:, :, :512].view(torch.int8), buf[:, :, 512:516].view(torch.float32).squeeze(-1)
+    from flash_mla.cache_formats import pack_int8_inline528 as pack
+    return pack(q, scale, block_size)
 
 
 def _distinct_indices(gen, T, num_slots, topk, device, mask_frac=0.0):
@@ -66,8 +101,6 @@ def decode_workload(fmt: str = "fp8", T: int = 128, H: int = 64, swa_slots: int 
     [topk/2, topk] (or == topk with ``full_lens``); attn_sink ~ N(0,1).  ``fmt`` "fp8" or "int8"
     (int8: 5 % of the latent rows scaled x50 unless ``outlier_frac`` says otherwise; ``layout``
     "inline528" or "separate")."""
-    from . import quantize_int8_ds_mla_rows
-
     g = _gen(device, seed)
     if outlier_frac is None:
         outlier_frac = 0.05 if fmt == "int8" else 0.0
@@ -125,8 +158,6 @@ def prefill_int8_workload(T: int = 4096, H: int = 64, swa_slots: int = 16384, sw
                           extra_topk: int = 512, seed: int = 0, device: str = "cuda"):
     """Causal prefill: for query position p the swa ids are uniform distinct in [0, p] padded with -1
     (lens min(p+1, topk)); the compressed extra stream follows the same rule on p // 4."""
-    from . import quantize_int8_ds_mla_rows
-
     g = _gen(device, seed)
     swa_lat = _latent(g, swa_slots, device, 0.05)
     extra_lat = _latent(g, extra_slots, device, 0.05)

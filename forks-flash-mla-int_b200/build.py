@@ -26,7 +26,7 @@ LIB = os.path.join(PKG, "lib")
 INCLUDE = os.path.join(ROOT, "include")
 
 CUDA_SOURCES = ["sparse_mla_attn_sm100.cu", "quantize_int8_sm100.cu", "cache_writers_sm100.cu", "c_api.cu", "decode_static_scratch.cu"]
-CUDA_HEADERS = ["sm100_ptx.cuh", "smla_internal.h"]
+CUDA_HEADERS = ["sm100_ptx.cuh", "smla_internal.h", "row_codec.cuh"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

@@ -2,6 +2,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cstdlib>
 
 #include "smla_internal.h"
@@ -9,25 +10,32 @@
 namespace {
 
 struct DevInfo {
-    bool known = false;
     int major = 0, sm_count = 0;
 };
-DevInfo g_dev[64];
+// Per-device facts, looked up once.  Hosts that run one thread per GPU call in concurrently: the two
+// words are published with an atomic flag (two threads that both miss simply look the same values up).
+std::atomic<int> g_dev_known[64];
+int g_dev_major[64], g_dev_sms[64];
 
 int device_info(DevInfo &out) {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return static_cast<int>(e);
-    DevInfo tmp;
-    DevInfo &d = (dev >= 0 && dev < 64) ? g_dev[dev] : tmp;
-    if (!d.known) {
-        e = cudaDeviceGetAttribute(&d.major, cudaDevAttrComputeCapabilityMajor, dev);
-        if (e != cudaSuccess) return static_cast<int>(e);
-        e = cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev);
-        if (e != cudaSuccess) return static_cast<int>(e);
-        d.known = true;
+    const bool tracked = dev >= 0 && dev < 64;
+    if (tracked && g_dev_known[dev].load(std::memory_order_acquire)) {
+        out.major = g_dev_major[dev];
+        out.sm_count = g_dev_sms[dev];
+        return SMLA_OK;
     }
-    out = d;
+    e = cudaDeviceGetAttribute(&out.major, cudaDevAttrComputeCapabilityMajor, dev);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    e = cudaDeviceGetAttribute(&out.sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (tracked) {
+        g_dev_major[dev] = out.major;
+        g_dev_sms[dev] = out.sm_count;
+        g_dev_known[dev].store(1, std::memory_order_release);
+    }
     return SMLA_OK;
 }
 
@@ -90,6 +98,15 @@ int smla_decode_kernel_launches(int sm_count, int num_tokens, int num_heads, int
     return smla::merge_mode_policy(items, ctas) == 0 ? 2 : 1;
 }
 
+int smla_decode_kernel_launches_captured(int sm_count, int num_tokens, int num_heads, int num_splits) {
+    if (num_splits <= 1 || num_tokens <= 0 || num_heads <= 0) return 1;
+    const long long ctas = smla::balanced_ctas(sm_count, smla::head_pad(num_heads),
+                                               static_cast<long long>(smla_attn_workspace_bytes(num_tokens, num_heads, num_splits)));
+    if (ctas < 2) return 1;
+    const long long items = static_cast<long long>(num_tokens) * ((num_heads + 63) / 64);
+    return smla::merge_mode_policy(items, ctas) == 1 ? 1 : 2;     // the slice merge is not used on a capturing stream
+}
+
 int smla_decode_plan(int num_tokens, int num_heads, int max_width_rows, int *num_splits, size_t *workspace_bytes) {
     DevInfo d;
     const int rc = device_info(d);
@@ -119,7 +136,7 @@ int smla_sparse_mla_decode(const smla_attn_params_t *p, void *stream) {
         if (!p->workspace || p->workspace_bytes < smla_attn_workspace_bytes(p->num_tokens, p->num_heads, splits))
             return SMLA_EWORKSPACE;
     }
-    return smla::launch_sparse_mla_attention(*p, splits, p->workspace, static_cast<cudaStream_t>(stream));
+    return smla::launch_sparse_mla_attention(*p, splits, p->workspace, p->workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
 int smla_sparse_mla_prefill(const smla_attn_params_t *p, void *stream) {
@@ -129,7 +146,7 @@ int smla_sparse_mla_prefill(const smla_attn_params_t *p, void *stream) {
     if (rc != SMLA_OK) return rc;
     if (d.major != 10) return SMLA_EARCH;
     if (max_width(*p) <= 0) return SMLA_EINVAL;   // "prefill requires at least one selected slot"
-    return smla::launch_sparse_mla_attention(*p, 1, nullptr, static_cast<cudaStream_t>(stream));
+    return smla::launch_sparse_mla_attention(*p, 1, nullptr, 0, static_cast<cudaStream_t>(stream));
 }
 
 int smla_quantize_int8_ds_mla_rows(const void *x, int x_dtype, int64_t rows, int64_t x_row_stride, int8_t *q,
@@ -156,5 +173,10 @@ int smla_write_fp8_ds_mla_cache(const void *x, int x_dtype, int64_t rows, int64_
 }
 
 int smla_read_device_status(int *status_out) { return smla::read_and_clear_device_status(status_out); }
+
+int smla_device_status_address(int **device_address) {
+    if (!device_address) return SMLA_EINVAL;
+    return smla::device_status_address(device_address);
+}
 
 }  // extern "C"

@@ -17,6 +17,7 @@
 // kernels overlap on the GPU (different streams, or graphs replayed concurrently) race on it.
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <mutex>
 
 #include "smla_internal.h"
@@ -62,22 +63,36 @@ int smla_sparse_mla_decode_static_scratch(const smla_attn_params_t *p, void *str
         const int width = p->swa.topk + (p->extra.cache ? p->extra.topk : 0);
         const int rc = smla_decode_plan(p->num_tokens, p->num_heads, width, &splits, nullptr);
         if (rc != SMLA_OK) return rc;
-        // The automatic choice only sizes scratch, so it is cut down to what the array holds (fewer
-        // CTAs share the tiles); below two it becomes the unsplit schedule.
-        while (splits > 1 && smla_attn_workspace_bytes(p->num_tokens, p->num_heads, splits) > kStaticScratchBytes) --splits;
     } else {
         int unused = 0;
         const int rc = smla_decode_plan(1, 1, 1, &unused, nullptr);   // architecture check only
         if (rc != SMLA_OK) return rc;
     }
-    // An explicit request must fit the fixed array as it is.
-    if (smla_attn_workspace_bytes(p->num_tokens, p->num_heads, splits) > kStaticScratchBytes) return SMLA_ETOOBIG;
     void *scratch = nullptr;
+    if (splits > 1) {
+        const long long want = static_cast<long long>(smla_attn_workspace_bytes(p->num_tokens, p->num_heads, splits));
+        if (p->num_splits > 1) {
+            // An explicit request is taken at its word, as by smla_sparse_mla_decode: it must fit as asked.
+            if (want > static_cast<long long>(kStaticScratchBytes)) return SMLA_ETOOBIG;
+        } else {
+            // The automatic choice only sizes scratch, and what the kernels touch does not grow with the
+            // token count: two partial slots of one head block per CTA plus 64 bytes per SM (39 MB on a
+            // 148-SM part at 64 heads per block), whatever smla_attn_workspace_bytes says for many tokens.
+            // The array is offered whole, the launcher takes as many CTAs as fit into it; the unsplit
+            // schedule is used only when not even two fit.
+            int dev = 0, sms = 0;
+            cudaError_t e = cudaGetDevice(&dev);
+            if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+            if (e != cudaSuccess) return static_cast<int>(e);
+            const long long have = std::min<long long>(want, static_cast<long long>(kStaticScratchBytes));
+            if (smla::balanced_ctas(sms, smla::head_pad(p->num_heads), have) < 2) splits = 1;
+        }
+    }
     if (splits > 1) {
         const int rc = static_scratch_address(&scratch);
         if (rc != SMLA_OK) return rc;
     }
-    return smla::launch_sparse_mla_attention(*p, splits, scratch, static_cast<cudaStream_t>(stream));
+    return smla::launch_sparse_mla_attention(*p, splits, scratch, kStaticScratchBytes, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -26,10 +26,14 @@ int launch_write_fp8_ds_mla(const void *x, int x_dtype, int64_t rows, int64_t x_
                             int slots_i64, void *cache, int64_t num_blocks, int block_size, int64_t block_stride,
                             cudaStream_t stream);
 
-// `force_single` = never split (prefill).  `split_ws`/`num_splits` as resolved by the caller.
-int launch_sparse_mla_attention(const smla_attn_params_t &p, int num_splits, void *workspace, cudaStream_t stream);
+// `num_splits` as resolved by the caller (1 = whole items, prefill).  `workspace_capacity` = bytes that may
+// be used at `workspace`: the balanced schedule gets as many CTAs as fit into the smaller of that and
+// smla_attn_workspace_bytes(T, H, num_splits).
+int launch_sparse_mla_attention(const smla_attn_params_t &p, int num_splits, void *workspace, size_t workspace_capacity,
+                                cudaStream_t stream);
 
 int read_and_clear_device_status(int *status_out);
+int device_status_address(int **addr_out);
 
 // CTAs of the balanced schedule for a workspace of `workspace_bytes` (two partial slots of `npad` heads
 // per CTA, 64 bytes of flags and descriptors per SM); fewer than 2 means whole items are dealt out.

@@ -27,7 +27,7 @@
 // tile in registers (256-bit loads issued a tile ahead) and writes them as bf16 into the single K
 // buffer chunk by chunk (128 dims), each chunk as soon as the previous tile's PV has released it;
 // (2) softmax -- warp w owns TMEM lanes 32*(w%4).. and head columns (N/4)*(w/4)..: S^T -> P^T with a
-// lazily moved, integer-valued reference max, running denominators, and the epilogue.  Warp 16
+// lazily moved reference max, running denominators, and the epilogue.  Warp 16
 // allocates TMEM and its lane 0 issues every tcgen05.mma; warp 17 fetches each item's Q tile (one TMA
 // tensor copy); warp 18 publishes the CTA's segments into a ring in shared memory.
 //
@@ -101,19 +101,27 @@ constexpr int kKBytes = 16 * kRowGroupBytes;     // 128 rows
 constexpr int kTmemCols = 512;
 constexpr int kTmemOCol = 64;                    // O^T chunks start here; S^T at column 0
 constexpr float kLog2e = 1.4426950408889634f;
-// The softmax reference m (log2 units, integer-valued) only has to keep 2^(s - m) inside the range of
-// bf16 / fp32, not near 1: a power-of-two offset changes no mantissa anywhere (P, the fp32 accumulators,
-// the denominators and the final quotient all scale exactly).  So m is set kRefHeadroom ABOVE the
-// maximum seen and is left alone until a score exceeds it by kRescaleThreshold: scores may grow by 2^100
-// after a segment's first tile (a few outlier rows among ordinary ones) before the accumulators are
-// rescaled, which stalls the tile pipeline (measured: 5 % outlier rows x50 cost 11 % with m kept at the
-// running maximum and an 8-unit threshold, 6 % now).  The bound on the sum: a rescale factor
-// 2^(m_old - m_new), or a merge weight 2^(m_i - M), multiplies terms that still matter (within 2^-24 of
-// the largest) only when its exponent is above -(kRescaleThreshold + kRefHeadroom + 24), which has to
-// stay a normal fp32 number (2^-126); with both at 80 the factor flushed to zero and took live
-// accumulators with it.
-constexpr float kRescaleThreshold = 60.0f;
-constexpr float kRefHeadroom = 40.0f;
+// The softmax reference m (log2 units) is the running maximum AS IT WAS WHEN m WAS LAST MOVED: it is left
+// alone until a score exceeds it by kRescaleThreshold, and then set to the new maximum itself, not to a
+// rounded value.  Two things follow.  (1) The row that holds the maximum gets P = 2^0 = 1, which bf16
+// holds exactly: where one row dominates -- the x50 outlier rows of the int8 workloads, |K| up to 200 --
+// the output carries no rounding error of that row's weight.  With an integer-valued reference (tried
+// first, because P then rounds identically however the rows are cut into segments) every weight was
+// rounded, and small elements of such rows were up to four times further from the fp32 oracle than the
+// reference's own kernels; a CPU emulation of both rules reproduces the factor.  (2) Ordinary data never
+// moves m after a segment's first tile (scores within a few units of each other); outlier rows move it
+// in most tiles either way (13 of 20 tiles with a 100-unit window, 18 of 20 with this one), and each
+// move rescales the accumulators, which stalls the tile pipeline.  The bound on the threshold: a rescale
+// factor 2^(m_old - m_new), or a merge weight 2^(m_i - M), multiplies terms that still matter (within
+// 2^-24 of the largest) only when its exponent is above -(kRescaleThreshold + kRefHeadroom + 24), which
+// has to stay a normal fp32 number (2^-126).
+constexpr float kRescaleThreshold = 8.0f;
+constexpr float kRefHeadroom = 0.0f;
+// What the exact weight of the top row is worth grows with |K| of that row, and large rows show as large
+// scores: above kBigScore (log2 units; ordinary N(0,1) data stays below 10) the reference follows the
+// running maximum exactly, below it the threshold applies.  Per head: m moves when s - m > move_threshold(m).
+constexpr float kBigScore = 32.0f;
+__device__ __forceinline__ float move_threshold(float m) { return fminf(fmaxf(kBigScore - m, 0.0f), kRescaleThreshold); }
 static_assert(kRescaleThreshold + kRefHeadroom + 24.0f <= 126.0f, "rescale factors must stay normal fp32 numbers");
 constexpr int kAllWorkersBar = 5;                // named barriers 1..4: the four column-slice groups
 // mbarrier slots
@@ -168,7 +176,8 @@ struct Smem {
     static constexpr int kM = kRed + 4 * NPAD * 4;       // running reference max per head
     static constexpr int kAlpha = kM + NPAD * 4;         // rescale factor / final 1/l per head
     static constexpr int kShift = kAlpha + NPAD * 4;     // m_old - m_new of the last reference move
-    static constexpr int kBars = kShift + NPAD * 4;      // kNumBars mbarriers
+    static constexpr int kThr = kShift + NPAD * 4;       // how far a score may exceed m before m moves (move_threshold)
+    static constexpr int kBars = kThr + NPAD * 4;        // kNumBars mbarriers
     static constexpr int kTmemPtr = kBars + 14 * 8;
     static constexpr int kAbort = kTmemPtr + 4;
     static constexpr int kSched = kAbort + 4 + 8;        // 160 ints: work distribution (scan scratch, iterator, segment ring)
@@ -933,7 +942,7 @@ __device__ __forceinline__ float initial_ref(const KernelArgs &a, bool complete,
     // A complete item folds the sink into its own denominator, so the sink takes part in the reference.
     // Without a sink the reference starts at 0: it has to be finite (scores are held relative to it)
     // and the first tile replaces it anyway.
-    if (complete && a.sink != nullptr && hl < hvalid) return ceilf(a.sink[h0 + hl] * kLog2e);
+    if (complete && a.sink != nullptr && hl < hvalid) return a.sink[h0 + hl] * kLog2e;
     return 0.0f;
 }
 
@@ -1131,6 +1140,7 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
     float *m_s = reinterpret_cast<float *>(smem + L::kM);
     float *alpha_s = reinterpret_cast<float *>(smem + L::kAlpha);
     float *shift_s = reinterpret_cast<float *>(smem + L::kShift);
+    float *thr_s = reinterpret_cast<float *>(smem + L::kThr);
     const int tid = warp * 32 + lane;
     const bool tracer = (warp == 0 && lane == 0);
     (void)tracer;
@@ -1230,6 +1240,7 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
             if (cg != nullptr) {   // reference of the segment that follows (read after the barrier)
                 const int c_h0 = cg[1] * 64;
                 m_s[tid] = initial_ref(a, (cg[7] & kSegComplete) != 0, c_h0, tid, min(NPAD, a.H - c_h0));
+                thr_s[tid] = move_threshold(m_s[tid]);
             }
         }
         named_bar_sync(kAllWorkersBar, kWorkerThreads);
@@ -1413,11 +1424,11 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
             // (always on a segment's first tile).  The vote spans the four warps that share these columns.
             bool need = first_tile;
 #pragma unroll
-            for (int j = 0; j < CW; ++j) need |= sm[j] > kRescaleThreshold;
+            for (int j = 0; j < CW; ++j) need |= sm[j] > thr_s[col0 + j];
             if (named_bar_or(group_bar, 128, need)) {
                 // Scores relative to the OLD reference are kept (not re-read from tensor memory, not held
-                // as raw values): s - m_new = (s - m_old) + (m_old - m_new), and both references are
-                // integers, so the sum is exact whenever s - m_old is finite.
+                // as raw values): s - m_new = (s - m_old) + (m_old - m_new); for the row that sets the new
+                // maximum the sum is zero to within 2^-17, far inside the bf16 quantum of P = 1.
                 float (&s)[CW] = sm;
                 float r[1];
                 ColReduce<CW, 16, true>::run(s, lane, r);
@@ -1428,16 +1439,15 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
                     const float tmr = fmaxf(fmaxf(red[col], red[NPAD + col]), fmaxf(red[2 * NPAD + col], red[3 * NPAD + col]));
                     const float m_old = m_s[col];
                     const float tm = tmr + m_old;     // column maximum, back in absolute log2 units
-                    // m stays INTEGER-valued (log2 units): 2^(s - m) then has the same mantissa whatever m
-                    // is, so P rounds to bf16 (almost) identically however the rows are cut into segments.
-                    // The first tile sets it outright (only the sink, if it counts here, holds it up);
+                    // The first tile sets m outright (only the sink, if it counts here, holds it up);
                     // nothing has been accumulated yet, so there is nothing to rescale.
                     const bool sink_here = (sg[7] & kSegComplete) != 0 && a.sink != nullptr;
-                    const bool up = first_tile ? (!sink_here || ceilf(tm) > m_old) : tm > m_old + kRescaleThreshold;
-                    const float m_new = up ? ceilf(tm) + kRefHeadroom : m_old;
+                    const bool up = first_tile ? (!sink_here || tm > m_old) : tm > m_old + thr_s[col];
+                    const float m_new = up ? tm + kRefHeadroom : m_old;
                     alpha_s[col] = (up && !first_tile) ? fast_exp2(m_old - m_new) : 1.0f;
                     shift_s[col] = m_old - m_new;
                     m_s[col] = m_new;
+                    thr_s[col] = move_threshold(m_new);
                 }
                 named_bar_sync(group_bar, 128);
                 lacc *= alpha_s[col0 + (lane >> kColShift)];
@@ -1460,9 +1470,13 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
                 uint32_t pk[CW / 2];
 #pragma unroll
                 for (int j = 0; j < CW; j += 2) {
-                    sm[j] = fast_exp2(sm[j]);
-                    sm[j + 1] = fast_exp2(sm[j + 1]);
-                    pk[j / 2] = pack_bf16x2(sm[j], sm[j + 1]);
+                    pk[j / 2] = pack_bf16x2(fast_exp2(sm[j]), fast_exp2(sm[j + 1]));
+                    // The denominator sums the ROUNDED probabilities, the ones PV multiplies: where one
+                    // row dominates, out = P~ K / sum P~ then carries no rounding error of P at all,
+                    // while P~ K / sum P is off by the rounding of P times |K| (0.4 for the x50 outlier
+                    // rows of the int8 workloads, four times what the reference's kernels show).
+                    sm[j] = __uint_as_float(pk[j / 2] << 16);
+                    sm[j + 1] = __uint_as_float(pk[j / 2] & 0xFFFF0000u);
                 }
                 if constexpr (CW == 16) {
                     st_shared_v4(p_addr, pk[0], pk[1], pk[2], pk[3]);
@@ -1551,8 +1565,11 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const __gri
     {
         const int *r0 = sched + kSchedRec;
         const int h0 = r0[1] * 64, hvalid = min(NPAD, a.H - h0);
-        if (tid < NPAD)
-            reinterpret_cast<float *>(smem + L::kM)[tid] = initial_ref(a, (r0[7] & kSegComplete) != 0, h0, tid, hvalid);
+        if (tid < NPAD) {
+            const float m0 = initial_ref(a, (r0[7] & kSegComplete) != 0, h0, tid, hvalid);
+            reinterpret_cast<float *>(smem + L::kM)[tid] = m0;
+            reinterpret_cast<float *>(smem + L::kThr)[tid] = move_threshold(m0);
+        }
     }
     SMLA_CTA_MARK(5);
     fence_async_smem();
@@ -1643,15 +1660,18 @@ int fill_stream(const smla_stream_t &s, int fmt, StreamDev &d) {
 template <int FMT, int NPAD>
 int launch_fwd(const KernelArgs &a, unsigned grid, cudaStream_t stream) {
     constexpr int smem_bytes = Smem<NPAD>::kTotal;
-    static bool attr_done[64] = {};
+    // The opt-in to 227 KB of dynamic shared memory is per device and per kernel instance; hosts that
+    // run one thread per GPU come through here concurrently, hence atomics (setting it twice is harmless).
+    static std::atomic<bool> attr_done[64];
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return static_cast<int>(e);
-    if (dev < 0 || dev >= 64 || !attr_done[dev]) {
+    const bool tracked = dev >= 0 && dev < 64;
+    if (!tracked || !attr_done[dev].load(std::memory_order_acquire)) {
         e = cudaFuncSetAttribute(sparse_mla_fwd_kernel<FMT, NPAD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  smem_bytes);
         if (e != cudaSuccess) return static_cast<int>(e);
-        if (dev >= 0 && dev < 64) attr_done[dev] = true;
+        if (tracked) attr_done[dev].store(true, std::memory_order_release);
     }
     sparse_mla_fwd_kernel<FMT, NPAD><<<grid, kThreads, smem_bytes, stream>>>(a);
     return static_cast<int>(cudaGetLastError());
@@ -1685,7 +1705,7 @@ EncodeTiledFn tensor_map_encoder() {
 // 5-D view of q [T, H, 512] whose box {8, 8, 64, npad/8, 1} is the Q operand's shared-memory layout.
 // False (the kernel then uses cp.async) when H is not a multiple of 8 or the driver refuses the map.
 bool make_q_tensor_map(const KernelArgs &a, int npad, CUtensorMap *map) {
-    if (a.H % 8 != 0 || getenv("SMLA_NO_TMA") != nullptr) return false;
+    if (a.H % 8 != 0) return false;
     EncodeTiledFn enc = tensor_map_encoder();
     if (enc == nullptr) return false;
     const cuuint64_t dims[5] = {8, 8, 64, static_cast<cuuint64_t>(a.H / 8), static_cast<cuuint64_t>(a.T)};
@@ -1710,17 +1730,15 @@ unsigned long long next_launch_tag() {
 }
 
 int sm_count_of_current_device(int &count) {
-    static int cached[64] = {};
+    static std::atomic<int> cached[64];
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return static_cast<int>(e);
-    if (dev >= 0 && dev < 64 && cached[dev] > 0) {
-        count = cached[dev];
-        return 0;
-    }
+    const bool tracked = dev >= 0 && dev < 64;
+    if (tracked && (count = cached[dev].load(std::memory_order_relaxed)) > 0) return 0;
     e = cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) return static_cast<int>(e);
-    if (dev >= 0 && dev < 64) cached[dev] = count;
+    if (tracked) cached[dev].store(count, std::memory_order_relaxed);
     return 0;
 }
 
@@ -1729,7 +1747,8 @@ int sm_count_of_current_device(int &count) {
 // `num_splits` > 1 with a workspace of smla_attn_workspace_bytes(T, H, num_splits) bytes selects the
 // balanced-tiles schedule with as many CTAs as the SM count and the workspace (two partial slots per
 // CTA plus one 16-byte descriptor) allow; otherwise whole items are dealt out to the CTAs.
-int launch_sparse_mla_attention(const smla_attn_params_t &p, int num_splits, void *workspace, cudaStream_t stream) {
+int launch_sparse_mla_attention(const smla_attn_params_t &p, int num_splits, void *workspace, size_t workspace_capacity,
+                                cudaStream_t stream) {
     if (p.num_tokens < 0 || p.num_heads <= 0 || !p.q || !p.out) return SMLA_EINVAL;
     if (p.num_tokens == 0) return SMLA_OK;
     if (p.cache_format != SMLA_FP8_DS_MLA && p.cache_format != SMLA_INT8_DS_MLA) return SMLA_EINVAL;
@@ -1766,7 +1785,8 @@ int launch_sparse_mla_attention(const smla_attn_params_t &p, int num_splits, voi
     if (num_splits > 1) {
         if (!workspace) return SMLA_EWORKSPACE;
         if (reinterpret_cast<uintptr_t>(workspace) & 15u) return SMLA_EALIGN;
-        ctas = balanced_ctas(sms, npad, static_cast<long long>(smla_attn_workspace_bytes(p.num_tokens, p.num_heads, num_splits)));
+        const size_t want = smla_attn_workspace_bytes(p.num_tokens, p.num_heads, num_splits);
+        ctas = balanced_ctas(sms, npad, static_cast<long long>(std::min(want, workspace_capacity)));
     }
     if (ctas >= 2) {
         a.balanced = 1;
@@ -1781,7 +1801,6 @@ int launch_sparse_mla_attention(const smla_attn_params_t &p, int num_splits, voi
             cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
             if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) a.fused_merge = 0;
         }
-        if (const char *e = getenv("SMLA_MERGE")) a.fused_merge = atoi(e);     // developer switch: 0 combine kernel, 1, 2
         a.tag = next_launch_tag();
     } else {
         a.balanced = 0;
@@ -1790,7 +1809,7 @@ int launch_sparse_mla_attention(const smla_attn_params_t &p, int num_splits, voi
     a.q_tma = make_q_tensor_map(a, npad, &a.q_map) ? 1 : 0;
     const unsigned grid = static_cast<unsigned>(ctas);
     const bool int8_wide = p.cache_format == SMLA_INT8_DS_MLA && a.swa.vec == 2 &&
-                           (p.extra.cache == nullptr || a.extra.vec == 2) && getenv("SMLA_NO_WIDE_INT8") == nullptr;
+                           (p.extra.cache == nullptr || a.extra.vec == 2);
     rc = (p.cache_format == SMLA_FP8_DS_MLA) ? launch_fwd_npad<SMLA_FP8_DS_MLA>(npad, a, grid, stream)
          : int8_wide                         ? launch_fwd_npad<kFmtInt8Wide>(npad, a, grid, stream)
                                              : launch_fwd_npad<SMLA_INT8_DS_MLA>(npad, a, grid, stream);
@@ -1825,6 +1844,15 @@ int read_and_clear_device_status(int *status_out) {
     e = cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));
     if (status_out) *status_out = v;
     return static_cast<int>(e);
+}
+
+// Device address of the status word on the CURRENT device (no synchronisation).
+int device_status_address(int **addr_out) {
+    void *ptr = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&ptr, g_device_status);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (addr_out) *addr_out = static_cast<int *>(ptr);
+    return SMLA_OK;
 }
 
 }  // namespace smla

@@ -22,6 +22,7 @@ from .cache_formats import (  # noqa: F401
 )
 from .decode_plan import (  # noqa: F401
     SparseMlaDecodePlan,
+    device_status_tensor,
     get_sparse_mla_decode_plan,
     sparse_mla_decode_planned,
 )
@@ -43,4 +44,5 @@ __all__ = [
     "get_sparse_mla_decode_plan",
     "sparse_mla_decode_planned",
     "SparseMlaDecodePlan",
+    "device_status_tensor",
 ]

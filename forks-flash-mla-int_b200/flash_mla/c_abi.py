@@ -18,9 +18,9 @@ SMLA_ETOOBIG = -5
 
 EXPORTS = (
     "smla_version", "smla_error_string", "smla_choose_num_splits", "smla_attn_workspace_bytes",
-    "smla_decode_plan", "smla_decode_kernel_launches", "smla_sparse_mla_decode", "smla_sparse_mla_decode_static_scratch", "smla_sparse_mla_prefill",
+    "smla_decode_plan", "smla_decode_kernel_launches", "smla_decode_kernel_launches_captured", "smla_sparse_mla_decode", "smla_sparse_mla_decode_static_scratch", "smla_sparse_mla_prefill",
     "smla_quantize_int8_ds_mla_rows", "smla_write_int8_ds_mla_cache", "smla_write_fp8_ds_mla_cache",
-    "smla_read_device_status",
+    "smla_read_device_status", "smla_device_status_address",
 )
 
 
@@ -82,6 +82,8 @@ def load() -> C.CDLL:
     lib.smla_decode_plan.argtypes = [C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_size_t)]
     lib.smla_decode_kernel_launches.argtypes = [C.c_int] * 4
     lib.smla_decode_kernel_launches.restype = C.c_int
+    lib.smla_decode_kernel_launches_captured.argtypes = [C.c_int] * 4
+    lib.smla_decode_kernel_launches_captured.restype = C.c_int
     lib.smla_sparse_mla_decode.argtypes = [C.POINTER(SmlaAttnParams), C.c_void_p]
     lib.smla_sparse_mla_prefill.argtypes = [C.POINTER(SmlaAttnParams), C.c_void_p]
     lib.smla_sparse_mla_decode_static_scratch.argtypes = [C.POINTER(SmlaAttnParams), C.c_void_p]
@@ -93,6 +95,8 @@ def load() -> C.CDLL:
     lib.smla_write_fp8_ds_mla_cache.argtypes = [C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_void_p, C.c_int,
                                                 C.c_void_p, C.c_int64, C.c_int, C.c_int64, C.c_void_p]
     lib.smla_read_device_status.argtypes = [C.POINTER(C.c_int)]
+    lib.smla_device_status_address.argtypes = [C.POINTER(C.c_void_p)]
+    lib.smla_device_status_address.restype = C.c_int
     _lib = lib
     return lib
 

@@ -29,7 +29,9 @@ class SparseMlaDecodePlan:
     max_width: int                 # swa top-k + extra top-k
     num_splits: int                # 1 = whole items per CTA; > 1 = balanced tiles with partial segments in scratch
     workspace_bytes: int
-    kernel_launches: int           # kernels one decode call launches (CUDA-graph node count)
+    kernel_launches: int           # kernels one decode call launches on an ordinary stream
+    graph_kernel_nodes: int        # kernel nodes of the same call captured in a CUDA graph (the slice-wise merge of a
+                                   # few tokens is replaced by the combine kernel under capture: 2 where the above says 1)
     workspace: Optional[torch.Tensor]
     out: torch.Tensor              # bf16 [num_tokens, num_heads, 512], overwritten by every call
 
@@ -45,9 +47,10 @@ def get_sparse_mla_decode_plan(num_tokens: int, num_heads: int, max_width: int,
                     "smla_decode_plan")
         sms = torch.cuda.get_device_properties(dev).multi_processor_count
         launches = lib.smla_decode_kernel_launches(sms, num_tokens, num_heads, splits.value)
+        nodes = lib.smla_decode_kernel_launches_captured(sms, num_tokens, num_heads, splits.value)
         ws = torch.empty((nbytes.value + 3) // 4, dtype=torch.float32, device=dev) if splits.value > 1 else None
         out = torch.empty(num_tokens, num_heads, HEAD_DIM, dtype=torch.bfloat16, device=dev)
-    return SparseMlaDecodePlan(num_tokens, num_heads, max_width, splits.value, nbytes.value, launches, ws, out)
+    return SparseMlaDecodePlan(num_tokens, num_heads, max_width, splits.value, nbytes.value, launches, nodes, ws, out)
 
 
 def sparse_mla_decode_planned(plan: SparseMlaDecodePlan, q: torch.Tensor, swa_cache: torch.Tensor,
@@ -74,3 +77,26 @@ def sparse_mla_decode_planned(plan: SparseMlaDecodePlan, q: torch.Tensor, swa_ca
                                                       attn_sink, extra_cache, extra_scale, extra_indices, extra_lens,
                                                       plan.out, plan.workspace)
     return plan.out
+
+
+class _DeviceWord:
+    """Minimal __cuda_array_interface__ view of one int32 in device memory."""
+
+    def __init__(self, address: int):
+        self.__cuda_array_interface__ = {"shape": (1,), "typestr": "<i4", "data": (address, False), "version": 2}
+
+
+def device_status_tensor(device: Optional[torch.device] = None) -> torch.Tensor:
+    """The library's per-device status word as a 1-element int32 CUDA tensor (an alias, not a copy).
+
+    The kernels set bits in it when one of their bounded waits runs out (e.g. a CTA waited a second for
+    a partial result of another CTA because something else held SMs); the outputs of that launch are
+    then not valid although the call returned long before.  A serving loop that must not synchronise
+    can copy the word to pinned memory behind each step, ``status.to(pinned, non_blocking=True)`` on
+    the decode stream, and look at it when the step's results are consumed; ``status.zero_()`` clears it."""
+    lib = c_abi.load()
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with torch.cuda.device(dev):
+        addr = ctypes.c_void_p(0)
+        c_abi.check(lib.smla_device_status_address(ctypes.byref(addr)), "smla_device_status_address")
+        return torch.as_tensor(_DeviceWord(addr.value), device=dev)

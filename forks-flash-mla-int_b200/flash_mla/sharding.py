@@ -36,15 +36,22 @@ def shard_tokens(kwargs: Dict[str, object], world_size: int, rank: int) -> Dict[
 
 
 def gather_outputs(local_out: torch.Tensor, num_tokens: int, group=None) -> torch.Tensor:
-    """all_gather of ragged token shards into [num_tokens, H, 512] (outside any timed region)."""
+    """The token shards of all ranks as one [num_tokens, H, 512] tensor on every rank (a convenience
+    for harnesses, outside any timed region; the data path itself needs no collective)."""
     import torch.distributed as dist
     world = dist.get_world_size(group)
+    me = dist.get_rank(group)
     shards = []
     for r in range(world):
         a, b = token_range(num_tokens, world, r)
         shards.append(torch.empty((b - a,) + tuple(local_out.shape[1:]), dtype=local_out.dtype,
                                   device=local_out.device))
-    dist.all_gather(shards, local_out.contiguous(), group=group) if len({s.shape for s in shards}) == 1 else \
-        [dist.broadcast(s if r != dist.get_rank(group) else s.copy_(local_out), src=dist.get_global_rank(group, r) if group else r, group=group)
-         for r, s in enumerate(shards)]
+    if len({s.shape for s in shards}) == 1:
+        dist.all_gather(shards, local_out.contiguous(), group=group)
+    else:
+        # ragged shards (num_tokens not a multiple of the world size): one broadcast per rank
+        shards[me].copy_(local_out)
+        for r in range(world):
+            src = dist.get_global_rank(group, r) if group is not None else r
+            dist.broadcast(shards[r], src=src, group=group)
     return torch.cat(shards, dim=0)

@@ -91,10 +91,13 @@ SMLA_API const char *smla_error_string(int code);
  * whole (token, 64-head block) items are dealt out to the CTAs and nothing is merged.  A result
  * S > 1 means the 128-row tiles of all items are cut into equal contiguous ranges, one per CTA (so
  * ragged lens and fewer items than SMs still fill the GPU); a CTA then leaves up to two partial
- * segments in scratch and a second kernel merges them.  S is the scratch the schedule needs, in
- * partials per (token, head): two slots of 64 heads per CTA plus the merge descriptors.  Counterpart
- * of sparse_mla_num_splits (csrc/flash_api.cpp:75-102); the environment variable
- * FLASH_MLA_SLOTS_PER_SPLIT is honoured as the least number of rows a CTA is given (read per call). */
+ * segments in scratch.  They are merged inside the attention kernel -- by the CTA that holds an
+ * item's first tiles, in its own epilogue, or, for a few tokens spread over the whole GPU, slice-wise
+ * by all CTAs of the item -- and only between ~10 and ~70 items by a second small kernel (see
+ * smla_decode_kernel_launches).  S is the scratch the schedule needs, in partials per (token, head):
+ * two slots of 64 heads per CTA plus the merge descriptors.  Counterpart of sparse_mla_num_splits
+ * (csrc/flash_api.cpp:75-102); the environment variable FLASH_MLA_SLOTS_PER_SPLIT is honoured as the
+ * least number of rows a CTA is given (read per call). */
 SMLA_API int smla_choose_num_splits(int sm_count, int num_tokens, int num_heads, int max_width);
 
 /* Bytes of split-KV scratch (fp32 partial outputs + {max, denominator} pairs) for `num_splits`
@@ -112,11 +115,26 @@ SMLA_API int smla_decode_plan(int num_tokens, int num_heads, int max_width, int 
 /* Kernels one decode call launches on a device with `sm_count` SMs when given `num_splits` and its
  * workspace: 1 (whole items, or the balanced schedule with the merge fused into the attention kernel)
  * or 2 (attention kernel + combine kernel: between ~10 and ~70 items on a 148-SM part).  For accounting
- * (benchmarks, CUDA-graph node counts); no counterpart in the reference. */
+ * (benchmarks); no counterpart in the reference.  On a CAPTURING stream the slice-wise merge (at most
+ * ~8 tokens of 64 heads) is replaced by the combine kernel, because a replayed graph repeats the launch
+ * tag that merge relies on: smla_decode_kernel_launches_captured gives the kernel-node count of a
+ * captured decode call. */
 SMLA_API int smla_decode_kernel_launches(int sm_count, int num_tokens, int num_heads, int num_splits);
+SMLA_API int smla_decode_kernel_launches_captured(int sm_count, int num_tokens, int num_heads, int num_splits);
 
 /* Sparse MLA decode.  Replaces run_sparse_mla_decode (csrc/flash_mla.h:125,
- * csrc/flash_sparse_mla_decode_sm80.cu:1198-1275) for both cache formats. */
+ * csrc/flash_sparse_mla_decode_sm80.cu:1198-1275) for both cache formats.
+ *
+ * Waits inside the kernels.  With num_splits > 1 the in-kernel merges make a CTA wait for partial
+ * results of OTHER CTAs of the same launch (a 64-bit flag per scratch slot).  Those waits cannot
+ * deadlock when the persistent grid is resident -- a CTA only waits for another CTA's FIRST segment,
+ * which waits for nothing -- and when part of the grid is not resident (another kernel holds SMs, MPS,
+ * a green context) the resident CTAs are a prefix of the grid, of which only the last can be waiting
+ * for a CTA that has not started.  Every wait in the kernels is still bounded (one second): a wait
+ * that runs out sets a bit in a per-device status word, the CTA leaves through its normal teardown and
+ * the affected output rows are NOT valid although the call returned 0 long before.  Callers that share
+ * the GPU with long-running kernels should check smla_read_device_status when they next synchronise
+ * (it costs a device synchronisation), or use num_splits = 1 (whole items: no CTA waits for another). */
 SMLA_API int smla_sparse_mla_decode(const smla_attn_params_t *params, void *stream);
 
 /* Split-KV decode that brings its own scratch: same contract and results as smla_sparse_mla_decode,
@@ -128,10 +146,15 @@ SMLA_API int smla_sparse_mla_decode(const smla_attn_params_t *params, void *stre
  * pool, cudaMalloc would synchronise the device inside the latency-critical loop, and it is not
  * allowed during stream capture.  This function calls no allocator of any kind.
  *   - An explicit num_splits whose scratch (smla_attn_workspace_bytes) exceeds
- *     SMLA_STATIC_SCRATCH_BYTES is rejected with SMLA_ETOOBIG and nothing is launched; the automatic
- *     choice (num_splits == 0) is lowered until it fits.
+ *     SMLA_STATIC_SCRATCH_BYTES is rejected with SMLA_ETOOBIG and nothing is launched.  With the
+ *     automatic choice (num_splits == 0) the array is offered whole: what the kernels touch is two
+ *     partial slots per CTA (39 MB on a 148-SM part), however many tokens there are, so the balanced
+ *     schedule runs with as many CTAs as fit (all of them on B200).
  *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress, that
- *     device current); make that first call before any stream capture.
+ *     device current).  Under CUDA's lazy module loading that first use is also when the driver sets
+ *     the array's memory aside: make the first call per device at start-up -- BEFORE the engine claims
+ *     the rest of HBM and outside any stream capture -- and expect a positive cudaError_t (out of
+ *     memory) from it if the device is already full.
  *   - All calls on a device share the array, which keeps the previous call's contents (nothing in it
  *     needs clearing); calls whose kernels overlap on the GPU race on it. */
 #define SMLA_STATIC_SCRATCH_BYTES (64u << 20)
@@ -185,6 +208,14 @@ SMLA_API int smla_write_fp8_ds_mla_cache(const void *x, int x_dtype, int64_t row
 /* Reads and clears the per-device error word the kernels set when a bounded wait ran out
  * (0 = none).  Synchronises the device; meant for tests and debugging, not for hot paths. */
 SMLA_API int smla_read_device_status(int *status_out);
+
+/* Device address of that status word on the current device, for hosts that must not synchronise: copy
+ * the 4 bytes asynchronously on the decode stream behind a step (cudaMemcpyAsync to pinned memory) and
+ * look at them whenever the stream is next known to have passed that point.  Non-zero = a bounded wait
+ * ran out in some launch since the word was last cleared (smla_read_device_status clears it; so does a
+ * 4-byte cudaMemsetAsync by the caller).  No synchronisation, no allocation.  No counterpart in the
+ * reference, whose kernels have no waits between CTAs. */
+SMLA_API int smla_device_status_address(int **device_address);
 
 #ifdef __cplusplus
 }

@@ -82,3 +82,33 @@ class RefDecode:
         if rc != 0:
             raise RuntimeError(f"reference decode launch failed: cudaError {rc}")
         return self.out
+
+
+class RefPrefill:
+    """The reference's prefill launcher (csrc/flash_sparse_mla_prefill_fused_sm80.cu:468-506): for
+    fp8_ds_mla it first dequantises the WHOLE cache into a dense bf16 buffer of swa + extra slots
+    (allocated here once, csrc/flash_api.cpp:546-567), for int8_ds_mla the fused kernel gathers raw rows."""
+
+    def __init__(self, q, swa_cache, swa_scale, swa_indices, swa_lens, scale=None, attn_sink=None, extra_cache=None,
+                 extra_scale=None, extra_indices=None, extra_lens=None):
+        import torch
+        self.lib = _load()
+        int8 = swa_scale is not None
+        self.out = torch.empty_like(q)
+        slots = swa_cache.shape[0] * swa_cache.shape[1]
+        if extra_cache is not None:
+            slots += extra_cache.shape[0] * extra_cache.shape[1]
+        self.kv = None if int8 else torch.empty((slots, 512), dtype=torch.bfloat16, device=q.device)
+        self.keep = (q, swa_cache, swa_scale, swa_indices, swa_lens, attn_sink, extra_cache, extra_scale,
+                     extra_indices, extra_lens)
+        extra = (extra_cache, extra_scale, extra_indices, extra_lens) if extra_cache is not None else None
+        self.p = _params(q, self.out, int8, scale if scale is not None else 512 ** -0.5,
+                         (swa_cache, swa_scale, swa_indices, swa_lens), extra, attn_sink)
+
+    def __call__(self):
+        import torch
+        rc = self.lib.ref_sparse_mla_prefill(self.p, self.kv.data_ptr() if self.kv is not None else None,
+                                             torch.cuda.current_stream().cuda_stream)
+        if rc != 0:
+            raise RuntimeError(f"reference prefill launch failed: cudaError {rc}")
+        return self.out

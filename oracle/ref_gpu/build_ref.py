@@ -9,6 +9,9 @@ B200 (.github/workflows/wheels.yaml:33).  Nothing is copied into this repository
 directory is git-ignored.
 
     python oracle/ref_gpu/build_ref.py [/path/to/reference]
+
+Without an argument the checkout is taken from $REFERENCE_ROOT, else from a directory named
+``reference`` beside this repository.
 """
 import os
 import subprocess
@@ -20,7 +23,12 @@ OUT_DIR = os.path.join(ROOT, "oracle", "_ref")
 OUT = os.path.join(OUT_DIR, "libref_sparse_mla.so")
 
 
-def build(reference_root="/root/reference"):
+def default_reference_root():
+    return os.environ.get("REFERENCE_ROOT") or os.path.join(os.path.dirname(ROOT), "reference")
+
+
+def build(reference_root=None):
+    reference_root = reference_root or default_reference_root()
     csrc = os.path.join(reference_root, "csrc")
     srcs = [os.path.join(csrc, "flash_sparse_mla_decode_sm80.cu"),
             os.path.join(csrc, "flash_sparse_mla_prefill_fused_sm80.cu")]
@@ -35,4 +43,4 @@ def build(reference_root="/root/reference"):
 
 
 if __name__ == "__main__":
-    print(build(sys.argv[1] if len(sys.argv) > 1 else "/root/reference"))
+    print(build(sys.argv[1] if len(sys.argv) > 1 else None))

@@ -1,8 +1,8 @@
 #!/usr/bin/env python3
 """Generate the golden fixtures in this directory FROM THE REFERENCE'S OWN PYTHON CODE.
 
-Run once in a container that has the reference checkout (path in REFERENCE_ROOT;
-the .npz files it writes are committed and are the only
+Run once in a container that has the reference checkout (path in REFERENCE_ROOT, else a
+directory named ``reference`` beside this repository); the .npz files it writes are committed and are the only
 thing the tests read.  Imported from the reference (nothing is copied):
 
 * ``_ref``                      tests/test_sparse_mla_prefill_adversarial.py:25-53
@@ -25,8 +25,9 @@ import sys
 import numpy as np
 import torch
 
-REF = os.environ.get("REFERENCE_ROOT", "/root/reference")
 HERE = os.path.dirname(os.path.abspath(__file__))
+# the reference checkout: $REFERENCE_ROOT, else a directory named "reference" beside this repository
+REF = os.environ.get("REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(HERE))), "reference")
 sys.path.insert(0, os.path.join(REF, "tests"))
 sys.path.insert(0, os.path.join(REF, "benchmarks"))
 

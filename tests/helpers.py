@@ -1,20 +1,27 @@
 """Shared helpers for the GPU parity tests: cache builders (oracle packers -> device tensors),
 the oracle call on device inputs, and the tolerance checks.
 
-Tolerances (stated once).  Outputs are bf16 and P is rounded to bf16 before PV (as in the
-reference kernels), so an output of magnitude x carries an error of up to about x * 2^-7 whatever
-the implementation: the golden fixtures built with the reference's deterministic packer reach
-|x| = 20 and the x50 outlier rows of BASELINE config 3 reach |x| = 160, where a CPU emulation of the
-algorithm (bf16 P, fp32 accumulation, bf16 output) is already 1.0 away from the fp32 oracle.  Bounds:
-    |out - ref| <= 2e-2 + 2e-2 |ref| + 2^-7 max_d |ref[t, h, :]|   elementwise: the reference's own gate,
-                                       assert_close(rtol=2e-2, atol=2e-2), tests/test_sparse_mla_prefill_adversarial.py:92-95,
-                                       plus one bf16 quantum of the (token, head) output row: where a few
-                                       large rows nearly cancel, the bf16 rounding of their weights is an
-                                       error relative to THEIR size, not to the small result
-    mean|out - ref| <= 2e-3 + 2^-8 mean|ref|
-    cos_diff < 8e-5                    (the reference's gate, same file)
-and, for N(0,1)-scale workloads without outlier rows (``strict_abs=True``), the plain north-star
+Tolerances (stated once).  The gate is the reference's own, verbatim
+(tests/test_sparse_mla_prefill_adversarial.py:92-95):
+    |out - ref| <= 2e-2 + 2e-2 |ref|      elementwise (torch.testing.assert_close(rtol=2e-2, atol=2e-2))
+    cos_diff(out, ref) < 8e-5
+and, for N(0,1)-scale workloads without outlier rows (``strict_abs=True``), also the plain north-star
 bounds max-abs <= 2e-2 and mean-abs <= 2e-3.
+
+One documented exception.  Outputs are bf16 and P is rounded to bf16 before PV (in the reference's
+kernels too), so where a few very large rows nearly cancel -- the x50 outlier rows of BASELINE config 3
+reach |out| = 160 -- the rounding of their weights is an error relative to THEIR size, not to the small
+result, and no bf16-P implementation meets the elementwise bound.  A test may pass
+``reference_kernel=`` (the output of the REFERENCE'S OWN CUDA kernel, oracle/ref_gpu, on the same inputs,
+or a function that computes it).
+The helper then first proves that the reference's kernel misses the plain gate on these inputs by a
+comparable margin -- at least a quarter of this library's excess: both kernels round P to bf16, and which
+elements of a row of cancelling +-200 values land outside the gate is rounding luck (the same token moves in
+and out of the gate with the split count in the reference's own kernel) -- and only then is one bf16 quantum
+of the (token, head) output row, 2^-7 max_d |ref[t, h, :]|, added to the elementwise bound.  For a sweep over
+slices of ONE data set the evidence may be given once, as ``reference_excess=`` (the reference kernel's
+excess over the plain gate on a slice of the same data).  If the reference's kernel passes the plain gate,
+so must this library: the widened bound is refused.
 """
 from __future__ import annotations
 
@@ -70,21 +77,70 @@ def oracle_out(q, swa_K, swa_idx, swa_lens, extra_K=None, extra_idx=None, extra_
                                        scale=scale, sink=n(sink), tokens=tokens)
 
 
-def assert_attention_close(out: torch.Tensor, ref: np.ndarray, what="", tokens=None, strict_abs=False):
+def gate_excess(got: np.ndarray, ref: np.ndarray, row_quantum: bool = False) -> float:
+    """Largest amount by which |got - ref| exceeds 2e-2 + 2e-2 |ref| (negative: inside the gate)."""
+    bound = MAX_ABS + 2e-2 * np.abs(ref)
+    if row_quantum:
+        bound = bound + 2.0 ** -7 * np.abs(ref).max(-1, keepdims=True)
+    return float((np.abs(got - ref) - bound).max())
+
+
+COMPARABLE = 0.25
+
+
+def assert_attention_close(out: torch.Tensor, ref: np.ndarray, what="", tokens=None, strict_abs=False,
+                           reference_kernel=None, reference_excess=None):
     got = out.detach().float().cpu().numpy()
     if tokens is not None:
         got, ref = got[tokens], ref[tokens]
+        if reference_kernel is not None and not callable(reference_kernel):
+            reference_kernel = reference_kernel[tokens]
     assert not np.isnan(got).any(), f"{what}: NaN in output"
     d = np.abs(got - ref)
     cd = oracle.cos_diff(got, ref) if (np.any(ref) or np.any(got)) else 0.0      # all-zero vs all-zero: equal
-    excess = (d - (MAX_ABS + 2e-2 * np.abs(ref) + 2.0 ** -7 * np.abs(ref).max(-1, keepdims=True))).max()
-    assert excess <= 0, f"{what}: error exceeds atol 2e-2 + rtol 2e-2 + row quantum by {excess:.3e} (max-abs {d.max():.3e})"
-    mean_bound = MEAN_ABS + 2.0 ** -8 * np.abs(ref).mean()
-    assert d.mean() <= mean_bound, f"{what}: mean-abs {d.mean():.3e} > {mean_bound:.3e}"
+    excess = gate_excess(got, ref)
+    if excess > 0 and reference_excess is not None:
+        assert reference_excess > 0 and reference_excess >= COMPARABLE * excess, (
+            f"{what}: outside the reference's gate by {excess:.3e}; on this data set the reference's own kernel is "
+            f"{'inside it' if reference_excess <= 0 else f'only {reference_excess:.3e} outside'}: a bug, not bf16 rounding")
+        excess = gate_excess(got, ref, row_quantum=True)
+        assert excess <= 0, f"{what}: error exceeds atol 2e-2 + rtol 2e-2 + row quantum by {excess:.3e} (max-abs {d.max():.3e})"
+    elif excess > 0 and reference_kernel is not None:
+        if callable(reference_kernel):          # only run the reference's kernel when it is needed
+            reference_kernel = reference_kernel()
+            if reference_kernel is not None and tokens is not None:
+                reference_kernel = reference_kernel[tokens]
+        assert reference_kernel is not None, (
+            f"{what}: outside the reference's gate by {excess:.3e} and the reference's kernels (oracle/_ref) are "
+            f"not built here to compare with")
+        theirs = np.asarray(reference_kernel, dtype=np.float32)
+        their_excess = gate_excess(theirs, ref)
+        assert their_excess > 0 and their_excess >= COMPARABLE * excess, (
+            f"{what}: outside the reference's gate by {excess:.3e} where the reference's own kernel is "
+            f"{'inside it' if their_excess <= 0 else f'only {their_excess:.3e} outside'}: a bug, not bf16 rounding")
+        excess = gate_excess(got, ref, row_quantum=True)
+        assert excess <= 0, f"{what}: error exceeds atol 2e-2 + rtol 2e-2 + row quantum by {excess:.3e} (max-abs {d.max():.3e})"
+    else:
+        assert excess <= 0, f"{what}: error exceeds atol 2e-2 + rtol 2e-2 |ref| by {excess:.3e} (max-abs {d.max():.3e})"
     assert cd < COS_DIFF, f"{what}: cos_diff {cd:.3e} >= {COS_DIFF}"
     if strict_abs:
         assert d.max() <= MAX_ABS, f"{what}: max-abs {d.max():.3e} > {MAX_ABS}"
         assert d.mean() <= MEAN_ABS, f"{what}: mean-abs {d.mean():.3e} > {MEAN_ABS}"
+
+
+def reference_kernel_out(kw: dict, prefill: bool = False):
+    """Output of the reference's own CUDA kernel on the keyword arguments of a flash_mla call
+    (numpy fp32), or None where oracle/_ref is not built."""
+    from oracle import ref_gpu
+    if not ref_gpu.available():
+        return None
+    cls = ref_gpu.RefPrefill if prefill else ref_gpu.RefDecode
+    run = cls(kw["q"], kw["swa_cache"], kw.get("swa_scale"), kw["swa_indices"], kw["swa_lens"], kw.get("scale"),
+              kw.get("attn_sink"), kw.get("extra_cache"), kw.get("extra_scale"), kw.get("extra_indices"),
+              kw.get("extra_lens"))
+    out = run().float().cpu().numpy()
+    torch.cuda.synchronize()
+    return out
 
 
 def device_status() -> int:

@@ -13,7 +13,7 @@ import pytest
 import torch
 
 from helpers import (assert_attention_close, bf16_from_bits, device_status, fp8_cache_from_latent,
-                     int8_cache_from_latent, oracle_out, to_dev)
+                     int8_cache_from_latent, oracle_out, reference_kernel_out, to_dev)
 import oracle
 
 pytestmark = pytest.mark.gpu
@@ -238,13 +238,27 @@ def test_decode_int8_swa_only_and_index_head_dim(fm):
 
 def test_decode_int8_split_stability(fm, monkeypatch):
     """...int8_adversarial.py:298-354: split-KV must not change the result beyond fp32-partial noise
-    (RMSE < 5e-4, max <= 2^-8) -- compare the automatic split count with one split."""
+    (RMSE < 5e-4, max <= 2^-8) -- compare the automatic split count with one split.  The caches are the
+    reference test's: uniform random int8 codes with row scales in [1e-4, 0.02]
+    (tests/test_sparse_mla_prefill_int8_adversarial.py:44-61).  The softmax reference of a segment is its
+    own running maximum, as in the reference's kernels, so P rounds to bf16 differently for different
+    cuts; the bound is the reference's."""
     from flash_mla import c_abi
-    rng = np.random.default_rng(43)
     torch.manual_seed(43)
     T, H, st, et = 1, 64, 128, 4096
-    sq, ss, swa_K, _b1 = int8_cache_from_latent(_rand_latent(rng, 512, 2.0), 128, "inline528")
-    eq, es, extra_K, _b2 = int8_cache_from_latent(_rand_latent(rng, 4096, 2.0), 64, "inline528")
+
+    def inline_cache(slots, bs):
+        nb = (slots + bs - 1) // bs
+        buf = torch.zeros(nb, bs, 528, dtype=torch.uint8, device="cuda")
+        buf[:, :, :512] = torch.randint(0, 256, (nb, bs, 512), dtype=torch.uint8, device="cuda")
+        sc = (torch.rand(nb, bs, device="cuda") * 0.02 + 1e-4).float()
+        buf[:, :, 512:516] = sc.view(nb, bs, 1).view(torch.uint8)
+        data, scale = buf[:, :, :512].view(torch.int8), buf[:, :, 512:516].view(torch.float32).squeeze(-1)
+        K = oracle.dequant_int8_ds_mla(data.contiguous().cpu().numpy(), scale.contiguous().cpu().numpy())
+        return data, scale, K, buf
+
+    sq, ss, swa_K, _b1 = inline_cache(512, 128)
+    eq, es, extra_K, _b2 = inline_cache(4096, 64)
     q = torch.randn(T, H, 512, device="cuda").to(torch.bfloat16)
     si = torch.randint(0, 512, (T, st), dtype=torch.int32, device="cuda")
     ei = torch.stack([torch.randperm(4096, device="cuda")[:et].int() for _ in range(T)])
@@ -374,7 +388,8 @@ def test_outlier_rows_and_large_scores(fm):
     lens = torch.full((T,), topk, dtype=torch.int32, device="cuda")
     ref = oracle_out(q, K, idx, lens, scale=SCALE)
     out = fm.sparse_mla_decode_int8(q, sq, ss, idx, lens, scale=SCALE)
-    assert_attention_close(out, ref, "outliers")
+    kw = dict(q=q, swa_cache=sq, swa_scale=ss, swa_indices=idx, swa_lens=lens, scale=SCALE)
+    assert_attention_close(out, ref, "outliers", reference_kernel=lambda: reference_kernel_out(kw))
 
 
 def test_scores_jump_far_above_the_first_tile(fm):
@@ -649,7 +664,7 @@ def test_decode_dsv4_shape_vs_oracle(fm, fmt, T, H):
     extra (block 64, top-k 2048), ~2 % masked ids, lens in [topk/2, topk], sink; N(0,1) data, so the
     plain max-abs 2e-2 / mean-abs 2e-3 bounds apply to fp8; the int8 variant has 5 % of its rows scaled
     x50 (config 3), whose outputs reach |x| ~ 100 and are held to the relative gate."""
-    from flash_mla import synthetic
+    import bench_workloads as synthetic
     kw, meta = synthetic.decode_workload(fmt=fmt, T=T, H=H, seed=3)
     op = fm.sparse_mla_decode_fp8 if fmt == "fp8" else fm.sparse_mla_decode_int8
     out = op(**kw)
@@ -662,7 +677,8 @@ def test_decode_dsv4_shape_vs_oracle(fm, fmt, T, H):
                                              kw["extra_scale"].contiguous().cpu().numpy())
     ref = oracle_out(kw["q"], swa_K, kw["swa_indices"], kw["swa_lens"], extra_K, kw["extra_indices"], kw["extra_lens"],
                      sink=kw["attn_sink"])
-    assert_attention_close(out, ref, f"{fmt} T={T} H={H}", strict_abs=(fmt == "fp8"))  # int8: x50 outlier rows
+    assert_attention_close(out, ref, f"{fmt} T={T} H={H}", strict_abs=(fmt == "fp8"),  # int8: x50 outlier rows
+                           reference_kernel=lambda: reference_kernel_out(kw))
 
 
 def test_full_size_properties_config2(fm):
@@ -670,7 +686,7 @@ def test_full_size_properties_config2(fm):
     (a) the order of a token's selected rows does not matter (softmax-weighted sum is permutation
     invariant); (b) a token whose rows are all the same slot returns that row when there is no sink;
     (c) sampled tokens agree with the oracle."""
-    from flash_mla import synthetic
+    import bench_workloads as synthetic
     kw, meta = synthetic.decode_workload(fmt="fp8", T=128, H=64, seed=0)
     out = fm.sparse_mla_decode_fp8(**kw)
     # (a) reverse each token's valid prefix in both streams
@@ -702,7 +718,7 @@ def test_full_size_properties_config2(fm):
 
 def test_prefill_int8_causal_config4_reduced(fm):
     """BASELINE config 4 geometry at T=512 (causal top-k with -1 padding, extra stream on p // 4)."""
-    from flash_mla import synthetic
+    import bench_workloads as synthetic
     kw, meta = synthetic.prefill_int8_workload(T=512, H=64, swa_slots=2048, swa_topk=1024, extra_slots=512,
                                                extra_topk=256, seed=4)
     out = fm.sparse_mla_prefill_int8(**kw)
@@ -712,12 +728,200 @@ def test_prefill_int8_causal_config4_reduced(fm):
     toks = [0, 1, 2, 3, 5, 127, 128, 129, 300, 511]
     ref = oracle_out(kw["q"], swa_K, kw["swa_indices"], kw["swa_lens"], extra_K, kw["extra_indices"], kw["extra_lens"],
                      sink=kw["attn_sink"], tokens=toks)
-    assert_attention_close(out, ref, "config 4 reduced", tokens=toks)
+    assert_attention_close(out, ref, "config 4 reduced", tokens=toks,
+                           reference_kernel=lambda: reference_kernel_out(kw, prefill=True))
+
+
+# ----------------------------------------------------------------------------- BASELINE configs at full geometry
+def _dequant_for_oracle(kw, fmt):
+    if fmt == "fp8":
+        swa_K = oracle.dequant_fp8_ds_mla(kw["swa_cache"].cpu().numpy())
+        extra_K = oracle.dequant_fp8_ds_mla(kw["extra_cache"].cpu().numpy())
+    else:
+        swa_K = oracle.dequant_int8_ds_mla(kw["swa_cache"].contiguous().cpu().numpy(), kw["swa_scale"].contiguous().cpu().numpy())
+        extra_K = oracle.dequant_int8_ds_mla(kw["extra_cache"].contiguous().cpu().numpy(),
+                                             kw["extra_scale"].contiguous().cpu().numpy())
+    return swa_K, extra_K
+
+
+@pytest.fixture(scope="module")
+def config3_data():
+    """BASELINE config 3's data once per cache layout: 65536-slot swa + 16384-slot extra int8 caches from
+    quantize_int8_ds_mla_rows with 5 % of the rows scaled x50, 512 tokens x 128 heads of queries and
+    indices; the sweep points are slices of it."""
+    import bench_workloads as synthetic
+    from helpers import gate_excess
+    made, evidence = {}, {}
+
+    def slice_of(full, T, H):
+        kw = dict(full)
+        for k in ("swa_indices", "swa_lens", "extra_indices", "extra_lens"):
+            kw[k] = full[k][:T].contiguous()
+        kw["q"] = full["q"][:T, :H].contiguous()
+        kw["attn_sink"] = full["attn_sink"][:H].contiguous()
+        return kw
+
+    def get(layout):
+        if layout not in made:
+            kw, _ = synthetic.decode_workload(fmt="int8", T=512, H=128, seed=33, layout=layout)
+            made[layout] = (kw, _dequant_for_oracle(kw, "int8"))
+        return made[layout]
+
+    def reference_excess(layout, H):
+        """How far the REFERENCE'S OWN CUDA kernel is outside the plain gate on this data (128 tokens, 8
+        sampled): the evidence the row-quantum allowance needs (tests/helpers.py).  None without oracle/_ref."""
+        if (layout, H) not in evidence:
+            full, (swa_K, extra_K) = get(layout)
+            kw = slice_of(full, 128, H)
+            theirs = reference_kernel_out(kw)
+            toks = [0, 18, 42, 64, 85, 106, 126, 127]
+            if theirs is None:
+                evidence[(layout, H)] = None
+            else:
+                ref = oracle_out(kw["q"], swa_K, kw["swa_indices"], kw["swa_lens"], extra_K, kw["extra_indices"],
+                                 kw["extra_lens"], sink=kw["attn_sink"], tokens=toks)
+                evidence[(layout, H)] = gate_excess(theirs[toks], ref[toks])
+        return evidence[(layout, H)]
+
+    get.slice_of = slice_of
+    get.reference_excess = reference_excess
+    return get
+
+
+@pytest.mark.parametrize("layout", ["inline528", "separate"])
+@pytest.mark.parametrize("H", [64, 128])
+@pytest.mark.parametrize("T", [1, 8, 32, 128, 512])
+def test_config3_full_geometry(fm, config3_data, T, H, layout):
+    """Every (T, H) point of BASELINE config 3 at DSV4 geometry (top-k 512 + 2048, ~2 % masked ids, lens
+    in [topk/2, topk], sink, x50 outlier rows), both int8 layouts, against the oracle on up to 8 sampled
+    tokens -- under the reference's own gate; a case may use the row-quantum allowance only after the
+    reference's CUDA kernel has been shown to miss the plain gate on the same inputs (tests/helpers.py).
+    Mirrors tests/test_sparse_mla_decode_int8_adversarial.py:179-295 (serving shapes at size)."""
+    full, (swa_K, extra_K) = config3_data(layout)
+    kw = config3_data.slice_of(full, T, H)
+    out = fm.sparse_mla_decode_int8(**kw)
+    toks = sorted({0, T // 7, T // 3, T // 2, (2 * T) // 3, (5 * T) // 6, max(T - 2, 0), T - 1})
+    ref = oracle_out(kw["q"], swa_K, kw["swa_indices"], kw["swa_lens"], extra_K, kw["extra_indices"], kw["extra_lens"],
+                     sink=kw["attn_sink"], tokens=toks)
+    assert_attention_close(out, ref, f"config 3 int8 {layout} T={T} H={H}", tokens=toks,
+                           reference_excess=config3_data.reference_excess(layout, H))
+
+
+def test_config4_full_geometry(fm):
+    """BASELINE config 4 at size: 4096 query tokens x 64 heads, int8 inline cache of 16384 slots with causal
+    top-k 2048 (-1 padding, lens min(p + 1, 2048)), extra stream of 4096 slots / top-k 512 on p // 4, sink.
+    Sampled positions include the edges of the causal rule."""
+    import bench_workloads as synthetic
+    kw, meta = synthetic.prefill_int8_workload(T=4096, H=64, seed=4)
+    out = fm.sparse_mla_prefill_int8(**kw)
+    swa_K, extra_K = _dequant_for_oracle(kw, "int8")
+    toks = [0, 1, 2, 3, 127, 128, 2047, 2048, 3000, 4095]
+    ref = oracle_out(kw["q"], swa_K, kw["swa_indices"], kw["swa_lens"], extra_K, kw["extra_indices"], kw["extra_lens"],
+                     sink=kw["attn_sink"], tokens=toks)
+    assert_attention_close(out, ref, "config 4", tokens=toks,
+                           reference_kernel=lambda: reference_kernel_out(kw, prefill=True))
+
+
+@pytest.mark.parametrize("fmt", ["fp8", "int8"])
+def test_config5_full_geometry(fm, fmt):
+    """BASELINE config 5's batch: 1024 tokens x 128 heads, 16384-slot caches, full lens 2048 + 512, both
+    formats; token sample against the oracle, and the token-sharded result (8 shards run one after the
+    other on this GPU) equals the unsharded one bit for bit."""
+    import bench_workloads as synthetic
+    from flash_mla.sharding import shard_tokens, token_range
+    kw, meta = synthetic.decode_workload(fmt=fmt, T=1024, H=128, swa_slots=16384, swa_topk=2048, extra_slots=16384,
+                                         extra_topk=512, mask_frac=0.0, full_lens=True, seed=5)
+    op = fm.sparse_mla_decode_fp8 if fmt == "fp8" else fm.sparse_mla_decode_int8
+    out = op(**kw)
+    swa_K, extra_K = _dequant_for_oracle(kw, fmt)
+    toks = [0, 341, 682, 1023]
+    ref = oracle_out(kw["q"], swa_K, kw["swa_indices"], kw["swa_lens"], extra_K, kw["extra_indices"], kw["extra_lens"],
+                     sink=kw["attn_sink"], tokens=toks)
+    assert_attention_close(out, ref, f"config 5 {fmt}", tokens=toks, strict_abs=(fmt == "fp8"),
+                           reference_kernel=lambda: reference_kernel_out(kw))
+    # the shards take the balanced schedule (items cut into segments), the whole batch whole items: the
+    # results agree as the reference's split and unsplit decode do
+    # (tests/test_sparse_mla_decode_int8_adversarial.py:298-354: RMSE < 5e-4, max <= 2^-8 on N(0,1) data)
+    for r in (0, 3, 7):
+        a, b = token_range(1024, 8, r)
+        part = op(**shard_tokens(kw, 8, r))
+        assert part.shape == out[a:b].shape
+        if fmt == "fp8":
+            d = (part.float() - out[a:b].float())
+            assert d.abs().max().item() <= 2.0 ** -8 and d.pow(2).mean().sqrt().item() < 5e-4, f"shard {r} of 8"
+        else:           # x50 outlier rows: one bf16 quantum of the row
+            top = out[a:b].float().abs().amax(dim=-1, keepdim=True)
+            assert ((part.float() - out[a:b].float()).abs() <= 2.0 ** -7 * top + 2.0 ** -8).all(), f"shard {r} of 8"
+
+
+@pytest.mark.parametrize("which", ["prefill_int8", "prefill_fp8", "decode_int8", "decode_fp8"])
+def test_peak_memory_independent_of_pool_size(fm, which):
+    """The ops allocate nothing sized by the KV pool: against a 600,000-slot pool with a tiny selection the
+    peak allocation of a call stays below its output plus (decode) the split-KV scratch the library asks
+    for plus 1 MiB.  A whole-pool bf16 buffer would be 586 MiB.  Mirrors
+    tests/test_sparse_mla_prefill_int8_memory.py:37-74 for all four operators."""
+    from flash_mla import c_abi
+    T, H, topk, bs, slots = 8, 64, 64, 64, 600_000
+    nb = (slots + bs - 1) // bs
+    g = torch.Generator(device="cuda").manual_seed(7)
+    q = torch.randn(T, H, 512, device="cuda", generator=g).to(torch.bfloat16)
+    idx = torch.randint(0, slots, (T, topk), device="cuda", generator=g, dtype=torch.int32)
+    lens = torch.full((T,), topk, dtype=torch.int32, device="cuda")
+    if which.endswith("int8"):
+        buf = torch.zeros(nb, bs, 528, dtype=torch.uint8, device="cuda")
+        buf[:, :, :512] = torch.randint(0, 256, (nb, bs, 512), dtype=torch.uint8, device="cuda", generator=g)
+        sc = (torch.rand(nb, bs, device="cuda", generator=g) * 0.02 + 1e-4).float()
+        buf[:, :, 512:516] = sc.view(nb, bs, 1).view(torch.uint8)
+        data, scale = buf[:, :, :512].view(torch.int8), buf[:, :, 512:516].view(torch.float32).squeeze(-1)
+        op = fm.sparse_mla_prefill_int8 if which.startswith("prefill") else fm.sparse_mla_decode_int8
+        call = lambda: op(q, data, scale, idx, lens, scale=SCALE)
+    else:
+        cache = torch.zeros(nb, bs, 584, dtype=torch.uint8, device="cuda")
+        cache[:, :, :448] = torch.randint(0, 120, (nb, bs, 448), dtype=torch.uint8, device="cuda", generator=g)   # finite e4m3 codes
+        cache.view(nb, bs * 584)[:, bs * 576:] = 127                                                               # scales 2^0
+        op = fm.sparse_mla_prefill if which.startswith("prefill") else fm.sparse_mla_decode_fp8
+        call = lambda: op(q, cache, idx, lens, scale=SCALE)
+    call()
+    torch.cuda.synchronize()
+    torch.cuda.reset_peak_memory_stats()
+    baseline = torch.cuda.memory_allocated()
+    out = call()
+    torch.cuda.synchronize()
+    peak = torch.cuda.max_memory_allocated() - baseline
+    scratch = 0
+    if which.startswith("decode"):
+        splits, nbytes = ctypes.c_int(1), ctypes.c_size_t(0)
+        c_abi.check(c_abi.load().smla_decode_plan(T, H, topk, ctypes.byref(splits), ctypes.byref(nbytes)), "smla_decode_plan")
+        scratch = nbytes.value
+    bound = out.numel() * out.element_size() + scratch + (1 << 20)
+    assert peak < bound, f"{which}: peak allocation {peak / 2**20:.2f} MiB, budget {bound / 2**20:.2f} MiB (pool: 600k slots)"
+    assert torch.isfinite(out.float()).all()
+
+
+def test_status_word_without_a_device_synchronisation(fm):
+    """The status word as a tensor: an alias of the device word (not a copy), zero after ordinary calls,
+    readable with an asynchronous copy on the stream of the decode calls."""
+    word = fm.device_status_tensor()
+    assert word.dtype == torch.int32 and word.numel() == 1 and word.is_cuda
+    g = torch.Generator().manual_seed(5)
+    cache, _ = fp8_cache_from_latent(torch.randn(1024, 512, generator=g).numpy(), 64)
+    q = torch.randn(4, 64, 512, generator=g).to(torch.bfloat16).cuda()
+    idx = torch.randint(0, 1024, (4, 256), generator=g, dtype=torch.int32).cuda()
+    lens = torch.full((4,), 256, dtype=torch.int32, device="cuda")
+    pinned = torch.full((1,), -1, dtype=torch.int32).pin_memory()
+    fm.sparse_mla_decode_fp8(q, cache, idx, lens)
+    pinned.copy_(word, non_blocking=True)
+    torch.cuda.current_stream().synchronize()
+    assert int(pinned[0]) == 0
+    word.fill_(8)                                   # what a kernel does when a wait runs out
+    assert device_status() == 8                     # the synchronising reader sees the same word ... and clears it
+    assert int(word.item()) == 0
 
 
 def test_host_pipeline_matches_plain_calls(fm):
     """Steps staggered over three streams (copy in / kernel / copy out) with buffers reused every
-    third step give, for every step, the output of the plain call on that step's inputs."""
+    third step give, for every step, the output of the plain call on that step's inputs.  Each step's
+    inputs travel as ONE packed pinned buffer."""
     from flash_mla.host_pipeline import HostPipeline
     T, H, n, topk = 16, 64, 2048, 512
     g = torch.Generator().manual_seed(77)
@@ -735,9 +939,15 @@ def test_host_pipeline_matches_plain_calls(fm):
     example = {k: v.cuda() for k, v in steps[0].items()}
     want = [run({k: v.cuda() for k, v in st.items()}, 0).cpu() for st in steps]
     pipe = HostPipeline(run, example, want[0].cuda(), depth=3)
+    packed = []
+    for st in steps:
+        buf, views = pipe.new_host_inputs()
+        for k, v in st.items():
+            views[k].copy_(v)
+        packed.append(buf)
     got = []
-    for i, st in enumerate(steps):
-        t = pipe.submit(i, st)
+    for i, buf in enumerate(packed):
+        pipe.submit(i, buf)
         if i >= 2:                                     # read step i-2 before its slot comes round again
             got.append(pipe.result((i - 2) % 3).clone())
     pipe.drain()

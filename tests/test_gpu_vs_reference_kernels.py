@@ -17,7 +17,7 @@ def test_matches_reference_cuda_kernels(fmt, T, H):
     if not ref_gpu.available():
         pytest.skip("oracle/_ref/libref_sparse_mla.so not built (needs the reference checkout)")
     import flash_mla
-    from flash_mla import synthetic
+    import bench_workloads as synthetic
     kw, meta = synthetic.decode_workload(fmt=fmt, T=T, H=H, swa_slots=4096, extra_slots=4096, swa_topk=256,
                                          extra_topk=768, seed=9, outlier_frac=0.0)
     op = flash_mla.sparse_mla_decode_fp8 if fmt == "fp8" else flash_mla.sparse_mla_decode_int8
@@ -42,7 +42,7 @@ def test_random_shapes_match_reference_cuda_kernels(seed):
     if not ref_gpu.available():
         pytest.skip("oracle/_ref/libref_sparse_mla.so not built (needs the reference checkout)")
     import flash_mla
-    from flash_mla import synthetic
+    import bench_workloads as synthetic
     from helpers import device_status
     rng = np.random.default_rng(seed)
     for it in range(60):

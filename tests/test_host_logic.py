@@ -107,6 +107,10 @@ def test_split_policy_and_workspace():
     assert k(148, 32, 64, f(148, 32, 64, 2560)) == 2        # in between: attention kernel + combine kernel
     assert k(148, 1024, 64, 1) == 1                         # whole items, nothing to merge
     assert k(148, 128, 64, 2) == 1                          # scratch for 62 CTAs only: still two or three segments per item
+    kc = lib.smla_decode_kernel_launches_captured           # on a capturing stream the slice merge gives way to the combine kernel
+    assert kc(148, 1, 64, f(148, 1, 64, 2560)) == 2 and kc(148, 8, 64, f(148, 8, 64, 2560)) == 2
+    assert kc(148, 128, 64, f(148, 128, 64, 2560)) == 1 and kc(148, 32, 64, f(148, 32, 64, 2560)) == 2
+    assert kc(148, 1024, 64, 1) == 1
     w = lib.smla_attn_workspace_bytes
     assert w(4, 64, 1) == 0
     assert w(4, 64, 8) == 4 * 64 * 8 * (512 + 2) * 4

@@ -70,6 +70,20 @@ def test_static_scratch_decode_matches_regular_decode_twice():
     c_abi.check(lib.smla_sparse_mla_decode(_params(c_abi, c, want, 1), stream))
     torch.cuda.synchronize()
     assert_attention_close(got, want.float().cpu().numpy(), "auto splits vs one split")
+    # automatic choice at 128 tokens x 128 heads: the policy's formula (67 MB) is more than the array
+    # holds, what the kernels touch (39 MB on 148 SMs) is not: the balanced schedule must still run, with the
+    # same CTAs -- hence the same bits -- as the regular entry point given a workspace of the formula's size
+    c = _case(505, T=128, H=128)
+    got, want = torch.empty_like(c["q"]), torch.empty_like(c["q"])
+    import ctypes
+    auto, nbytes = ctypes.c_int(0), ctypes.c_size_t(0)
+    c_abi.check(lib.smla_decode_plan(128, 128, 128 + 1024, ctypes.byref(auto), ctypes.byref(nbytes)))
+    assert auto.value > 1 and nbytes.value > c_abi.SMLA_STATIC_SCRATCH_BYTES
+    ws = torch.empty(nbytes.value // 4, dtype=torch.float32, device="cuda")
+    c_abi.check(lib.smla_sparse_mla_decode_static_scratch(_params(c_abi, c, got, 0), stream))
+    c_abi.check(lib.smla_sparse_mla_decode(_params(c_abi, c, want, 0, ws), stream))
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
     assert device_status() == 0
 
 
