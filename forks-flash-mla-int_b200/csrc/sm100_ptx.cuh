@@ -169,21 +169,6 @@ __device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t (&r)[16]) {
         : "r"(taddr)
         : "memory");
 }
-// The same load without the wait: the registers may only be read after tmem_ld_fence_x16(r), which waits
-// for every tcgen05.ld of this thread and names the registers so that the compiler keeps their readers behind it.
-__device__ __forceinline__ void tmem_ld_x16_async(uint32_t taddr, uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_ld_fence_x16(uint32_t (&r)[16]) {
-    asm volatile("tcgen05.wait::ld.sync.aligned;"
-                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
-                 :
-                 : "memory");
-}
 // registers -> 16 consecutive 32-bit columns of this thread's TMEM lane (call tmem_st_wait after).
 __device__ __forceinline__ void tmem_st_x16(uint32_t taddr, const uint32_t (&r)[16]) {
     asm volatile(
@@ -214,23 +199,6 @@ __host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n, int a_mn_ma
            (static_cast<uint32_t>(b_mn_major) << 16) | (static_cast<uint32_t>(n >> 3) << 17) |
            (static_cast<uint32_t>(m >> 4) << 24);
 }
-// Same, with each descriptor given as (low word, high word): lets the caller step the start
-// address with 32-bit adds.
-__device__ __forceinline__ void umma_bf16_ss_lohi(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
-                                                  uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        ".reg .b64 da, db;\n\t"
-        "setp.ne.b32 p, %6, 0;\n\t"
-        "mov.b64 da, {%1, %2};\n\t"
-        "mov.b64 db, {%3, %4};\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t"
-        "}"
-        :
-        : "r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
 // One lane of a converged warp (1 in that lane, 0 in the others).
 __device__ __forceinline__ uint32_t elect_one() {
     uint32_t r;
@@ -260,7 +228,8 @@ __device__ __forceinline__ void umma_bf16_ss_pred(uint32_t d_tmem, uint64_t a_de
         : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(go)
         : "memory");
 }
-// umma_commit by the lane with `go` != 0 (same use as umma_bf16_ss_pred).
+// Arrive on an mbarrier once every tcgen05 operation this thread issued so far has completed; issued by
+// the lane with `go` != 0 (same use as umma_bf16_ss_pred).
 __device__ __forceinline__ void umma_commit_pred(uint32_t bar, uint32_t go) {
     asm volatile(
         "{\n\t"
@@ -272,12 +241,6 @@ __device__ __forceinline__ void umma_commit_pred(uint32_t bar, uint32_t go) {
         : "r"(bar), "r"(go)
         : "memory");
 }
-// Arrive on an mbarrier once every tcgen05 operation this thread issued so far has completed.
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
-                 : "memory");
-}
-
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

@@ -1413,18 +1413,26 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
             // sm = S^T * scale - m, with m read once per tile (the same for all rows).
             const bool row_valid = row < rows_left;
             float sm[CW];
+            bool need = first_tile;
             {
+                // The reference max m is only moved when some score exceeds it by more than its threshold
+                // (always on a segment's first tile).  The vote spans the four warps that share these
+                // columns.  m and the thresholds are read four columns at a time (one broadcast load each).
                 uint32_t sraw[CW];
                 TmemIO<CW>::ld(tmem_lane + col0, sraw);
 #pragma unroll
-                for (int j = 0; j < CW; ++j)
-                    sm[j] = row_valid ? fmaf(__uint_as_float(sraw[j]), a.scale_log2, -m_s[col0 + j]) : -INFINITY;
-            }
-            // The reference max m is only moved when some score exceeds it by more than the threshold
-            // (always on a segment's first tile).  The vote spans the four warps that share these columns.
-            bool need = first_tile;
+                for (int v = 0; v < CW / 4; ++v) {
+                    const float4 m4 = *reinterpret_cast<const float4 *>(m_s + col0 + 4 * v);
+                    const float4 t4 = *reinterpret_cast<const float4 *>(thr_s + col0 + 4 * v);
+                    const float mm[4] = {m4.x, m4.y, m4.z, m4.w}, tt[4] = {t4.x, t4.y, t4.z, t4.w};
 #pragma unroll
-            for (int j = 0; j < CW; ++j) need |= sm[j] > thr_s[col0 + j];
+                    for (int u = 0; u < 4; ++u) {
+                        const int j = 4 * v + u;
+                        sm[j] = row_valid ? fmaf(__uint_as_float(sraw[j]), a.scale_log2, -mm[u]) : -INFINITY;
+                        need |= sm[j] > tt[u];
+                    }
+                }
+            }
             if (named_bar_or(group_bar, 128, need)) {
                 // Scores relative to the OLD reference are kept (not re-read from tensor memory, not held
                 // as raw values): s - m_new = (s - m_old) + (m_old - m_new); for the row that sets the new
@@ -1453,7 +1461,12 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
                 lacc *= alpha_s[col0 + (lane >> kColShift)];
 #pragma unroll
                 for (int j = 0; j < CW; ++j) sm[j] += shift_s[col0 + j];
-                if (!first_tile) {   // O^T[:, h] *= alpha[h]; the previous PV completed before this tile's S^T did
+                // O^T[:, h] *= alpha[h]; the previous PV completed before this tile's S^T did.  Only the column
+                // slices in which some head moved are touched (the same answer in all four warps of a slice).
+                bool moved = false;
+#pragma unroll
+                for (int j = 0; j < CW; ++j) moved |= alpha_s[col0 + j] != 1.0f;
+                if (!first_tile && moved) {
 #pragma unroll 1
                     for (int c = 0; c < 4; ++c) {
                         uint32_t o[CW];
