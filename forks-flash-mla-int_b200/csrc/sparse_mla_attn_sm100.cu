@@ -55,30 +55,6 @@ namespace smla {
 
 __device__ int g_device_status = 0;
 
-#ifdef SMLA_TRACE   // developer timing trace of one CTA (never defined in the product build)
-#ifndef SMLA_TRACE_CTA
-#define SMLA_TRACE_CTA 0
-#endif
-__device__ unsigned long long g_trace[32 * 16];
-#define SMLA_MARK(tile, k)                                                              \
-    do {                                                                                \
-        if (blockIdx.x == SMLA_TRACE_CTA && (tile) < 32) g_trace[(tile) * 16 + (k)] = clock64(); \
-    } while (0)
-__device__ unsigned long long g_cta_times[256 * 8];
-__device__ __forceinline__ unsigned long long smla_globaltimer() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-#define SMLA_CTA_MARK(k)                                                                        \
-    do {                                                                                        \
-        if (threadIdx.x == 0 && blockIdx.x < 256) g_cta_times[blockIdx.x * 8 + (k)] = smla_globaltimer(); \
-    } while (0)
-#else
-#define SMLA_MARK(tile, k) do {} while (0)
-#define SMLA_CTA_MARK(k) do {} while (0)
-#endif
-
 namespace {
 
 constexpr int kD = 512;
@@ -755,6 +731,16 @@ __device__ __forceinline__ void publish_segment(const KernelArgs &a, int *sched,
         }
         zero_item(a, s, lane, 32);
     }
+    if (ok && lane < 5) {
+        // Warm L2 (and the TLB) with the slot ids of the segment's first tile: nobody has touched that
+        // token's index row yet, and the workers need the ids in the last tile of the segment before,
+        // to issue the gather.  Records are published three segments ahead, so the lines have arrived by then.
+        const int g0 = s.tile0 * kTileRows;
+        const int g = min(g0 + lane * 32, min(g0 + kTileRows, s.n) - 1);
+        const int *ip = g < s.ns ? a.swa.indices + static_cast<long long>(s.t) * a.swa.idx_stride + g
+                                 : a.extra.indices + static_cast<long long>(s.t) * a.extra.idx_stride + (g - s.ns);
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(ip));
+    }
     {   // warm the lens of the tokens the next calls will ask for (lane i: i + 1 items ahead)
         const long long ahead = a.balanced ? static_cast<long long>(it.t) + lane
                                            : (static_cast<long long>(it.item) + static_cast<long long>(lane) * it.stride) / a.head_blocks;
@@ -869,7 +855,6 @@ __device__ __forceinline__ void mma_role(uint8_t *smem, uint32_t tmem_base) {
         if ((rec[7] & kSegValid) == 0) break;
         const int ntl = rec[5];
         for (int it = 0; it < ntl; ++it, ++gt) {
-            SMLA_MARK(gt, 0);
             if (it == 0 && !mbar_wait(bars + kBarQ * 8, so & 1, abort_flag)) {   // this item's Q tile
                 if (lane == 0) give_up(abort_flag, kStatusMmaWait);
                 return;
@@ -888,7 +873,6 @@ __device__ __forceinline__ void mma_role(uint8_t *smem, uint32_t tmem_base) {
                 }
             }
             umma_commit_pred(bars + kBarS * 8, go);
-            SMLA_MARK(gt, 1);
             if (!mbar_wait(bars + kBarP * 8, gt & 1, abort_flag)) {
                 if (lane == 0) give_up(abort_flag, kStatusMmaWait);
                 return;
@@ -902,7 +886,6 @@ __device__ __forceinline__ void mma_role(uint8_t *smem, uint32_t tmem_base) {
                 return;
             }
             tc_fence_after_sync();
-            SMLA_MARK(gt, 5);
             const uint32_t acc0 = it > 0 ? 1u : 0u;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
@@ -915,7 +898,6 @@ __device__ __forceinline__ void mma_role(uint8_t *smem, uint32_t tmem_base) {
                 umma_commit_pred(bars + (kBarFree + c) * 8, go);   // chunk c of the K buffer may be refilled
             }
             if (it + 1 == ntl) umma_commit_pred(bars + kBarO * 8, go);
-            SMLA_MARK(gt, 6);
         }
     }
 }
@@ -1142,8 +1124,6 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
     float *shift_s = reinterpret_cast<float *>(smem + L::kShift);
     float *thr_s = reinterpret_cast<float *>(smem + L::kThr);
     const int tid = warp * 32 + lane;
-    const bool tracer = (warp == 0 && lane == 0);
-    (void)tracer;
 
     // convert job
     const int quarter = lane >> 3;
@@ -1183,7 +1163,6 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
         float *wk_s = reinterpret_cast<float *>(smem + L::kK);     // [others][NPAD] weights (the K buffer is idle: last segment)
         warp_wait(bars + kBarO * 8, parity, abort_flag, lane, kStatusEpilogueWait);
         tc_fence_after_sync();
-        if (tracer) SMLA_MARK(gt < 32 ? gt : 31, 13);
         store_col_partial<CW>(red + q * NPAD + col0, lacc, lane);
         lacc = 0.0f;
         if (owner && warp == 0) {
@@ -1327,7 +1306,6 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(bars + kBarOFree * 8);     // the next segment's first PV may overwrite O^T
-        if (tracer) SMLA_MARK(gt < 32 ? gt : 31, 14);
     };
 
     uint4 raw[J];
@@ -1370,7 +1348,6 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 if (gt > 0) warp_wait(bars + (kBarFree + c) * 8, (gt - 1) & 1, abort_flag, lane, kStatusGatherWait);
-                if (tracer && c == 0) SMLA_MARK(gt, 7);
                 if constexpr (FMT == kFmtInt8Wide) {
                     // chunk c = pieces 8c .. 8c+7 of the row; which registers hold them depends on the
                     // row's alignment (see load_row_pieces)
@@ -1388,12 +1365,10 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
                         if (mine) convert_step<FMT>(raw[j], j, quarter, cur.sc0, cur.sc1, k_row_addr);
                     }
                 }
-                if (tracer && (c == 0 || c == 3)) SMLA_MARK(gt, 8 + c);
                 fence_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bars + (kBarReady + c) * 8);
             }
-            if (tracer) SMLA_MARK(gt, 12);
             // Raw bytes of the next tile.  Issued only now, after this tile's last conversion fence: a
             // proxy fence also waits for the thread's global loads in flight, so loads issued between
             // the chunks would put a memory latency on every hand-over.  They land while QK^T runs.
@@ -1409,7 +1384,6 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
             // ---- softmax of this tile
             warp_wait(bars + kBarS * 8, gt & 1, abort_flag, lane, kStatusSoftmaxWait);
             tc_fence_after_sync();
-            if (tracer) SMLA_MARK(gt, 2);
             // sm = S^T * scale - m, with m read once per tile (the same for all rows).
             const bool row_valid = row < rows_left;
             float sm[CW];
@@ -1478,7 +1452,6 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
                     tmem_st_wait();
                 }
             }
-            if (tracer) SMLA_MARK(gt, 3);
             {   // P^T = 2^(S^T - m) rounded to bf16, MN-major B-operand layout (8 heads = 16 bytes per row)
                 uint32_t pk[CW / 2];
 #pragma unroll
@@ -1500,7 +1473,6 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
                     asm volatile("st.shared.v2.b32 [%0], {%1,%2};" ::"r"(p_addr), "r"(pk[0]), "r"(pk[1]) : "memory");
                 }
             }
-            if (tracer) SMLA_MARK(gt, 4);
             fence_async_smem();
             tc_fence_before_sync();
             __syncwarp();
@@ -1528,7 +1500,6 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const __gri
     using L = Smem<NPAD>;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
-    SMLA_CTA_MARK(0);
     // ---- this CTA's share of the work
     int *sched = reinterpret_cast<int *>(smem + L::kSched);
     if (a.balanced && !a.fused_merge && tid == 0) reinterpret_cast<int4 *>(a.desc)[blockIdx.x] = make_int4(-1, 0, 0, 0);
@@ -1545,7 +1516,6 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const __gri
         }
     }
     __syncthreads();
-    SMLA_CTA_MARK(3);
     // ---- set-up, three things side by side: first segment record, barriers, tensor memory
     if (warp == 0) publish_segment(a, sched, 0, lane);      // sets the published count to 1
     if (tid == 32) {
@@ -1568,7 +1538,6 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const __gri
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
-    SMLA_CTA_MARK(4);
     if ((sched[kSchedRec + 7] & kSegValid) == 0) {   // nothing but items without rows
         if (warp == kMmaWarp) tmem_dealloc(*reinterpret_cast<volatile uint32_t *>(smem + L::kTmemPtr), kTmemCols);
         return;
@@ -1584,13 +1553,11 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const __gri
             reinterpret_cast<float *>(smem + L::kThr)[tid] = move_threshold(m0);
         }
     }
-    SMLA_CTA_MARK(5);
     fence_async_smem();
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(smem + L::kTmemPtr);
-    SMLA_CTA_MARK(1);
 
     if (warp < kWorkerWarps) {
         worker_role<FMT, NPAD>(a, smem, tmem_base, warp, lane);
@@ -1607,7 +1574,6 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const __gri
     }
 
     __syncthreads();
-    SMLA_CTA_MARK(2);
     if (warp == kMmaWarp) {
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, kTmemCols);
@@ -1835,17 +1801,6 @@ int launch_sparse_mla_attention(const smla_attn_params_t &p, int num_splits, voi
     }
     return rc;
 }
-
-#ifdef SMLA_TRACE
-extern "C" __attribute__((visibility("default"))) int smla_debug_read_trace(unsigned long long *host_out) {
-    cudaDeviceSynchronize();
-    return static_cast<int>(cudaMemcpyFromSymbol(host_out, g_trace, sizeof(unsigned long long) * 32 * 16));
-}
-extern "C" __attribute__((visibility("default"))) int smla_debug_read_cta_times(unsigned long long *host_out) {
-    cudaDeviceSynchronize();
-    return static_cast<int>(cudaMemcpyFromSymbol(host_out, g_cta_times, sizeof(unsigned long long) * 256 * 8));
-}
-#endif
 
 int read_and_clear_device_status(int *status_out) {
     int v = 0;
