@@ -55,6 +55,10 @@ WORKLOADS = {
                                                           extra_slots=16384, extra_topk=512, mask_frac=0.0,
                                                           full_lens=True)),
     "int8_prefill_T4096_H64": ("prefill_int8", dict(T=4096, H=64)),
+    # dense paged MLA decode (flash_mla_with_kvcache): the reference's dense test shapes, bf16 cache, pages of 64
+    "dense_bf16_decode_b128_s4096_h128": ("dense", dict(b=128, s_q=1, mean_sk=4096, h_q=128, varlen=False)),
+    "dense_bf16_decode_b128_s4096_h16": ("dense", dict(b=128, s_q=1, mean_sk=4096, h_q=16, varlen=False)),
+    "dense_bf16_decode_b128_s8192_h64_sq2_varlen": ("dense", dict(b=128, s_q=2, mean_sk=8192, h_q=64, varlen=True)),
     # cache writers (the step before the attention calls): 2^20 new bf16 latent rows scattered into a paged cache
     "write_int8_cache_rows1M": ("write_int8", dict(rows=1 << 20, block_size=64)),
     "write_fp8_cache_rows1M": ("write_fp8", dict(rows=1 << 20, block_size=64)),
@@ -646,6 +650,138 @@ def config5_record(world, rank, dev, barrier, repeats=10, steps=5):
     return out
 
 
+# ----------------------------------------------------------------------------- dense paged MLA decode
+def dense_oracle_sample(kw, causal, budget_s=12.0):
+    """The CPU oracle on as many sequences (from the first) as fit the time budget."""
+    import oracle
+    import torch
+    cpu = {k: v.detach().cpu() for k, v in kw.items()}
+    t0 = time.perf_counter()
+    oracle.dense_mla_decode(cpu["q"], cpu["k_cache"], cpu["block_table"], cpu["cache_seqlens"], causal=causal, sequences=[0])
+    per = max(time.perf_counter() - t0, 1e-4)
+    n = int(max(1, min(cpu["q"].shape[0], budget_s / per)))
+    t0 = time.perf_counter()
+    out, lse = oracle.dense_mla_decode(cpu["q"], cpu["k_cache"], cpu["block_table"], cpu["cache_seqlens"], causal=causal,
+                                       sequences=list(range(n)))
+    return n, time.perf_counter() - t0, out, lse, torch.get_num_threads()
+
+
+def run_dense_reference(a, kw_build):
+    """Reference arm of the dense workloads: the reference's dense path is CUDA only (and needs its cutlass
+    submodule, absent from the checkout), so the arm times the CPU oracle port on a bounded sample."""
+    import bench_workloads
+    small = dict(kw_build, b=min(kw_build["b"], 8))
+    kw, _ = bench_workloads.dense_decode_workload(device="cpu", seed=0, **small)
+    causal = kw_build["s_q"] > 1
+    toks = 0
+    t_all = 0.0
+    for _ in range(a.steps):
+        n, dt, _, _, threads = dense_oracle_sample(kw, causal, budget_s=6.0)
+        toks += n * kw_build["s_q"]
+        t_all += dt
+    val = toks / t_all
+    print(json.dumps({
+        "impl": "reference", "metric": "dense MLA decode tokens/s", "value": val, "unit": "tokens/s", "n_gpus": a.gpus,
+        "steps": a.steps, "warmup": a.warmup, "ms_per_step": t_all / a.steps * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": a.workload, **kw_build},
+        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": threads, "kind": "port",
+                         "sample": f"{n} sequences of the batch per step, {a.steps} steps"},
+        "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+
+
+def run_dense(a, kw_build, world, rank, local, dev, barrier):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    import flash_mla
+    import bench_workloads
+    import oracle
+    kw, meta = bench_workloads.dense_decode_workload(device=dev, seed=rank, **kw_build)
+    causal = kw_build["s_q"] > 1
+    md, ns = flash_mla.get_mla_metadata(kw["cache_seqlens"], kw_build["s_q"] * kw_build["h_q"], 1)
+    tokens = kw_build["b"] * kw_build["s_q"]
+
+    def step(q=None):
+        return flash_mla.flash_mla_with_kvcache(kw["q"] if q is None else q, kw["k_cache"], kw["block_table"],
+                                                kw["cache_seqlens"], 512, md, ns, causal=causal)
+
+    def timed(fn, steps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    for _ in range(a.warmup):
+        step()
+    sampler = ClockSampler(local) if rank == 0 else None
+    ms = timed(step, a.steps)
+    clocks = sampler.stop() if sampler else None
+
+    # end to end: q from pinned host memory, out and lse back to pinned host memory, every step (the cache stays in HBM)
+    hq = kw["q"].cpu().pin_memory()
+    dq = torch.empty_like(kw["q"])
+    out0, lse0 = step()
+    hout = torch.empty(out0.shape, dtype=out0.dtype).pin_memory()
+    hlse = torch.empty(lse0.shape, dtype=lse0.dtype).pin_memory()
+
+    def e2e_step():
+        dq.copy_(hq, non_blocking=True)
+        o, l = step(dq)
+        hout.copy_(o, non_blocking=True)
+        hlse.copy_(l, non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    e2e_steps = max(3, min(a.steps, 10))
+    ms_e2e = timed(e2e_step, e2e_steps)
+
+    if rank == 0:
+        cache_bytes = kw["k_cache"].numel() * 2
+        line = {
+            "metric": "dense MLA decode tokens/s", "value": world * tokens * a.steps / (ms / 1e3), "unit": "tokens/s",
+            "n_gpus": world, "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms / a.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": a.workload, **kw_build, "page_block_size": kw["k_cache"].shape[1],
+                       "l2": f"{cache_bytes / 2**20:.0f} MiB cache read per step > 126 MiB L2",
+                       "sharding": "sequences sharded across GPUs, no collective"},
+            "roofline": roofline_record(meta, ms / a.steps / 1e3, a.workload),
+            "tflops": meta["flops"] / (ms / a.steps / 1e3) / 1e12,
+            "e2e": {"value": world * tokens * e2e_steps / (ms_e2e / 1e3), "unit": "tokens/s",
+                    "h2d_bytes_per_step": hq.numel() * 2, "d2h_bytes_per_step": hout.numel() * 2 + hlse.numel() * 4,
+                    "ms_per_step": ms_e2e / e2e_steps, "steps": e2e_steps,
+                    "note": "q from pinned host memory, out and lse back to pinned host memory, every step; the paged cache stays in HBM"},
+            "gpu_launches": a.steps,
+            "device_status": int(flash_mla.device_status_tensor().item()),
+        }
+        if clocks:
+            line["clocks"] = clocks
+        if world == 1 and not a.no_cpu_baseline:
+            n, dt, ref_out, ref_lse, threads = dense_oracle_sample(kw, causal)
+            line["cpu_baseline"] = {"value": n * kw_build["s_q"] / dt, "unit": "tokens/s", "cores": threads, "kind": "port",
+                                    "sample": f"first {n} of {kw_build['b']} sequences of the same step"}
+            got, got_lse = out0[:n].float().cpu().numpy(), lse0[:n].cpu().numpy()
+            line["parity"] = {"sequences_checked": n, "cos_diff_out": oracle.cos_diff(got, ref_out[:n]),
+                              "cos_diff_lse": oracle.cos_diff(got_lse, ref_lse[:n]),
+                              "max_abs_out": float(np.abs(got - ref_out[:n]).max()),
+                              "max_abs_lse": float(np.abs(got_lse - ref_lse[:n]).max()),
+                              "gate": "cos_diff < 8e-5 for out and lse (the reference's dense test)"}
+            line["parity"]["within_gate"] = bool(line["parity"]["cos_diff_out"] < 8e-5 and line["parity"]["cos_diff_lse"] < 8e-5)
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -659,6 +795,10 @@ def main():
     a.warmup = max(a.warmup, 3) if a.impl == "native" else a.warmup
 
     if a.impl == "reference":
+        if WORKLOADS[a.workload][0] == "dense":
+            if int(os.environ.get("RANK", "0")) == 0:
+                run_dense_reference(a, WORKLOADS[a.workload][1])
+            return
         run_reference(a)
         return
 
@@ -682,6 +822,9 @@ def main():
 
     if WORKLOADS[a.workload][0].startswith("write"):
         run_writer(a, *WORKLOADS[a.workload], world, rank, local, dev, barrier)
+        return
+    if WORKLOADS[a.workload][0] == "dense":
+        run_dense(a, WORKLOADS[a.workload][1], world, rank, local, dev, barrier)
         return
 
     run = AttentionRun(a.workload, dev, seed=rank)

@@ -180,3 +180,33 @@ def prefill_int8_workload(T: int = 4096, H: int = 64, swa_slots: int = 16384, sw
                 flops=4 * H * 512 * rows_in,
                 bytes=rows_valid * 516 + 2 * (T * H * 512 * 2) + 4 * rows_in + 8 * T + 4 * H, keep=keep)
     return kw, meta
+
+
+def dense_decode_workload(b: int = 128, s_q: int = 1, mean_sk: int = 4096, h_q: int = 128, varlen: bool = False,
+                          block_size: int = 64, seed: int = 0, device="cuda", poison_tail: bool = True):
+    """The reference's dense test case (tests/test_flash_mla_sm80.py:43-63): ``b`` sequences of ``mean_sk`` rows
+    (``varlen``: normal around it with sigma mean_sk / 2, at least s_q), q and the bf16 cache N(0, 1), pages in
+    a scrambled order, rows past each length NaN so that any read of them shows in the result."""
+    gen = _gen(device, seed)
+    d = 576
+    lens = torch.full((b,), mean_sk, dtype=torch.int32)
+    if varlen:
+        cpu_gen = torch.Generator().manual_seed(seed + 1)
+        lens = (torch.randn(b, generator=cpu_gen) * (mean_sk / 2) + mean_sk).clamp(min=s_q).to(torch.int32)
+    max_pad = (int(lens.max()) + 255) // 256 * 256
+    pages_per_seq = max_pad // block_size
+    perm = torch.randperm(b * pages_per_seq, generator=torch.Generator().manual_seed(seed + 2))
+    block_table = perm.to(torch.int32).view(b, pages_per_seq).to(device)
+    q = torch.randn(b, s_q, h_q, d, generator=gen, device=device, dtype=torch.float32).to(torch.bfloat16)
+    k_cache = torch.empty(b * pages_per_seq, block_size, 1, d, device=device, dtype=torch.bfloat16)
+    for i in range(b):           # sequence by sequence: a 128 x 8192 batch is 1.2 GB of bf16
+        rows = torch.randn(max_pad, 1, d, generator=gen, device=device, dtype=torch.float32).to(torch.bfloat16)
+        if poison_tail:
+            rows[int(lens[i]):] = float("nan")
+        k_cache[block_table[i].long()] = rows.view(pages_per_seq, block_size, 1, d)
+    lens = lens.to(device)
+    rows_total = int(lens.sum()) * s_q        # without the causal trim (at most s_q - 1 rows per query)
+    meta = {"flops": 2 * rows_total * h_q * (576 + 512),
+            "bytes": int(lens.sum()) * 1152 + b * s_q * h_q * (576 + 512) * 2 + b * pages_per_seq * 4,
+            "rows_in_lens": rows_total}
+    return {"q": q, "k_cache": k_cache, "block_table": block_table, "cache_seqlens": lens}, meta

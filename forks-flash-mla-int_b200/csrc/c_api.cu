@@ -139,6 +139,32 @@ int smla_sparse_mla_decode(const smla_attn_params_t *p, void *stream) {
     return smla::launch_sparse_mla_attention(*p, splits, p->workspace, p->workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
+int smla_dense_mla_decode(const smla_dense_params_t *p, void *stream) {
+    if (!p) return SMLA_EINVAL;
+    DevInfo d;
+    int rc = device_info(d);
+    if (rc != SMLA_OK) return rc;
+    if (d.major != 10) return SMLA_EARCH;
+    if (p->batch <= 0 || p->seqlen_q <= 0 || p->num_heads <= 0 || p->page_block_size <= 0 || p->block_table_stride < 0)
+        return SMLA_EINVAL;
+    const long long tokens_ll = static_cast<long long>(p->batch) * p->seqlen_q;
+    if (tokens_ll > 0x7FFFFFFFLL) return SMLA_ETOOBIG;
+    const int tokens = static_cast<int>(tokens_ll);
+    smla_dense_params_t q = *p;
+    if (q.num_splits < 0) return SMLA_EINVAL;
+    if (q.num_splits == 0) {
+        // The sequences' lengths live on the device: the policy sees the longest a block table row allows.
+        const long long width = std::min<long long>(p->block_table_stride * p->page_block_size, 0x7FFFFFFFLL);
+        q.num_splits = smla_choose_num_splits(d.sm_count, tokens, p->num_heads, static_cast<int>(width));
+        if (q.num_splits > 1 && (!p->workspace || p->workspace_bytes < smla_attn_workspace_bytes(tokens, p->num_heads, q.num_splits)))
+            q.num_splits = 1;
+    } else if (q.num_splits > 1) {
+        if (!p->workspace || p->workspace_bytes < smla_attn_workspace_bytes(tokens, p->num_heads, q.num_splits))
+            return SMLA_EWORKSPACE;
+    }
+    return smla::launch_dense_mla_attention(q, static_cast<cudaStream_t>(stream));
+}
+
 int smla_sparse_mla_prefill(const smla_attn_params_t *p, void *stream) {
     if (!p) return SMLA_EINVAL;
     DevInfo d;

@@ -304,6 +304,87 @@ void write_ds_mla_cache(const char *what, bool fp8, const Tensor &latent_in, con
     }
 }
 
+// ------------------------------------------------------------------ dense paged MLA
+// fwd_kvcache_mla / get_mla_metadata of the reference (csrc/flash_api.cpp:110-157, 159-322; schemas at
+// :811-814).  The persistent kernel cuts the work itself from the sequence lengths on the device, so the
+// metadata tensors are placeholders of the reference's dtypes that fwd_kvcache_mla accepts and ignores.
+void get_mla_metadata(const Tensor &seqlens_k, Tensor &tile_scheduler_metadata, Tensor &num_splits) {
+    STD_TORCH_CHECK(seqlens_k.scalar_type() == ScalarType::Int, "seqlens_k must have dtype int32");
+    STD_TORCH_CHECK(seqlens_k.dim() == 1, "seqlens_k must have shape (batch_size,)");
+    tile_scheduler_metadata = torch::stable::new_zeros(seqlens_k, {1, 8});
+    num_splits = torch::stable::new_zeros(seqlens_k, {seqlens_k.size(0) + 1});
+}
+
+void fwd_kvcache_mla(const Tensor &q_in, const Tensor &kcache, const std::optional<Tensor> &vcache, int64_t head_size_v,
+                     const Tensor &seqlens_k, const Tensor &block_table_in, double softmax_scale, bool is_causal,
+                     Tensor &out, Tensor &softmax_lse) {
+    STD_TORCH_CHECK(q_in.is_cuda() && kcache.is_cuda() && seqlens_k.is_cuda() && block_table_in.is_cuda(),
+                    "q, kcache, seqlens_k and block_table must be on CUDA");
+    STD_TORCH_CHECK(q_in.dim() == 4, "q must have shape (batch_size, seqlen_q, num_heads, head_size)");
+    STD_TORCH_CHECK(q_in.scalar_type() == ScalarType::BFloat16 && kcache.scalar_type() == ScalarType::BFloat16,
+                    "query and key must be bfloat16");
+    STD_TORCH_CHECK(q_in.size(3) == 576 && head_size_v == 512, "only head_size 576 with head_size_v 512 is built");
+    STD_TORCH_CHECK(kcache.dim() == 4 && kcache.size(2) == 1 && kcache.size(3) == 576,
+                    "kcache must have shape (num_blocks, page_block_size, 1, 576)");
+    STD_TORCH_CHECK(kcache.stride(3) == 1, "Input tensor must have contiguous last dimension");
+    if (vcache.has_value())
+        STD_TORCH_CHECK(vcache->data_ptr() == kcache.data_ptr(), "vcache must be a view of kcache (or None)");
+    STD_TORCH_CHECK(block_table_in.scalar_type() == ScalarType::Int && block_table_in.dim() == 2,
+                    "block_table must be an int32 (batch_size, max_num_blocks_per_seq) tensor");
+    STD_TORCH_CHECK(seqlens_k.scalar_type() == ScalarType::Int, "seqlens_k must have dtype int32");
+    const int64_t B = q_in.size(0), SQ = q_in.size(1), H = q_in.size(2);
+    STD_TORCH_CHECK(B > 0, "batch size must be postive");
+    STD_TORCH_CHECK(seqlens_k.dim() == 1 && seqlens_k.size(0) == B && block_table_in.size(0) == B,
+                    "seqlens_k / block_table do not match the batch size");
+    const int device = q_in.get_device_index();
+    torch::stable::accelerator::DeviceGuard guard(device);
+
+    // Tokens are (sequence, query position) pairs: q is read as [B * SQ, H, 576].
+    const bool q_ok = q_in.stride(3) == 1 && q_in.stride(0) == SQ * q_in.stride(1) && q_in.stride(1) % 8 == 0 &&
+                      q_in.stride(2) % 8 == 0 && aligned16(q_in);
+    const Tensor q = q_ok ? q_in : torch::stable::contiguous(q_in);
+    const Tensor block_table = block_table_in.stride(1) == 1 ? block_table_in : torch::stable::contiguous(block_table_in);
+    const Tensor lens = seqlens_k.is_contiguous() ? seqlens_k : torch::stable::contiguous(seqlens_k);
+    out = torch::stable::new_empty(q, {B, SQ, H, 512});
+    softmax_lse = torch::stable::new_empty(q, {B, H, SQ}, ScalarType::Float);
+
+    smla_dense_params_t p = {};
+    p.batch = static_cast<int32_t>(B);
+    p.seqlen_q = static_cast<int32_t>(SQ);
+    p.num_heads = static_cast<int32_t>(H);
+    p.causal = is_causal ? 1 : 0;
+    p.softmax_scale = static_cast<float>(softmax_scale);
+    p.q = q.data_ptr();
+    p.q_token_stride = q.stride(1);
+    p.q_head_stride = q.stride(2);
+    p.out = out.data_ptr();
+    p.out_token_stride = out.stride(1);
+    p.out_head_stride = out.stride(2);
+    p.softmax_lse = static_cast<float *>(softmax_lse.data_ptr());
+    p.k_cache = kcache.data_ptr();
+    p.k_block_stride = kcache.stride(0) * 2;
+    p.k_row_stride = kcache.stride(1) * 2;
+    p.num_blocks = static_cast<int32_t>(kcache.size(0));
+    p.page_block_size = static_cast<int32_t>(kcache.size(1));
+    p.block_table = static_cast<const int32_t *>(block_table.data_ptr());
+    p.block_table_stride = block_table.stride(0);
+    p.cache_seqlens = static_cast<const int32_t *>(lens.data_ptr());
+
+    const int64_t width = std::min<int64_t>(block_table.size(1) * kcache.size(1), 0x7FFFFFFF);
+    int splits = 1;
+    size_t ws_bytes = 0;
+    check_rc(smla_decode_plan(static_cast<int>(B * SQ), p.num_heads, static_cast<int>(width), &splits, &ws_bytes),
+             "dense MLA decode plan");
+    std::optional<Tensor> workspace;
+    if (splits > 1) {
+        workspace = torch::stable::new_empty(q, {static_cast<int64_t>((ws_bytes + 3) / 4)}, ScalarType::Float);
+        p.workspace = workspace->data_ptr();
+        p.workspace_bytes = ws_bytes;
+    }
+    p.num_splits = splits;
+    check_rc(smla_dense_mla_decode(&p, current_stream(device)), "dense MLA decode");
+}
+
 // ------------------------------------------------------------------ boxed shims
 using torch::stable::detail::from;
 using torch::stable::detail::to;
@@ -354,6 +435,21 @@ void boxed_quantize(StableIValue *stack, uint64_t, uint64_t) {
     stack[1] = from(s);
 }
 
+void boxed_get_mla_metadata(StableIValue *stack, uint64_t, uint64_t) {
+    Tensor meta, splits;
+    get_mla_metadata(to<Tensor>(stack[0]), meta, splits);
+    stack[0] = from(meta);
+    stack[1] = from(splits);
+}
+
+void boxed_fwd_kvcache_mla(StableIValue *stack, uint64_t, uint64_t) {
+    Tensor out, lse;
+    fwd_kvcache_mla(to<Tensor>(stack[0]), to<Tensor>(stack[1]), to<std::optional<Tensor>>(stack[2]), to<int64_t>(stack[3]),
+                    to<Tensor>(stack[4]), to<Tensor>(stack[5]), to<double>(stack[6]), to<bool>(stack[7]), out, lse);
+    stack[0] = from(out);
+    stack[1] = from(lse);
+}
+
 void boxed_decode_planned(StableIValue *stack, uint64_t, uint64_t) {
     fwd_sparse_decode_mla_planned(to<Tensor>(stack[0]), to<Tensor>(stack[1]), to<std::optional<Tensor>>(stack[2]),
                                   to<Tensor>(stack[3]), to<Tensor>(stack[4]), to<double>(stack[5]),
@@ -389,6 +485,10 @@ STABLE_TORCH_LIBRARY(flash_mla, m) {
           "Tensor swa_indices, Tensor swa_lens, float scale, Tensor? attn_sink, "
           "Tensor? extra_cache, Tensor? extra_scale, Tensor? extra_indices, Tensor? extra_lens) -> Tensor");
     m.def("quantize_int8_ds_mla_rows(Tensor k) -> (Tensor, Tensor)");
+    m.def("get_mla_metadata(Tensor seqlens_k, int num_heads_per_head_k, int num_heads_k) -> (Tensor, Tensor)");
+    m.def("fwd_kvcache_mla(Tensor q, Tensor kcache, Tensor? vcache, int head_size_v, Tensor seqlens_k, "
+          "Tensor block_table, float softmax_scale, bool is_causal, Tensor tile_scheduler_metadata, "
+          "Tensor num_splits, bool warp_spec) -> (Tensor, Tensor)");
     m.def("fwd_sparse_decode_mla_planned(Tensor q, Tensor swa_cache, Tensor? swa_scale, Tensor swa_indices, "
           "Tensor swa_lens, float scale, Tensor? attn_sink, Tensor? extra_cache, Tensor? extra_scale, "
           "Tensor? extra_indices, Tensor? extra_lens, Tensor(a!) out, Tensor? workspace) -> ()");
@@ -402,6 +502,8 @@ STABLE_TORCH_LIBRARY_IMPL(flash_mla, CUDA, m) {
     m.impl("fwd_sparse_int8_prefill_mla", &boxed_int8<true>);
     m.impl("fwd_sparse_int8_decode_mla", &boxed_int8<false>);
     m.impl("quantize_int8_ds_mla_rows", &boxed_quantize);
+    m.impl("get_mla_metadata", &boxed_get_mla_metadata);
+    m.impl("fwd_kvcache_mla", &boxed_fwd_kvcache_mla);
     m.impl("fwd_sparse_decode_mla_planned", &boxed_decode_planned);
     m.impl("write_int8_ds_mla_cache", &boxed_write_int8);
     m.impl("write_fp8_ds_mla_cache", &boxed_write_fp8);

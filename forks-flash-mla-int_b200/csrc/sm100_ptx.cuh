@@ -80,6 +80,10 @@ __device__ __forceinline__ void cp_async_16_zfill(uint32_t dst, const void *src,
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// Waits until at most N of this thread's committed cp.async groups are still in flight.
+template <int N>
+__device__ __forceinline__ void cp_async_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ void fence_async_smem() {   // generic-proxy smem writes -> async proxy (tensor core)
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }

@@ -31,6 +31,7 @@ int launch_write_fp8_ds_mla(const void *x, int x_dtype, int64_t rows, int64_t x_
 // smla_attn_workspace_bytes(T, H, num_splits).
 int launch_sparse_mla_attention(const smla_attn_params_t &p, int num_splits, void *workspace, size_t workspace_capacity,
                                 cudaStream_t stream);
+int launch_dense_mla_attention(const smla_dense_params_t &p, cudaStream_t stream);
 
 int read_and_clear_device_status(int *status_out);
 int device_status_address(int **addr_out);

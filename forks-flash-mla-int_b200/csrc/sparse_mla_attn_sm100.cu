@@ -61,6 +61,11 @@ constexpr int kD = 512;
 // Third value of the kernels' FMT parameter: int8_ds_mla rows that are 16-byte aligned inside 32-byte
 // aligned blocks (the usual 528-byte tokens), gathered with 256-bit loads (see load_row_pieces).
 constexpr int kFmtInt8Wide = 2;
+// Fourth value: dense paged MLA (bf16 rows of 576 dims found through a block table; scores over all 576
+// dims, values = the first 512).  The 64 RoPE dims of a tile sit in a fifth K chunk that shares its
+// shared memory with P^T: they are only read by QK^T, P^T is only written after QK^T has completed.
+constexpr int kFmtBf16Dense = 3;
+constexpr int kDenseRowBytes = 1152;             // 576 bf16
 constexpr int kTileRows = 128;
 constexpr int kWorkerWarps = 16;                 // gather/dequant + softmax + epilogue
 constexpr int kWorkerThreads = kWorkerWarps * 32;
@@ -140,15 +145,25 @@ struct KernelArgs {
     int T, H, head_blocks, balanced;
     float scale_log2;
     int q_tma;            // the Q tile is fetched with one TMA tensor copy through q_map (else cp.async)
-    CUtensorMap q_map;    // 5-D view of q: {8 dims, 8 heads, 64 dim groups, H/8 head groups, T}
+    CUtensorMap q_map;    // 5-D view of q: {8 dims, 8 heads, 64 (dense: 72) dim groups, H/8 head groups, T}
+    // dense paged MLA only (dense_sq > 0): token t is query position t % dense_sq of sequence t / dense_sq;
+    // swa.indices is the block table, swa.lens the sequences' lengths; with `causal` query position i sees
+    // the first len - (dense_sq - 1 - i) rows.  lse[(b * H + h) * dense_sq + i], natural log, may be null.
+    float *lse;
+    int dense_sq, causal;
 };
 
-template <int NPAD>
+template <int NPAD, bool DENSE = false>
 struct Smem {
-    static constexpr int kQ = 0;                         // Q tile, core(hg, dg) at hg*8192 + dg*128
-    static constexpr int kK = kQ + NPAD * 1024;          // K tile, core(rg, dg) at rg*8192 + dg*128
-    static constexpr int kP = kK + kKBytes;              // P^T,   core(hg, rg) at hg*2048 + rg*128
-    static constexpr int kRed = kP + NPAD * 256;         // [4][NPAD] floats
+    static constexpr int kQDimGroups = DENSE ? 72 : 64;  // 16-byte pieces of a Q row
+    static constexpr int kQRowGroup = kQDimGroups * kCoreBytes;   // 8 heads of Q
+    static constexpr int kQBytes = (NPAD / 8) * kQRowGroup;
+    static constexpr int kQ = 0;                         // Q tile, core(hg, dg) at hg*kQRowGroup + dg*128
+    static constexpr int kK = kQ + kQBytes;              // K tile, core(rg, dg) at rg*8192 + dg*128
+    static constexpr int kP = kK + kKBytes;              // P^T,   core(hg, rg) at hg*2048 + rg*128; dense: also
+                                                         // the tile's RoPE dims, core(rg, dg) at rg*1024 + dg*128
+    static constexpr int kPBytes = DENSE ? 16384 : NPAD * 256;
+    static constexpr int kRed = kP + kPBytes;            // [4][NPAD] floats
     static constexpr int kM = kRed + 4 * NPAD * 4;       // running reference max per head
     static constexpr int kAlpha = kM + NPAD * 4;         // rescale factor / final 1/l per head
     static constexpr int kShift = kAlpha + NPAD * 4;     // m_old - m_new of the last reference move
@@ -160,12 +175,18 @@ struct Smem {
     // Epilogue staging, 8 KB per column-slice group.  With 64 heads only 16 KB are left, so groups 0
     // and 1 stage in the P buffer (idle between a segment's last PV and the next softmax).
     static constexpr int kStage = kSched + 640;
-    static constexpr int kStageBytes = (NPAD == 64) ? 16384 : 32768;
+    static constexpr int kStageBytes = DENSE ? 0 : (NPAD == 64) ? 16384 : 32768;   // dense: output stored from registers
     static constexpr int kTotal = kStage + kStageBytes;
     static_assert(kTotal <= 232448, "more than 227 KB of shared memory");
 };
 
 // ------------------------------------------------------------------ small device helpers
+constexpr float kLn2 = 0.6931471805599453f;
+// Where the log-sum-exp of (token t, head h) goes (dense paged MLA: [sequence, head, query position]).
+__device__ __forceinline__ float *lse_ptr(const KernelArgs &a, int t, int h) {
+    const int b = t / a.dense_sq, i = t - b * a.dense_sq;
+    return a.lse + (static_cast<long long>(b) * a.H + h) * a.dense_sq + i;
+}
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t *>(&v);
@@ -315,6 +336,15 @@ struct RowRef {
     int vec;   // see StreamDev::vec
 };
 
+// Dense paged MLA: row g of a sequence is position g % block_size of the page its block table names.
+__device__ __forceinline__ int load_dense_slot_id(const KernelArgs &a, int t, int n, int g) {
+    if (g >= n) return -1;
+    const int b = a.dense_sq == 1 ? t : t / a.dense_sq;
+    const int page_i = a.swa.block_shift >= 0 ? (g >> a.swa.block_shift) : g / a.swa.block_size;
+    const int page = __ldg(a.swa.indices + static_cast<long long>(b) * a.swa.idx_stride + page_i);
+    return page < 0 ? -1 : page * a.swa.block_size + (g - page_i * a.swa.block_size);
+}
+
 __device__ __forceinline__ int load_slot_id(const KernelArgs &a, int t, int ns, int n, int g) {
     if (g < ns) return __ldg(a.swa.indices + static_cast<long long>(t) * a.swa.idx_stride + g);
     if (g < n) return __ldg(a.extra.indices + static_cast<long long>(t) * a.extra.idx_stride + (g - ns));
@@ -339,7 +369,9 @@ __device__ __forceinline__ RowRef<FMT> make_row_ref(const KernelArgs &a, int ns,
     const uint8_t *blk = s.cache + static_cast<long long>(b) * s.block_stride;
     r.ok = true;
     r.vec = s.vec;
-    if constexpr (FMT == SMLA_FP8_DS_MLA) {
+    if constexpr (FMT == kFmtBf16Dense) {
+        r.ptr = blk + static_cast<long long>(i) * s.pos_stride;
+    } else if constexpr (FMT == SMLA_FP8_DS_MLA) {
         r.ptr = blk + static_cast<long long>(i) * 576;
         const uint2 sc = ldg_nc_v2(blk + static_cast<long long>(s.block_size) * 576 + static_cast<long long>(i) * 8);
         r.sc0 = sc.x;
@@ -361,7 +393,7 @@ __device__ __forceinline__ RowRef<FMT> make_row_ref(const KernelArgs &a, int ns,
 // instructions per lane and tile instead of 9 (int8 rows: see kFmtInt8Wide).  The count matters more than the bytes: while the tensor pipe
 // streams operands, every load instruction takes ~20 cycles of issue (measured: twice as many loads
 // for the same bytes cost 18 % of the kernel).
-template <int FMT> struct Steps { static constexpr int kCount = (FMT == SMLA_INT8_DS_MLA) ? 8 : 9; };
+template <int FMT> struct Steps { static constexpr int kCount = (FMT == kFmtBf16Dense) ? 1 : (FMT == SMLA_INT8_DS_MLA) ? 8 : 9; };
 
 // The order is fixed per cache format at compile time (a run-time choice cost the int8 kernel 10 %):
 // fp8 rows use the wide order (their 576-byte pitch keeps them 32-byte aligned whenever the cache is;
@@ -378,7 +410,13 @@ template <int FMT>
 __device__ __forceinline__ void load_row_pieces(const RowRef<FMT> &r, int quarter, uint4 (&raw)[Steps<FMT>::kCount]) {
     constexpr int J = Steps<FMT>::kCount;
     // Invalid rows are zero rows; the choice is made per load (a select, no divergent branch).
-    if constexpr (FMT == kFmtInt8Wide) {
+    if constexpr (FMT == kFmtBf16Dense) {
+        // bf16 rows go to the K buffer with cp.async when the buffer is free (no registers could hold
+        // 288 bytes per thread a tile ahead); a tile ahead they are only pulled into L2.
+        raw[0] = make_uint4(0u, 0u, 0u, 0u);
+        if (r.ok && quarter == 0)      // one bulk prefetch per row (1152 bytes)
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(r.ptr), "r"(kDenseRowBytes) : "memory");
+    } else if constexpr (FMT == kFmtInt8Wide) {
         // 512 data bytes from a 16-byte aligned address: an even row is 16 aligned 32-byte windows; an
         // odd row is fetched from 16 bytes earlier (the tail of the token before it, readable), so
         // that its windows are aligned too: raw[2c] is then piece 8c + 2q - 1 and raw[2c + 1] piece
@@ -481,6 +519,11 @@ struct Seg {
 };
 
 __device__ __forceinline__ void token_rows(const KernelArgs &a, int t, int &ns, int &n) {
+    if (a.dense_sq > 0) {     // dense paged MLA: all rows of the sequence, minus what the causal mask hides
+        const int b = t / a.dense_sq, i = t - b * a.dense_sq;
+        ns = n = max(__ldg(a.swa.lens + b) - (a.causal ? a.dense_sq - 1 - i : 0), 0);
+        return;
+    }
     ns = min(max(__ldg(a.swa.lens + t), 0), a.swa.topk);
     const int ne = (a.extra.cache != nullptr) ? min(max(__ldg(a.extra.lens + t), 0), a.extra.topk) : 0;
     n = ns + ne;
@@ -708,6 +751,8 @@ __device__ __forceinline__ void load_iter(const int *p, SegIter &it, long long &
 // An item without rows: its output is zero (the reference's "no selected slot" case).
 __device__ __forceinline__ void zero_item(const KernelArgs &a, const Seg &s, int tid, int nthreads) {
     const int h0 = s.hb * 64, hv = min(64, a.H - h0);
+    if (a.lse != nullptr)
+        for (int h = tid; h < hv; h += nthreads) *lse_ptr(a, s.t, h0 + h) = -INFINITY;
     for (int i = tid; i < hv * (kD / 8); i += nthreads) {
         const int h = i / (kD / 8), d8 = i - h * (kD / 8);
         *reinterpret_cast<uint4 *>(a.out + static_cast<long long>(s.t) * a.o_ts + static_cast<long long>(h0 + h) * a.o_hs +
@@ -731,7 +776,7 @@ __device__ __forceinline__ void publish_segment(const KernelArgs &a, int *sched,
         }
         zero_item(a, s, lane, 32);
     }
-    if (ok && lane < 5) {
+    if (ok && lane < 5 && a.dense_sq == 0) {
         // Warm L2 (and the TLB) with the slot ids of the segment's first tile: nobody has touched that
         // token's index row yet, and the workers need the ids in the last tile of the segment before,
         // to issue the gather.  Records are published three segments ahead, so the lines have arrived by then.
@@ -827,9 +872,9 @@ __device__ __forceinline__ bool wait_published(const int *sched, int k, volatile
 // tensor pipe alone (M128 x N64 x K16 with both operands fetched from shared memory).  In this kernel the
 // one-lane form issued one MMA per ~75 cycles, so every PV chunk released its part of the K buffer late
 // and the conversion of the next tile, which follows those releases, was paced by MMA issue.
-template <int NPAD>
+template <int NPAD, bool DENSE>
 __device__ __forceinline__ void mma_role(uint8_t *smem, uint32_t tmem_base) {
-    using L = Smem<NPAD>;
+    using L = Smem<NPAD, DENSE>;
     // Segment k is read from record k % 5 of the ring.  Warp 0 wrote it three segments earlier, before
     // conversions this thread has since waited for, and overwrites it only during segment k + 2.
     const volatile int *ring = reinterpret_cast<const volatile int *>(smem + L::kSched) + kSchedRec;
@@ -844,7 +889,8 @@ __device__ __forceinline__ void mma_role(uint8_t *smem, uint32_t tmem_base) {
     // (128 B), K step = next row group (8192 B); MN-major B = P^T: N step = next head group (2048 B),
     // K step = next row group (128 B).  Only the 14-bit start-address field changes between MMAs.
     const uint64_t qa = umma_desc(smem_u32(smem + L::kK), kCoreBytes, kRowGroupBytes);
-    const uint64_t qb = umma_desc(smem_u32(smem + L::kQ), kCoreBytes, kRowGroupBytes);
+    const uint64_t qb = umma_desc(smem_u32(smem + L::kQ), kCoreBytes, L::kQRowGroup);
+    const uint64_t ra = umma_desc(smem_u32(smem + L::kP), kCoreBytes, 1024);      // dense: the tile's 64 RoPE dims
     const uint64_t pa = umma_desc(smem_u32(smem + L::kK), kRowGroupBytes, kCoreBytes);
     const uint64_t pb = umma_desc(smem_u32(smem + L::kP), kCoreBytes, 2048);
 
@@ -870,6 +916,16 @@ __device__ __forceinline__ void mma_role(uint8_t *smem, uint32_t tmem_base) {
                 for (int k = 0; k < 8; ++k) {
                     const uint64_t off = static_cast<uint64_t>(((16 * c + 2 * k) * kCoreBytes) >> 4);
                     umma_bf16_ss_pred(tmem_base, qa + off, qb + off, idesc_qk, (c | k) != 0 ? 1u : 0u, go);
+                }
+                if constexpr (DENSE) {
+                    if (c == 3) {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const uint64_t aoff = static_cast<uint64_t>((2 * k * kCoreBytes) >> 4);
+                            const uint64_t boff = static_cast<uint64_t>(((64 + 2 * k) * kCoreBytes) >> 4);
+                            umma_bf16_ss_pred(tmem_base, ra + aoff, qb + boff, idesc_qk, 1u, go);
+                        }
+                    }
                 }
             }
             umma_commit_pred(bars + kBarS * 8, go);
@@ -906,17 +962,18 @@ __device__ __forceinline__ void mma_role(uint8_t *smem, uint32_t tmem_base) {
 // Q tile of one item -> shared memory (K-major core matrices), with cp.async so that no registers are
 // held and all pieces are in flight at once; heads beyond the item's last one are zero-filled.
 // The caller later runs cp_async_wait_all() + fence_async_smem() before the tensor pipe may read it.
-template <int NPAD>
+template <int NPAD, bool DENSE>
 __device__ __forceinline__ void issue_q_tile(const KernelArgs &a, uint8_t *smem, int t, int h0, int hvalid, int warp,
                                              int lane, int nwarps) {
-    using L = Smem<NPAD>;
+    using L = Smem<NPAD, DENSE>;
     const __nv_bfloat16 *qt = a.q + static_cast<long long>(t) * a.q_ts + static_cast<long long>(h0) * a.q_hs;
     const uint32_t q_addr = smem_u32(smem + L::kQ);
-    for (int idx = warp; idx < (NPAD / 8) * 16; idx += nwarps) {
-        const int hg = idx >> 4, dg = (idx & 15) * 4 + (lane >> 3), h = hg * 8 + (lane & 7);
+    constexpr int kQuads = L::kQDimGroups / 4;      // groups of four 16-byte pieces per head row
+    for (int idx = warp; idx < (NPAD / 8) * kQuads; idx += nwarps) {
+        const int hg = idx / kQuads, dg = (idx - hg * kQuads) * 4 + (lane >> 3), h = hg * 8 + (lane & 7);
         const bool ok = h < hvalid;
         const __nv_bfloat16 *src = qt + static_cast<long long>(ok ? h : 0) * a.q_hs + dg * 8;
-        cp_async_16_zfill(q_addr + hg * kRowGroupBytes + dg * kCoreBytes + (lane & 7) * 16, src, ok ? 16u : 0u);
+        cp_async_16_zfill(q_addr + hg * L::kQRowGroup + dg * kCoreBytes + (lane & 7) * 16, src, ok ? 16u : 0u);
     }
 }
 
@@ -934,7 +991,7 @@ __device__ __forceinline__ float initial_ref(const KernelArgs &a, bool complete,
 // past L1 (another SM wrote them).
 template <typename SlotOf>
 __device__ __forceinline__ void merge_head(const float *part_o, const float *part_ml, SlotOf slot_of, int S, int npad,
-                                           int hl, float sink_l2, __nv_bfloat16 *dst, int lane) {
+                                           int hl, float sink_l2, __nv_bfloat16 *dst, int lane, float *lse_dst = nullptr) {
     auto ml_of = [&](int k) {
         return __ldcg(reinterpret_cast<const float2 *>(part_ml) + static_cast<long long>(slot_of(k)) * npad + hl);
     };
@@ -987,6 +1044,7 @@ __device__ __forceinline__ void merge_head(const float *part_o, const float *par
         }
     }
     const float inv = denom > 0.0f ? 1.0f / denom : 0.0f;
+    if (lse_dst != nullptr && lane == 0) *lse_dst = denom > 0.0f ? (M + log2f(denom)) * kLn2 : -INFINITY;
 #pragma unroll
     for (int v = 0; v < 4; ++v) {
         const uint2 pk = make_uint2(pack_bf16x2(acc[4 * v] * inv, acc[4 * v + 1] * inv),
@@ -1001,9 +1059,9 @@ __device__ __forceinline__ void merge_head(const float *part_o, const float *par
 // waits, time-bounded, for the flags of all segments of each item it took part in and merges ITS SHARE
 // of the item's heads (CTA j of S: heads [j*H/S, (j+1)*H/S)), so the merge is spread over as many SMs
 // as the item was.  Every CTA has raised all its flags before it waits for anybody's: no cycles.
-template <int NPAD>
+template <int NPAD, bool DENSE>
 __device__ __forceinline__ void merge_head_slices(const KernelArgs &a, uint8_t *smem, int tid, int warp, int lane) {
-    using L = Smem<NPAD>;
+    using L = Smem<NPAD, DENSE>;
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::kAbort);
     const volatile int *fin = reinterpret_cast<const volatile int *>(smem + L::kSched) + kSchedFin;
 #pragma unroll 1
@@ -1039,7 +1097,8 @@ __device__ __forceinline__ void merge_head_slices(const KernelArgs &a, uint8_t *
         for (int hl = hbeg + warp; hl < hend; hl += kWorkerWarps) {
             const float sink_l2 = a.sink ? a.sink[h0 + hl] * kLog2e : -INFINITY;
             merge_head(a.part_o, a.part_ml, slot_of, S, NPAD, hl, sink_l2,
-                       a.out + static_cast<long long>(t) * a.o_ts + static_cast<long long>(h0 + hl) * a.o_hs, lane);
+                       a.out + static_cast<long long>(t) * a.o_ts + static_cast<long long>(h0 + hl) * a.o_hs, lane,
+                       a.lse != nullptr ? lse_ptr(a, t, h0 + hl) : nullptr);
         }
     }
 }
@@ -1050,9 +1109,9 @@ __device__ __forceinline__ void merge_head_slices(const KernelArgs &a, uint8_t *
 // the segments in the ring, wait for every tile's S^T barrier so that they know when the last QK^T of
 // a segment has completed (the Q buffer is then free), fetch the next item's Q tile with cp.async
 // and hand it to the MMA thread through the Q barrier.
-template <int NPAD>
+template <int NPAD, bool DENSE>
 __device__ __forceinline__ void qload_role(const KernelArgs &a, uint8_t *smem, int qwarp, int lane) {
-    using L = Smem<NPAD>;
+    using L = Smem<NPAD, DENSE>;
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::kAbort);
     const uint32_t bars = smem_u32(smem + L::kBars);
     const volatile int *ring = reinterpret_cast<const volatile int *>(smem + L::kSched) + kSchedRec;
@@ -1067,11 +1126,11 @@ __device__ __forceinline__ void qload_role(const KernelArgs &a, uint8_t *smem, i
             // [head % 8][8 dims], which is the K-major core-matrix layout of the Q operand; head groups
             // beyond H are zero-filled.  The innermost coordinate is 0 (TMA needs it 16-byte aligned).
             if (qwarp == 0 && lane == 0) {
-                mbar_arrive_expect_tx(bars + kBarQ * 8, NPAD * 1024);
+                mbar_arrive_expect_tx(bars + kBarQ * 8, L::kQBytes);
                 tma_load_5d(smem_u32(smem + L::kQ), &a.q_map, bars + kBarQ * 8, 0, 0, 0, h0 / 8, rec[0]);
             }
         } else {
-            issue_q_tile<NPAD>(a, smem, rec[0], h0, min(NPAD, a.H - h0), qwarp, lane, kQLoadWarps);
+            issue_q_tile<NPAD, DENSE>(a, smem, rec[0], h0, min(NPAD, a.H - h0), qwarp, lane, kQLoadWarps);
             cp_async_wait_all();
             fence_async_smem();
             __syncwarp();
@@ -1086,9 +1145,9 @@ __device__ __forceinline__ void qload_role(const KernelArgs &a, uint8_t *smem, i
 // Publishes the segment records.  Records 1..4 at once, then record s + 3 when the first tile of
 // segment s has been scored: the ring slot it overwrites belonged to segment s - 2, whose last reader
 // (its epilogue, run in the first tile of segment s - 1) has finished by then.
-template <int NPAD>
+template <int NPAD, bool DENSE>
 __device__ __forceinline__ void scheduler_role(const KernelArgs &a, uint8_t *smem, int lane) {
-    using L = Smem<NPAD>;
+    using L = Smem<NPAD, DENSE>;
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::kAbort);
     const uint32_t bars = smem_u32(smem + L::kBars);
     int *sched = reinterpret_cast<int *>(smem + L::kSched);
@@ -1112,7 +1171,7 @@ __device__ __forceinline__ void scheduler_role(const KernelArgs &a, uint8_t *sme
 // The raw bytes of the next tile are always in flight, across segment boundaries too.
 template <int FMT, int NPAD>
 __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, uint32_t tmem_base, int warp, int lane) {
-    using L = Smem<NPAD>;
+    using L = Smem<NPAD, FMT == kFmtBf16Dense>;
     constexpr int J = Steps<FMT>::kCount;
     constexpr int CW = NPAD / 4;   // head columns per warp in the softmax job
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::kAbort);
@@ -1206,10 +1265,12 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
                     wk_s[k * NPAD + tid] = w;
                 }
                 const float inv = 1.0f / denom;
+                if (a.lse != nullptr && tid < hvalid) *lse_ptr(a, t, h0 + tid) = (M + log2f(denom)) * kLn2;
                 alpha_s[tid] = w_own * inv;
                 for (int k = 0; k < others; ++k) wk_s[k * NPAD + tid] *= inv;
             } else if (direct) {
                 if (a.sink != nullptr && tid < hvalid) l += fast_exp2(a.sink[h0 + tid] * kLog2e - m_s[tid]);
+                if (a.lse != nullptr && tid < hvalid) *lse_ptr(a, t, h0 + tid) = (m_s[tid] + log2f(l)) * kLn2;
                 alpha_s[tid] = 1.0f / l;
             } else if (tid < hvalid) {
                 float *ml = a.part_ml + (static_cast<long long>(slot) * NPAD + tid) * 2;
@@ -1224,61 +1285,91 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
         }
         named_bar_sync(kAllWorkersBar, kWorkerThreads);
         if (direct) {
-            const uint32_t stage = (NPAD == 64 && cs < 2) ? smem_u32(smem + L::kP) + cs * 8192
-                                                          : smem_u32(smem + L::kStage) + (NPAD == 64 ? cs - 2 : cs) * 8192;
-            const int gtid = q * 32 + lane;     // thread of the group; also the dim inside a 128-dim chunk
-            __nv_bfloat16 *orow = a.out + static_cast<long long>(t) * a.o_ts + static_cast<long long>(h0 + col0) * a.o_hs;
-#pragma unroll 1
-            for (int r = 0; r < CW / HR; ++r) {
-                // Owner: the first other segment's rows of this round are fetched for all four chunks at
-                // once (this is the CTA's last epilogue: the gather registers are free), so that their
-                // latency is paid once per round and not once per chunk.
-                float pv[kFinal ? 4 : 1][HR];
-                if constexpr (kFinal) {
-                    if (owner) {
-                        const float *src = a.part_o + (static_cast<long long>(2 * (blockIdx.x + 1)) * NPAD + col0 + r * HR) * kD + gtid;
-#pragma unroll
-                        for (int c = 0; c < 4; ++c)
-#pragma unroll
-                            for (int j = 0; j < HR; ++j) pv[c][j] = __ldcg(src + c * 128 + j * kD);
+            if constexpr (FMT == kFmtBf16Dense) {
+                // Dense paged MLA has no staging area (its longer Q rows take the room): a thread holds one dim
+                // of HR heads and stores it as it is; the 32 lanes of a warp hold 32 consecutive dims, so each
+                // 2-byte store instruction writes one 64-byte segment of a head's output row.
+                __nv_bfloat16 *orow = a.out + static_cast<long long>(t) * a.o_ts + static_cast<long long>(h0 + col0) * a.o_hs + row;
+    #pragma unroll 1
+                for (int r = 0; r < CW / HR; ++r) {
+    #pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t o[HR];
+                        TmemIO<HR>::ld(tmem_lane + kTmemOCol + c * NPAD + col0 + r * HR, o);
+                        float val[HR];
+    #pragma unroll
+                        for (int j = 0; j < HR; ++j) val[j] = __uint_as_float(o[j]) * alpha_s[col0 + r * HR + j];
+                        if constexpr (kFinal) {
+                            for (int k = 0; k < others; ++k) {      // un-normalised rows of the item's other segments
+                                const float *src = a.part_o + (static_cast<long long>(2 * (blockIdx.x + 1 + k)) * NPAD + col0 + r * HR) * kD +
+                                                   c * 128 + row;
+    #pragma unroll
+                                for (int j = 0; j < HR; ++j) val[j] = fmaf(wk_s[k * NPAD + col0 + r * HR + j], __ldcg(src + j * kD), val[j]);
+                            }
+                        }
+    #pragma unroll
+                        for (int j = 0; j < HR; ++j)
+                            if (col0 + r * HR + j < hvalid)
+                                orow[static_cast<long long>(r * HR + j) * a.o_hs + c * 128] = __float2bfloat16_rn(val[j]);
                     }
                 }
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t o[HR];
-                    TmemIO<HR>::ld(tmem_lane + kTmemOCol + c * NPAD + col0 + r * HR, o);
-                    const uint32_t dst = stage + (c * 128 + gtid) * 2;
-                    float val[HR];
-#pragma unroll
-                    for (int j = 0; j < HR; ++j) val[j] = __uint_as_float(o[j]) * alpha_s[col0 + r * HR + j];
+        } else {
+                const uint32_t stage = (NPAD == 64 && cs < 2) ? smem_u32(smem + L::kP) + cs * 8192
+                                                              : smem_u32(smem + L::kStage) + (NPAD == 64 ? cs - 2 : cs) * 8192;
+                const int gtid = q * 32 + lane;     // thread of the group; also the dim inside a 128-dim chunk
+                __nv_bfloat16 *orow = a.out + static_cast<long long>(t) * a.o_ts + static_cast<long long>(h0 + col0) * a.o_hs;
+    #pragma unroll 1
+                for (int r = 0; r < CW / HR; ++r) {
+                    // Owner: the first other segment's rows of this round are fetched for all four chunks at
+                    // once (this is the CTA's last epilogue: the gather registers are free), so that their
+                    // latency is paid once per round and not once per chunk.
+                    float pv[kFinal ? 4 : 1][HR];
                     if constexpr (kFinal) {
                         if (owner) {
-#pragma unroll
-                            for (int j = 0; j < HR; ++j) val[j] = fmaf(wk_s[col0 + r * HR + j], pv[c][j], val[j]);
-                        }
-                        for (int k = 1; k < others; ++k) {      // un-normalised rows of the item's further segments
-                            const float *src = a.part_o + (static_cast<long long>(2 * (blockIdx.x + 1 + k)) * NPAD + col0 + r * HR) * kD +
-                                               c * 128 + gtid;
-#pragma unroll
-                            for (int j = 0; j < HR; ++j) val[j] = fmaf(wk_s[k * NPAD + col0 + r * HR + j], __ldcg(src + j * kD), val[j]);
+                            const float *src = a.part_o + (static_cast<long long>(2 * (blockIdx.x + 1)) * NPAD + col0 + r * HR) * kD + gtid;
+    #pragma unroll
+                            for (int c = 0; c < 4; ++c)
+    #pragma unroll
+                                for (int j = 0; j < HR; ++j) pv[c][j] = __ldcg(src + c * 128 + j * kD);
                         }
                     }
-#pragma unroll
-                    for (int j = 0; j < HR; ++j) {
-                        const __nv_bfloat16 v = __float2bfloat16_rn(val[j]);
-                        asm volatile("st.shared.u16 [%0], %1;" ::"r"(dst + j * 1024), "h"(*reinterpret_cast<const uint16_t *>(&v)) : "memory");
+    #pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t o[HR];
+                        TmemIO<HR>::ld(tmem_lane + kTmemOCol + c * NPAD + col0 + r * HR, o);
+                        const uint32_t dst = stage + (c * 128 + gtid) * 2;
+                        float val[HR];
+    #pragma unroll
+                        for (int j = 0; j < HR; ++j) val[j] = __uint_as_float(o[j]) * alpha_s[col0 + r * HR + j];
+                        if constexpr (kFinal) {
+                            if (owner) {
+    #pragma unroll
+                                for (int j = 0; j < HR; ++j) val[j] = fmaf(wk_s[col0 + r * HR + j], pv[c][j], val[j]);
+                            }
+                            for (int k = 1; k < others; ++k) {      // un-normalised rows of the item's further segments
+                                const float *src = a.part_o + (static_cast<long long>(2 * (blockIdx.x + 1 + k)) * NPAD + col0 + r * HR) * kD +
+                                                   c * 128 + gtid;
+    #pragma unroll
+                                for (int j = 0; j < HR; ++j) val[j] = fmaf(wk_s[k * NPAD + col0 + r * HR + j], __ldcg(src + j * kD), val[j]);
+                            }
+                        }
+    #pragma unroll
+                        for (int j = 0; j < HR; ++j) {
+                            const __nv_bfloat16 v = __float2bfloat16_rn(val[j]);
+                            asm volatile("st.shared.u16 [%0], %1;" ::"r"(dst + j * 1024), "h"(*reinterpret_cast<const uint16_t *>(&v)) : "memory");
+                        }
                     }
+                    named_bar_sync(group_bar, 128);
+    #pragma unroll
+                    for (int i = 0; i < HR / 2; ++i) {
+                        const int h = 2 * i + (gtid >> 6), piece = gtid & 63;
+                        uint4 v;
+                        asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(stage + h * 1024 + piece * 16));
+                        if (col0 + r * HR + h < hvalid)
+                            *reinterpret_cast<uint4 *>(orow + static_cast<long long>(r * HR + h) * a.o_hs + piece * 8) = v;
+                    }
+                    named_bar_sync(group_bar, 128);     // the stage may be rewritten
                 }
-                named_bar_sync(group_bar, 128);
-#pragma unroll
-                for (int i = 0; i < HR / 2; ++i) {
-                    const int h = 2 * i + (gtid >> 6), piece = gtid & 63;
-                    uint4 v;
-                    asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(stage + h * 1024 + piece * 16));
-                    if (col0 + r * HR + h < hvalid)
-                        *reinterpret_cast<uint4 *>(orow + static_cast<long long>(r * HR + h) * a.o_hs + piece * 8) = v;
-                }
-                named_bar_sync(group_bar, 128);     // the stage may be rewritten
             }
         } else {
 #pragma unroll 1
@@ -1314,7 +1405,8 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
     {   // raw bytes of the very first tile (segment 0 was published before the roles split)
         const int *r0 = sched + kSchedRec;
         g = r0[4] * kTileRows + my_row;
-        cur = make_row_ref<FMT>(a, r0[3], r0[2], g, load_slot_id(a, r0[0], r0[3], r0[2], g));
+        cur = make_row_ref<FMT>(a, r0[3], r0[2], g, FMT == kFmtBf16Dense ? load_dense_slot_id(a, r0[0], r0[2], g)
+                                                                          : load_slot_id(a, r0[0], r0[3], r0[2], g));
         load_row_pieces<FMT>(cur, quarter, raw);
     }
 
@@ -1342,8 +1434,44 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
             const bool more = in_seg || have_next;
             const int n_t = in_seg ? sg[0] : ng[0], n_ns = in_seg ? sg[3] : ng[3], n_n = in_seg ? sg[2] : ng[2];
             const int g_next = in_seg ? g + kTileRows : ng[4] * kTileRows + my_row;
-            const int id_next = more ? load_slot_id(a, n_t, n_ns, n_n, g_next) : -1;
+            const int id_next = !more ? -1 : FMT == kFmtBf16Dense ? load_dense_slot_id(a, n_t, n_n, g_next)
+                                                                  : load_slot_id(a, n_t, n_ns, n_n, g_next);
 
+            if constexpr (FMT == kFmtBf16Dense) {
+                // ---- bf16 rows: cp.async straight into the K chunks as the previous tile's PV releases them
+                // (this thread: four 16-byte pieces of its row per chunk), the RoPE dims with chunk 3 into the buffer
+                // they share with P^T, which PV has finished reading by then; handed over as they land.
+                const uint8_t *src = cur.ok ? cur.ptr : a.swa.cache;
+                const uint32_t nbytes = cur.ok ? 16u : 0u;        // rows outside the sequence are zero-filled
+                const uint32_t rope_row_addr = smem_u32(smem + L::kP) + warp * 1024 + (lane & 7) * 16;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    if (gt > 0) warp_wait(bars + (kBarFree + c) * 8, (gt - 1) & 1, abort_flag, lane, kStatusGatherWait);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int dg = 16 * c + 4 * i + quarter;      // the four lanes of a row: 64 contiguous bytes
+                        cp_async_16_zfill(k_row_addr + dg * kCoreBytes, src + dg * 16, nbytes);
+                    }
+                    if (c == 3) {
+#pragma unroll
+                        for (int i = 0; i < 2; ++i) {
+                            const int dg = 4 * i + quarter;
+                            cp_async_16_zfill(rope_row_addr + dg * kCoreBytes, src + 1024 + dg * 16, nbytes);
+                        }
+                    }
+                    cp_async_commit();
+                }
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    if (c == 0) cp_async_wait_group<3>();
+                    else if (c == 1) cp_async_wait_group<2>();
+                    else if (c == 2) cp_async_wait_group<1>();
+                    else cp_async_wait_group<0>();
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bars + (kBarReady + c) * 8);
+                }
+            } else {
             // ---- convert: raw registers -> K chunks, each as soon as the previous tile's PV released it
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
@@ -1369,6 +1497,7 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bars + (kBarReady + c) * 8);
             }
+            }
             // Raw bytes of the next tile.  Issued only now, after this tile's last conversion fence: a
             // proxy fence also waits for the thread's global loads in flight, so loads issued between
             // the chunks would put a memory latency on every hand-over.  They land while QK^T runs.
@@ -1376,6 +1505,16 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
             // issue of a load blocks the warp while the SM's load queue is full.)
             cur = make_row_ref<FMT>(a, n_ns, n_n, more ? g_next : n_n, id_next);
             if (more) load_row_pieces<FMT>(cur, quarter, raw);
+            if constexpr (FMT == kFmtBf16Dense) {
+                // Dense rows come from HBM once (no reuse between query tokens as in the sparse workloads):
+                // measured, a row asked for one tile ahead arrives 7-8k cycles after its cp.async was issued,
+                // so the tile after next is pulled into L2 as well (two tiles of all SMs are 43 MB).
+                if (left > 2) {
+                    const int g2 = g_next + kTileRows;
+                    const RowRef<FMT> ahead = make_row_ref<FMT>(a, sg[3], sg[2], g2, load_dense_slot_id(a, sg[0], sg[2], g2));
+                    load_row_pieces<FMT>(ahead, quarter, raw);
+                }
+            }
             g = g_next;
 
             // ---- the previous segment's epilogue, while the tensor pipe computes this tile's QK^T
@@ -1490,14 +1629,14 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
             break;
         }
     }
-    if (a.fused_merge == 2) merge_head_slices<NPAD>(a, smem, tid, warp, lane);
+    if (a.fused_merge == 2) merge_head_slices<NPAD, FMT == kFmtBf16Dense>(a, smem, tid, warp, lane);
 }
 
 // ------------------------------------------------------------------ the kernel
 template <int FMT, int NPAD>
 __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const __grid_constant__ KernelArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
-    using L = Smem<NPAD>;
+    using L = Smem<NPAD, FMT == kFmtBf16Dense>;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
     // ---- this CTA's share of the work
@@ -1562,15 +1701,15 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const __gri
     if (warp < kWorkerWarps) {
         worker_role<FMT, NPAD>(a, smem, tmem_base, warp, lane);
     } else if (warp == kMmaWarp) {
-        mma_role<NPAD>(smem, tmem_base);
+        mma_role<NPAD, FMT == kFmtBf16Dense>(smem, tmem_base);
     } else if (a.q_tma) {
         // one tensor copy per item needs one thread; the next warp publishes the schedule
-        if (warp == kMmaWarp + 1) qload_role<NPAD>(a, smem, 0, lane);
-        if (warp == kMmaWarp + 2) scheduler_role<NPAD>(a, smem, lane);
+        if (warp == kMmaWarp + 1) qload_role<NPAD, FMT == kFmtBf16Dense>(a, smem, 0, lane);
+        if (warp == kMmaWarp + 2) scheduler_role<NPAD, FMT == kFmtBf16Dense>(a, smem, lane);
     } else {
         // cp.async fallback for Q: two loader warps, one scheduler warp
-        if (warp == kMmaWarp + 2) scheduler_role<NPAD>(a, smem, lane);
-        else qload_role<NPAD>(a, smem, warp == kMmaWarp + 1 ? 0 : 1, lane);
+        if (warp == kMmaWarp + 2) scheduler_role<NPAD, FMT == kFmtBf16Dense>(a, smem, lane);
+        else qload_role<NPAD, FMT == kFmtBf16Dense>(a, smem, warp == kMmaWarp + 1 ? 0 : 1, lane);
     }
 
     __syncthreads();
@@ -1589,7 +1728,8 @@ __global__ void __launch_bounds__(128) sparse_mla_combine_kernel(const float *__
                                                                  const int4 *__restrict__ desc,
                                                                  const float *__restrict__ sink,
                                                                  __nv_bfloat16 *__restrict__ out, long long o_ts,
-                                                                 long long o_hs, int head_blocks, int npad) {
+                                                                 long long o_hs, int head_blocks, int npad,
+                                                                 float *__restrict__ lse, int num_heads, int dense_sq) {
     const int lane = threadIdx.x & 31;
     const int c = blockIdx.x;
     const int4 d = desc[c];
@@ -1597,8 +1737,13 @@ __global__ void __launch_bounds__(128) sparse_mla_combine_kernel(const float *__
     if (d.x < 0 || hl >= d.w) return;
     const int t = d.x / head_blocks, h = (d.x - t * head_blocks) * 64 + hl;
     auto slot_of = [&](int k) { return k == 0 ? d.z : 2 * (c + k); };
+    float *lse_dst = nullptr;
+    if (lse != nullptr) {
+        const int b = t / dense_sq, i = t - b * dense_sq;
+        lse_dst = lse + (static_cast<long long>(b) * num_heads + h) * dense_sq + i;
+    }
     merge_head(part_o, part_ml, slot_of, d.y, npad, hl, sink ? sink[h] * kLog2e : -INFINITY,
-               out + static_cast<long long>(t) * o_ts + static_cast<long long>(h) * o_hs, lane);
+               out + static_cast<long long>(t) * o_ts + static_cast<long long>(h) * o_hs, lane, lse_dst);
 }
 
 // ------------------------------------------------------------------ host side
@@ -1638,7 +1783,7 @@ int fill_stream(const smla_stream_t &s, int fmt, StreamDev &d) {
 
 template <int FMT, int NPAD>
 int launch_fwd(const KernelArgs &a, unsigned grid, cudaStream_t stream) {
-    constexpr int smem_bytes = Smem<NPAD>::kTotal;
+    constexpr int smem_bytes = Smem<NPAD, FMT == kFmtBf16Dense>::kTotal;
     // The opt-in to 227 KB of dynamic shared memory is per device and per kernel instance; hosts that
     // run one thread per GPU come through here concurrently, hence atomics (setting it twice is harmless).
     static std::atomic<bool> attr_done[64];
@@ -1683,14 +1828,14 @@ EncodeTiledFn tensor_map_encoder() {
 
 // 5-D view of q [T, H, 512] whose box {8, 8, 64, npad/8, 1} is the Q operand's shared-memory layout.
 // False (the kernel then uses cp.async) when H is not a multiple of 8 or the driver refuses the map.
-bool make_q_tensor_map(const KernelArgs &a, int npad, CUtensorMap *map) {
+bool make_q_tensor_map(const KernelArgs &a, int npad, int dim_groups, CUtensorMap *map) {
     if (a.H % 8 != 0) return false;
     EncodeTiledFn enc = tensor_map_encoder();
     if (enc == nullptr) return false;
-    const cuuint64_t dims[5] = {8, 8, 64, static_cast<cuuint64_t>(a.H / 8), static_cast<cuuint64_t>(a.T)};
+    const cuuint64_t dims[5] = {8, 8, static_cast<cuuint64_t>(dim_groups), static_cast<cuuint64_t>(a.H / 8), static_cast<cuuint64_t>(a.T)};
     const cuuint64_t strides[4] = {static_cast<cuuint64_t>(a.q_hs) * 2, 16, static_cast<cuuint64_t>(a.q_hs) * 16,
                                    static_cast<cuuint64_t>(a.q_ts) * 2};
-    const cuuint32_t box[5] = {8, 8, 64, static_cast<cuuint32_t>(npad / 8), 1};
+    const cuuint32_t box[5] = {8, 8, static_cast<cuuint32_t>(dim_groups), static_cast<cuuint32_t>(npad / 8), 1};
     const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
     const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<__nv_bfloat16 *>(a.q), dims, strides, box,
                            estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
@@ -1719,6 +1864,63 @@ int sm_count_of_current_device(int &count) {
     if (e != cudaSuccess) return static_cast<int>(e);
     if (tracked) cached[dev].store(count, std::memory_order_relaxed);
     return 0;
+}
+
+}  // namespace
+
+namespace {
+// The part every attention entry point shares: pick the schedule (balanced tiles with as many CTAs as the
+// SM count and the workspace allow, else whole items), the merge form, the Q tensor map, and launch.
+int schedule_and_launch(KernelArgs &a, int fmt, int num_splits, void *workspace, size_t workspace_capacity,
+                        cudaStream_t stream) {
+    const int npad = head_pad(a.H);
+    a.head_blocks = (a.H + 63) / 64;
+    const long long items = static_cast<long long>(a.T) * a.head_blocks;
+    if (items > 0x7FFFFFFFLL) return SMLA_ETOOBIG;
+    int sms = 0;
+    int rc = sm_count_of_current_device(sms);
+    if (rc != 0) return rc;
+
+    long long ctas = 0;
+    if (num_splits > 1) {
+        if (!workspace) return SMLA_EWORKSPACE;
+        if (reinterpret_cast<uintptr_t>(workspace) & 15u) return SMLA_EALIGN;
+        const size_t want = smla_attn_workspace_bytes(a.T, a.H, num_splits);
+        ctas = balanced_ctas(sms, npad, static_cast<long long>(std::min(want, workspace_capacity)));
+    }
+    if (ctas >= 2) {
+        a.balanced = 1;
+        a.part_o = static_cast<float *>(workspace);
+        a.part_ml = a.part_o + static_cast<size_t>(2 * ctas) * npad * kD;
+        a.desc = reinterpret_cast<int *>(a.part_ml + static_cast<size_t>(2 * ctas) * npad * 2);      // 16 B per CTA
+        a.flags = reinterpret_cast<unsigned long long *>(a.desc + 4 * ctas);                         // 16 B per CTA
+        a.fused_merge = merge_mode_policy(items, ctas);
+        if (a.fused_merge == 2) {
+            // The slice merge relies on the tag being new for every execution; a graph replays the same
+            // arguments, so a capturing stream gets the combine kernel instead.
+            cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+            if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) a.fused_merge = 0;
+        }
+        a.tag = next_launch_tag();
+    } else {
+        a.balanced = 0;
+        ctas = std::min<long long>(items, sms);
+    }
+    a.q_tma = make_q_tensor_map(a, npad, fmt == kFmtBf16Dense ? 72 : 64, &a.q_map) ? 1 : 0;
+    const unsigned grid = static_cast<unsigned>(ctas);
+    const bool int8_wide = fmt == SMLA_INT8_DS_MLA && a.swa.vec == 2 && (a.extra.cache == nullptr || a.extra.vec == 2);
+    rc = (fmt == kFmtBf16Dense)      ? launch_fwd_npad<kFmtBf16Dense>(npad, a, grid, stream)
+         : (fmt == SMLA_FP8_DS_MLA) ? launch_fwd_npad<SMLA_FP8_DS_MLA>(npad, a, grid, stream)
+         : int8_wide                ? launch_fwd_npad<kFmtInt8Wide>(npad, a, grid, stream)
+                                    : launch_fwd_npad<SMLA_INT8_DS_MLA>(npad, a, grid, stream);
+    if (rc != 0) return rc;
+    if (a.balanced && !a.fused_merge) {
+        sparse_mla_combine_kernel<<<dim3(grid, static_cast<unsigned>((npad + 3) / 4)), 128, 0, stream>>>(
+            a.part_o, a.part_ml, reinterpret_cast<const int4 *>(a.desc), a.sink, a.out, a.o_ts, a.o_hs, a.head_blocks,
+            npad, a.lse, a.H, a.dense_sq);
+        rc = static_cast<int>(cudaGetLastError());
+    }
+    return rc;
 }
 
 }  // namespace
@@ -1752,54 +1954,51 @@ int launch_sparse_mla_attention(const smla_attn_params_t &p, int num_splits, voi
         rc = fill_stream(p.extra, p.cache_format, a.extra);
         if (rc != SMLA_OK) return rc;
     }
-    const int npad = head_pad(p.num_heads);
-    a.head_blocks = (p.num_heads + 63) / 64;
-    const long long items = static_cast<long long>(p.num_tokens) * a.head_blocks;
-    if (items > 0x7FFFFFFFLL) return SMLA_ETOOBIG;
-    int sms = 0;
-    rc = sm_count_of_current_device(sms);
-    if (rc != 0) return rc;
+    return schedule_and_launch(a, p.cache_format, num_splits, workspace, workspace_capacity, stream);
+}
 
-    long long ctas = 0;
-    if (num_splits > 1) {
-        if (!workspace) return SMLA_EWORKSPACE;
-        if (reinterpret_cast<uintptr_t>(workspace) & 15u) return SMLA_EALIGN;
-        const size_t want = smla_attn_workspace_bytes(p.num_tokens, p.num_heads, num_splits);
-        ctas = balanced_ctas(sms, npad, static_cast<long long>(std::min(want, workspace_capacity)));
-    }
-    if (ctas >= 2) {
-        a.balanced = 1;
-        a.part_o = static_cast<float *>(workspace);
-        a.part_ml = a.part_o + static_cast<size_t>(2 * ctas) * npad * kD;
-        a.desc = reinterpret_cast<int *>(a.part_ml + static_cast<size_t>(2 * ctas) * npad * 2);      // 16 B per CTA
-        a.flags = reinterpret_cast<unsigned long long *>(a.desc + 4 * ctas);                         // 16 B per CTA
-        a.fused_merge = merge_mode_policy(items, ctas);
-        if (a.fused_merge == 2) {
-            // The slice merge relies on the tag being new for every execution; a graph replays the same
-            // arguments, so a capturing stream gets the combine kernel instead.
-            cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-            if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) a.fused_merge = 0;
-        }
-        a.tag = next_launch_tag();
-    } else {
-        a.balanced = 0;
-        ctas = std::min<long long>(items, sms);
-    }
-    a.q_tma = make_q_tensor_map(a, npad, &a.q_map) ? 1 : 0;
-    const unsigned grid = static_cast<unsigned>(ctas);
-    const bool int8_wide = p.cache_format == SMLA_INT8_DS_MLA && a.swa.vec == 2 &&
-                           (p.extra.cache == nullptr || a.extra.vec == 2);
-    rc = (p.cache_format == SMLA_FP8_DS_MLA) ? launch_fwd_npad<SMLA_FP8_DS_MLA>(npad, a, grid, stream)
-         : int8_wide                         ? launch_fwd_npad<kFmtInt8Wide>(npad, a, grid, stream)
-                                             : launch_fwd_npad<SMLA_INT8_DS_MLA>(npad, a, grid, stream);
-    if (rc != 0) return rc;
-    if (a.balanced && !a.fused_merge) {
-        sparse_mla_combine_kernel<<<dim3(grid, static_cast<unsigned>((npad + 3) / 4)), 128, 0, stream>>>(
-            a.part_o, a.part_ml, reinterpret_cast<const int4 *>(a.desc), a.sink, a.out, a.o_ts, a.o_hs, a.head_blocks,
-            npad);
-        rc = static_cast<int>(cudaGetLastError());
-    }
-    return rc;
+// Dense paged MLA decode: every query position of every sequence is an item list entry ("token"), its rows
+// are the sequence's first n rows found through the block table; the same persistent kernel, schedules
+// and merges as the sparse path, with bf16 rows copied (not converted) into the K buffer.
+int launch_dense_mla_attention(const smla_dense_params_t &p, cudaStream_t stream) {
+    if (p.batch <= 0 || p.seqlen_q <= 0 || p.num_heads <= 0 || !p.q || !p.out || !p.k_cache || !p.block_table ||
+        !p.cache_seqlens || p.page_block_size <= 0 || p.num_blocks < 0)
+        return SMLA_EINVAL;
+    const long long tokens = static_cast<long long>(p.batch) * p.seqlen_q;
+    if (tokens > 0x7FFFFFFFLL) return SMLA_ETOOBIG;
+    if ((reinterpret_cast<uintptr_t>(p.q) & 15u) || (p.q_token_stride & 7) || (p.q_head_stride & 7) ||
+        (reinterpret_cast<uintptr_t>(p.out) & 15u) || (p.out_token_stride & 7) || (p.out_head_stride & 7) ||
+        (reinterpret_cast<uintptr_t>(p.k_cache) & 15u) || (p.k_block_stride & 15) || (p.k_row_stride & 15) ||
+        p.k_row_stride < kDenseRowBytes)
+        return SMLA_EALIGN;
+    KernelArgs a = {};
+    a.q = static_cast<const __nv_bfloat16 *>(p.q);
+    a.q_ts = p.q_token_stride;
+    a.q_hs = p.q_head_stride;
+    a.out = static_cast<__nv_bfloat16 *>(p.out);
+    a.o_ts = p.out_token_stride;
+    a.o_hs = p.out_head_stride;
+    a.sink = nullptr;
+    a.T = static_cast<int>(tokens);
+    a.H = p.num_heads;
+    a.scale_log2 = p.softmax_scale * kLog2e;
+    a.lse = p.softmax_lse;
+    a.dense_sq = p.seqlen_q;
+    a.causal = (p.causal && p.seqlen_q > 1) ? 1 : 0;
+    a.swa.cache = static_cast<const uint8_t *>(p.k_cache);
+    a.swa.indices = p.block_table;
+    a.swa.lens = p.cache_seqlens;
+    a.swa.idx_stride = p.block_table_stride;
+    a.swa.block_stride = p.k_block_stride;
+    a.swa.pos_stride = p.k_row_stride;
+    a.swa.topk = 0x7FFFFFFF;
+    const long long slots = static_cast<long long>(p.num_blocks) * p.page_block_size;
+    if (slots > 0x7FFFFFFFLL) return SMLA_ETOOBIG;
+    a.swa.num_slots = static_cast<int>(slots);
+    a.swa.block_size = p.page_block_size;
+    a.swa.block_shift = (p.page_block_size & (p.page_block_size - 1)) ? -1 : __builtin_ctz(static_cast<unsigned>(p.page_block_size));
+    a.swa.vec = 1;
+    return schedule_and_launch(a, kFmtBf16Dense, p.num_splits, p.workspace, p.workspace_bytes, stream);
 }
 
 int read_and_clear_device_status(int *status_out) {

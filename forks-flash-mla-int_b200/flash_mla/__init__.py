@@ -1,9 +1,10 @@
-"""flash_mla for B200 (sm_100a): the sparse-MLA path of AppMana/forks-flash-mla-int.
+"""flash_mla for B200 (sm_100a): the sparse-MLA path of AppMana/forks-flash-mla-int and its dense sibling.
 
 Same names and argument contract as the reference package (flash_mla/__init__.py:3-15) for
-the sparse ops and the int8 row quantizer; ``write_fp8_ds_mla_cache`` / ``write_int8_ds_mla_cache``
-(encode new rows and scatter them into a paged cache) are additions the reference does not have.  The dense-MLA entry points and the Triton decoder
-(``get_mla_metadata``, ``flash_mla_with_kvcache``, ``flash_mla_with_kvcache_int8``,
+the sparse ops, the int8 row quantizer and dense bf16 paged MLA decode (``get_mla_metadata``,
+``flash_mla_with_kvcache``); ``write_fp8_ds_mla_cache`` / ``write_int8_ds_mla_cache``
+(encode new rows and scatter them into a paged cache) are additions the reference does not have.  The
+int8 dense decoder and the Triton decoder (``flash_mla_with_kvcache_int8``,
 ``sparse_mla_decode_int8_triton``) are not part of this library.
 
 Importing the package loads the compiled extension; there is no CPU or eager fallback -- a
@@ -12,6 +13,8 @@ missing library raises ImportError.
 __version__ = "2.0.0+b200"
 
 from .flash_mla_interface import (  # noqa: F401
+    flash_mla_with_kvcache,
+    get_mla_metadata,
     sparse_mla_decode_fp8,
     sparse_mla_prefill,
 )
@@ -33,6 +36,8 @@ from .int8_sparse_mla import (  # noqa: F401
 )
 
 __all__ = [
+    "get_mla_metadata",
+    "flash_mla_with_kvcache",
     "sparse_mla_decode_fp8",
     "sparse_mla_prefill",
     "sparse_mla_decode_int8",

@@ -18,7 +18,7 @@ SMLA_ETOOBIG = -5
 
 EXPORTS = (
     "smla_version", "smla_error_string", "smla_choose_num_splits", "smla_attn_workspace_bytes",
-    "smla_decode_plan", "smla_decode_kernel_launches", "smla_decode_kernel_launches_captured", "smla_sparse_mla_decode", "smla_sparse_mla_decode_static_scratch", "smla_sparse_mla_prefill",
+    "smla_decode_plan", "smla_decode_kernel_launches", "smla_decode_kernel_launches_captured", "smla_sparse_mla_decode", "smla_sparse_mla_decode_static_scratch", "smla_sparse_mla_prefill", "smla_dense_mla_decode",
     "smla_quantize_int8_ds_mla_rows", "smla_write_int8_ds_mla_cache", "smla_write_fp8_ds_mla_cache",
     "smla_read_device_status", "smla_device_status_address",
 )
@@ -62,6 +62,34 @@ class SmlaAttnParams(C.Structure):
     ]
 
 
+class SmlaDenseParams(C.Structure):
+    _fields_ = [
+        ("batch", C.c_int32),
+        ("seqlen_q", C.c_int32),
+        ("num_heads", C.c_int32),
+        ("causal", C.c_int32),
+        ("softmax_scale", C.c_float),
+        ("q", C.c_void_p),
+        ("q_token_stride", C.c_int64),
+        ("q_head_stride", C.c_int64),
+        ("out", C.c_void_p),
+        ("out_token_stride", C.c_int64),
+        ("out_head_stride", C.c_int64),
+        ("softmax_lse", C.c_void_p),
+        ("k_cache", C.c_void_p),
+        ("k_block_stride", C.c_int64),
+        ("k_row_stride", C.c_int64),
+        ("num_blocks", C.c_int32),
+        ("page_block_size", C.c_int32),
+        ("block_table", C.c_void_p),
+        ("block_table_stride", C.c_int64),
+        ("cache_seqlens", C.c_void_p),
+        ("num_splits", C.c_int32),
+        ("workspace", C.c_void_p),
+        ("workspace_bytes", C.c_size_t),
+    ]
+
+
 _lib = None
 
 
@@ -86,6 +114,7 @@ def load() -> C.CDLL:
     lib.smla_decode_kernel_launches_captured.restype = C.c_int
     lib.smla_sparse_mla_decode.argtypes = [C.POINTER(SmlaAttnParams), C.c_void_p]
     lib.smla_sparse_mla_prefill.argtypes = [C.POINTER(SmlaAttnParams), C.c_void_p]
+    lib.smla_dense_mla_decode.argtypes = [C.POINTER(SmlaDenseParams), C.c_void_p]
     lib.smla_sparse_mla_decode_static_scratch.argtypes = [C.POINTER(SmlaAttnParams), C.c_void_p]
     lib.smla_quantize_int8_ds_mla_rows.argtypes = [C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_void_p,
                                                    C.c_void_p, C.c_void_p]
@@ -139,6 +168,29 @@ def attn_params(q, out, fmt: int, softmax_scale: float, swa: SmlaStream, extra: 
     p.swa = swa
     if extra is not None:
         p.extra = extra
+    p.num_splits = num_splits
+    if workspace is not None:
+        p.workspace = workspace.data_ptr()
+        p.workspace_bytes = workspace.numel() * workspace.element_size()
+    return p
+
+
+def dense_params(q, k_cache, block_table, cache_seqlens, out, lse=None, softmax_scale=None, causal=False,
+                 num_splits: int = 0, workspace=None) -> SmlaDenseParams:
+    """q [b, s_q, h, 576] contiguous bf16; k_cache [num_blocks, page, 1, 576] bf16; out [b, s_q, h, 512];
+    lse fp32 [b, h, s_q] or None."""
+    p = SmlaDenseParams()
+    p.batch, p.seqlen_q, p.num_heads = q.shape[0], q.shape[1], q.shape[2]
+    p.causal = 1 if causal else 0
+    p.softmax_scale = softmax_scale if softmax_scale is not None else q.shape[-1] ** -0.5
+    p.q, p.q_token_stride, p.q_head_stride = q.data_ptr(), q.stride(1), q.stride(2)
+    p.out, p.out_token_stride, p.out_head_stride = out.data_ptr(), out.stride(1), out.stride(2)
+    p.softmax_lse = lse.data_ptr() if lse is not None else None
+    p.k_cache = k_cache.data_ptr()
+    p.k_block_stride, p.k_row_stride = k_cache.stride(0) * 2, k_cache.stride(1) * 2
+    p.num_blocks, p.page_block_size = k_cache.shape[0], k_cache.shape[1]
+    p.block_table, p.block_table_stride = block_table.data_ptr(), block_table.stride(0)
+    p.cache_seqlens = cache_seqlens.data_ptr()
     p.num_splits = num_splits
     if workspace is not None:
         p.workspace = workspace.data_ptr()

@@ -164,6 +164,33 @@ SMLA_API int smla_sparse_mla_decode_static_scratch(const smla_attn_params_t *par
  * (csrc/flash_mla.h:159-160, csrc/flash_sparse_mla_prefill_fused_sm80.cu:468-506). */
 SMLA_API int smla_sparse_mla_prefill(const smla_attn_params_t *params, void *stream);
 
+/* Dense paged MLA decode: every query attends to ALL rows of its sequence's paged bf16 KV cache (one kv
+ * head; scores over 576 dims, values = the first 512).  Replaces the path behind flash_mla_with_kvcache:
+ * mha_fwd_kvcache_mla (csrc/flash_api.cpp:159-322), Flash_fwd_mla_params (csrc/flash_mla.h:5-49) and
+ * run_mha_fwd_splitkv_mla.  Query tokens are (sequence, query position) pairs flattened in that order.
+ * No scheduler metadata is needed: the persistent kernel cuts the work itself (get_mla_metadata of the
+ * reference has no counterpart here; the binding returns placeholders of the reference's shapes). */
+typedef struct smla_dense_params {
+    int32_t batch, seqlen_q, num_heads;   /* q [batch, seqlen_q, num_heads, 576] bf16                            */
+    int32_t causal;                       /* query position i sees the first len - (seqlen_q - 1 - i) rows       */
+    float softmax_scale;
+    const void *q;                        /* 16-byte aligned                                                     */
+    int64_t q_token_stride, q_head_stride;       /* elements; token = batch index * seqlen_q + query position   */
+    void *out;                            /* [batch, seqlen_q, num_heads, 512] bf16                              */
+    int64_t out_token_stride, out_head_stride;   /* elements                                                    */
+    float *softmax_lse;                   /* [batch, num_heads, seqlen_q] fp32, natural log; may be NULL         */
+    const void *k_cache;                  /* [num_blocks, page_block_size, 1, 576] bf16, 16-byte aligned         */
+    int64_t k_block_stride, k_row_stride; /* bytes, multiples of 16, k_row_stride >= 1152                        */
+    int32_t num_blocks, page_block_size;
+    const int32_t *block_table;           /* [batch, max_blocks_per_seq] page numbers (negative: zero rows)      */
+    int64_t block_table_stride;           /* elements                                                            */
+    const int32_t *cache_seqlens;         /* [batch] rows of each sequence                                       */
+    int32_t num_splits;                   /* as smla_attn_params_t: 0 = choose, 1 = whole items, > 1 with workspace */
+    void *workspace;                      /* smla_attn_workspace_bytes(batch * seqlen_q, num_heads, num_splits)  */
+    size_t workspace_bytes;
+} smla_dense_params_t;
+SMLA_API int smla_dense_mla_decode(const smla_dense_params_t *params, void *stream);
+
 /* int8_ds_mla row quantizer, bit-exact with quantize_int8_ds_mla_rows
  * (flash_mla/int8_sparse_mla.py:15-26): scale = max(amax|x|, 1e-12) / 127 and
  * q = clamp(rint(x / scale), -127, 127) in IEEE fp32.

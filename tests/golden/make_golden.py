@@ -12,6 +12,9 @@ thing the tests read.  Imported from the reference (nothing is copied):
                                 tests/test_sparse_mla_prefill_int8_adversarial.py:44-74
 * ``quantize_int8_ds_mla_rows`` flash_mla/int8_sparse_mla.py:15-26 (loaded by file path,
                                 the package __init__ needs the compiled extension)
+* ``scaled_dot_product_attention`` tests/test_flash_mla_sm80.py:10-27 (that file imports the compiled
+                                package at its top; an empty stand-in module named ``flash_mla`` lets the
+                                import go through, the oracle function itself needs nothing from it)
 
     python tests/golden/make_golden.py
 """
@@ -42,6 +45,15 @@ _spec = importlib.util.spec_from_file_location(
 _mod = importlib.util.module_from_spec(_spec)
 _spec.loader.exec_module(_mod)
 ref_quantize = _mod.quantize_int8_ds_mla_rows
+
+
+import types  # noqa: E402
+
+if "flash_mla" not in sys.modules:
+    _stub = types.ModuleType("flash_mla")
+    _stub.get_mla_metadata = _stub.flash_mla_with_kvcache = None
+    sys.modules["flash_mla"] = _stub
+from test_flash_mla_sm80 import scaled_dot_product_attention as ref_dense_sdpa  # noqa: E402
 
 
 def bits(x: torch.Tensor) -> np.ndarray:
@@ -162,6 +174,38 @@ def config1_cpu_oracle():
          lens=lens.numpy(), out=out.numpy())
 
 
+def dense_mla_small():
+    """The dense test's oracle (tests/test_flash_mla_sm80.py:75-93) on a small ragged batch: three sequences,
+    two query positions, 16 heads, pages of 32 rows, rows past each length poisoned with NaN as there."""
+    torch.manual_seed(11)
+    b, s_q, h_q, h_kv, d, dv, block_size = 3, 2, 16, 1, 576, 512, 32
+    cache_seqlens = torch.tensor([70, 300, 129], dtype=torch.int32)
+    max_seqlen_pad = 512
+    q = torch.randn(b, s_q, h_q, d).to(torch.bfloat16)
+    # pages in a scrambled order so that the block table matters
+    perm = torch.randperm(b * max_seqlen_pad // block_size)
+    block_table = perm.to(torch.int32).view(b, max_seqlen_pad // block_size)
+    blocked_k = torch.zeros(perm.numel(), block_size, h_kv, d, dtype=torch.bfloat16)
+    seq_rows = torch.randn(b, max_seqlen_pad, h_kv, d).to(torch.bfloat16)
+    for i in range(b):
+        seq_rows[i, cache_seqlens[i].item():] = float("nan")
+        blocked_k[block_table[i].long()] = seq_rows[i].view(-1, block_size, h_kv, d)
+    res = {}
+    for causal in (False, True):
+        out = torch.empty(b, s_q, h_q, dv, dtype=torch.float32)
+        lse = torch.empty(b, h_q, s_q, dtype=torch.float32)
+        for i in range(b):
+            n = cache_seqlens[i].item()
+            O, LSE = ref_dense_sdpa(q[i].transpose(0, 1), seq_rows[i, :n].transpose(0, 1),
+                                    seq_rows[i, :n, :, :dv].transpose(0, 1), h_q=h_q, h_kv=h_kv, is_causal=causal)
+            out[i] = O.transpose(0, 1)
+            lse[i] = LSE
+        res["out_causal" if causal else "out"] = out.numpy()
+        res["lse_causal" if causal else "lse"] = lse.numpy()
+    save("dense_mla_small.npz", q_bf16=bits(q), k_cache_bf16=bits(blocked_k), block_table=block_table.numpy(),
+         cache_seqlens=cache_seqlens.numpy(), **res)
+
+
 if __name__ == "__main__":
     torch.set_num_threads(8)
     quantizer_kat()
@@ -169,3 +213,4 @@ if __name__ == "__main__":
     fp8_two_stream()
     int8_two_stream()
     config1_cpu_oracle()
+    dense_mla_small()

@@ -1,0 +1,139 @@
+"""GPU parity tests of dense paged MLA decode (``flash_mla_with_kvcache``): the sm_100a kernel through the
+reference-shaped Python API and through the C ABI, against the golden fixture made with the reference's own
+oracle and against the CPU oracle on seeded inputs.  The cases mirror the reference's dense test,
+tests/test_flash_mla_sm80.py:43-121 (batch, query positions, heads, ragged lengths, causal mask, NaN in
+every row past a sequence's length), and use its gate: ``cos_diff < 8e-5`` for the output and for the lse.
+"""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import bf16_from_bits, device_status
+import oracle
+from bench_workloads import dense_decode_workload
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def fm():
+    import flash_mla
+    return flash_mla
+
+
+@pytest.fixture(autouse=True)
+def _status_clean():
+    yield
+    assert device_status() == 0, "a kernel wait ran out (device status word set)"
+
+
+def check(out, lse, ref_out, ref_lse, what, sequences=None):
+    out = out.float().cpu().numpy()
+    lse = lse.float().cpu().numpy()
+    if sequences is not None:
+        out, lse, ref_out, ref_lse = out[sequences], lse[sequences], ref_out[sequences], ref_lse[sequences]
+    assert np.isfinite(out).all(), f"{what}: non-finite output (a row past a sequence's length was read?)"
+    assert oracle.cos_diff(out, ref_out) < 8e-5, f"{what}: out cos_diff {oracle.cos_diff(out, ref_out):.3e}"
+    fin = np.isfinite(ref_lse)
+    assert (np.isfinite(lse) == fin).all(), f"{what}: lse finiteness differs"
+    assert oracle.cos_diff(lse[fin], ref_lse[fin]) < 8e-5, f"{what}: lse cos_diff"
+    # the reference's elementwise bound for the sparse ops holds here too (outputs are O(1))
+    assert np.abs(out - ref_out).max() <= 2e-2 + 2e-2 * np.abs(ref_out).max(), f"{what}: max abs {np.abs(out - ref_out).max():.3e}"
+    assert np.abs(lse[fin] - ref_lse[fin]).max() <= 2e-3 + 1e-3 * np.abs(ref_lse[fin]).max(), f"{what}: lse max abs"
+
+
+def run_api(fm, kw, causal):
+    meta, splits = fm.get_mla_metadata(kw["cache_seqlens"], kw["q"].shape[1] * kw["q"].shape[2], 1)
+    return fm.flash_mla_with_kvcache(kw["q"], kw["k_cache"], kw["block_table"], kw["cache_seqlens"], 512,
+                                     meta, splits, causal=causal)
+
+
+# ----------------------------------------------------------------------------- golden fixture
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("via", ["python", "c_abi"])
+def test_dense_golden(fm, golden, causal, via):
+    g = golden("dense_mla_small.npz")
+    q = bf16_from_bits(g["q_bf16"])
+    kc = bf16_from_bits(g["k_cache_bf16"])
+    bt = torch.from_numpy(g["block_table"]).cuda()
+    lens = torch.from_numpy(g["cache_seqlens"]).cuda()
+    if via == "python":
+        out, lse = run_api(fm, {"q": q, "k_cache": kc, "block_table": bt, "cache_seqlens": lens}, causal)
+    else:
+        from flash_mla import c_abi
+        lib = c_abi.load()
+        out = torch.empty(*q.shape[:3], 512, device="cuda", dtype=torch.bfloat16)
+        lse = torch.empty(q.shape[0], q.shape[2], q.shape[1], device="cuda", dtype=torch.float32)
+        p = c_abi.dense_params(q, kc, bt, lens, out, lse, causal=causal, num_splits=1)
+        c_abi.check(lib.smla_dense_mla_decode(ctypes.byref(p), torch.cuda.current_stream().cuda_stream))
+    check(out, lse, g["out_causal" if causal else "out"], g["lse_causal" if causal else "lse"], f"golden {via} causal={causal}")
+
+
+# ----------------------------------------------------------------------------- the reference test's sweep, reduced
+@pytest.mark.parametrize("h_q", [16, 32, 64, 128])
+@pytest.mark.parametrize("s_q", [1, 2])
+@pytest.mark.parametrize("varlen", [False, True])
+def test_dense_sweep(fm, h_q, s_q, varlen):
+    kw, _ = dense_decode_workload(b=6, s_q=s_q, mean_sk=1500, h_q=h_q, varlen=varlen, block_size=32, seed=h_q + s_q)
+    out, lse = run_api(fm, kw, causal=True)
+    ref_out, ref_lse = oracle.dense_mla_decode(kw["q"], kw["k_cache"], kw["block_table"], kw["cache_seqlens"], causal=True)
+    check(out, lse, ref_out, ref_lse, f"h_q={h_q} s_q={s_q} varlen={varlen}")
+
+
+@pytest.mark.parametrize("b,mean_sk,block_size", [(1, 8192, 64), (2, 4096, 64), (12, 3000, 64), (40, 700, 32), (700, 200, 64)])
+def test_dense_every_schedule_and_merge(fm, b, mean_sk, block_size):
+    """One sequence spread over the whole GPU (slice merge), a few (combine kernel), dozens (merge in the
+    epilogue of the CTA holding a sequence's first rows), many (whole items, nothing to merge)."""
+    kw, _ = dense_decode_workload(b=b, s_q=1, mean_sk=mean_sk, h_q=64, varlen=True, block_size=block_size, seed=b)
+    out, lse = run_api(fm, kw, causal=False)
+    seqs = list(range(min(b, 8))) + ([b - 1] if b > 8 else [])
+    ref_out, ref_lse = oracle.dense_mla_decode(kw["q"], kw["k_cache"], kw["block_table"], kw["cache_seqlens"], sequences=seqs)
+    check(out, lse, ref_out, ref_lse, f"b={b}", sequences=seqs)
+
+
+def test_dense_edges(fm):
+    """Lengths at the edges: exactly s_q rows (the shortest the reference generates), exact multiples of the
+    128-row tile and of the page, one row more, and 12 heads (not a multiple of 8: Q arrives by cp.async)."""
+    kw, _ = dense_decode_workload(b=6, s_q=2, mean_sk=512, h_q=12, varlen=False, block_size=64, seed=3)
+    kw["cache_seqlens"] = torch.tensor([2, 128, 129, 64, 512, 257], dtype=torch.int32, device="cuda")
+    # re-poison the rows past the new lengths
+    for i, n in enumerate(kw["cache_seqlens"].tolist()):
+        rows = kw["k_cache"][kw["block_table"][i].long()].view(-1, 1, 576)
+        rows[n:] = float("nan")
+        kw["k_cache"][kw["block_table"][i].long()] = rows.view(-1, 64, 1, 576)
+    for causal in (False, True):
+        out, lse = run_api(fm, kw, causal)
+        ref_out, ref_lse = oracle.dense_mla_decode(kw["q"], kw["k_cache"], kw["block_table"], kw["cache_seqlens"], causal=causal)
+        check(out, lse, ref_out, ref_lse, f"edges causal={causal}")
+
+
+def test_dense_full_size_sample(fm):
+    """The reference test's own size (b=128, s_k=4096, h_q=128, s_q=2, ragged, causal), checked on a sample
+    of the sequences."""
+    kw, _ = dense_decode_workload(b=128, s_q=2, mean_sk=4096, h_q=128, varlen=True, block_size=64, seed=1)
+    out, lse = run_api(fm, kw, causal=True)
+    lens = kw["cache_seqlens"].cpu()
+    seqs = sorted({0, 127, int(lens.argmax()), int(lens.argmin()), 17, 63})
+    ref_out, ref_lse = oracle.dense_mla_decode(kw["q"], kw["k_cache"], kw["block_table"], kw["cache_seqlens"], causal=True, sequences=seqs)
+    check(out, lse, ref_out, ref_lse, "b=128 s_k=4096 h_q=128 s_q=2", sequences=seqs)
+
+
+def test_dense_split_equals_whole_items(fm):
+    """The balanced schedule with in-kernel merges against whole items (num_splits = 1) through the C ABI."""
+    from flash_mla import c_abi
+    lib = c_abi.load()
+    kw, _ = dense_decode_workload(b=24, s_q=1, mean_sk=2500, h_q=64, varlen=True, block_size=64, seed=9)
+    q = kw["q"]
+    res = []
+    for splits in (1, 0):
+        out = torch.empty(*q.shape[:3], 512, device="cuda", dtype=torch.bfloat16)
+        lse = torch.empty(q.shape[0], q.shape[2], q.shape[1], device="cuda", dtype=torch.float32)
+        ws = torch.empty(64 << 20, dtype=torch.uint8, device="cuda")
+        p = c_abi.dense_params(q, kw["k_cache"], kw["block_table"], kw["cache_seqlens"], out, lse, num_splits=splits, workspace=ws)
+        c_abi.check(lib.smla_dense_mla_decode(ctypes.byref(p), torch.cuda.current_stream().cuda_stream))
+        torch.cuda.synchronize()
+        res.append((out.float(), lse))
+    assert (res[0][0] - res[1][0]).abs().max().item() <= 2 ** -7
+    assert (res[0][1] - res[1][1]).abs().max().item() <= 1e-3     # denominators sum bf16-rounded probabilities

@@ -31,7 +31,7 @@ def test_library_exports_every_declared_symbol():
 
 
 def test_struct_layout_matches_header():
-    """ctypes mirrors of the two structs: field order as in the header, natural alignment."""
+    """ctypes mirrors of the three structs: field order as in the header, natural alignment."""
     from flash_mla import c_abi
     text = open(os.path.join(ROOT, "include", "sparse_mla_b200.h")).read()
 
@@ -48,6 +48,7 @@ def test_struct_layout_matches_header():
         return names
     assert fields("smla_stream") == [f[0] for f in c_abi.SmlaStream._fields_]
     assert fields("smla_attn_params") == [f[0] for f in c_abi.SmlaAttnParams._fields_]
+    assert fields("smla_dense_params") == [f[0] for f in c_abi.SmlaDenseParams._fields_]
     assert ctypes.sizeof(c_abi.SmlaStream) == 88
     assert ctypes.sizeof(c_abi.SmlaAttnParams) == 272
 
@@ -58,7 +59,8 @@ def test_struct_layout_matches_c_compiler(tmp_path):
     from flash_mla import c_abi
     if shutil.which("gcc") is None:
         pytest.skip("no C compiler")
-    checks = [("smla_stream_t", c_abi.SmlaStream), ("smla_attn_params_t", c_abi.SmlaAttnParams)]
+    checks = [("smla_stream_t", c_abi.SmlaStream), ("smla_attn_params_t", c_abi.SmlaAttnParams),
+              ("smla_dense_params_t", c_abi.SmlaDenseParams)]
     lines = ['#include <stdio.h>', '#include <stddef.h>', '#include "sparse_mla_b200.h"', 'int main(void){']
     for cname, cls in checks:
         lines.append(f'printf("%zu\\n", sizeof({cname}));')

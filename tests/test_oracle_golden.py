@@ -173,3 +173,17 @@ def test_scatter_writers_match_packers():
             assert np.array_equal(flat[sl, :512].view(np.int8), qw[i]) and flat[sl, 512:516].view(np.float32)[0] == sw[i]
     untouched = np.setdiff1d(np.arange(64), slots[(slots >= 0) & (slots < 64)])
     assert (flat[untouched] == 0xA5).all()
+
+
+def test_dense_mla_oracle_matches_reference_oracle(golden):
+    """``oracle.dense_mla_decode`` against outputs of the reference's dense oracle
+    (tests/test_flash_mla_sm80.py:10-27 on the rows of each sequence), with and without the causal mask;
+    rows past a sequence's length are NaN in the fixture and must not reach the result."""
+    g = golden("dense_mla_small.npz")
+    from oracle import dense_mla_decode
+    q = bf16_bits_to_f32(g["q_bf16"])
+    kc = bf16_bits_to_f32(g["k_cache_bf16"])
+    for causal in (False, True):
+        out, lse = dense_mla_decode(q, kc, g["block_table"], g["cache_seqlens"], causal=causal)
+        np.testing.assert_allclose(out, g["out_causal" if causal else "out"], rtol=2e-5, atol=2e-6)
+        np.testing.assert_allclose(lse, g["lse_causal" if causal else "lse"], rtol=2e-5, atol=2e-6)
