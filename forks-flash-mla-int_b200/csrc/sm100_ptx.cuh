@@ -41,6 +41,13 @@ __device__ __forceinline__ void tma_load_5d(uint32_t dst, const void *tensor_map
         ::"r"(dst), "l"(tensor_map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(bar)
         : "memory");
 }
+// TMA tiled load of one 3-D box (no multicast).  c0 times the element size must be a multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const void *tensor_map, uint32_t bar, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(tensor_map), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+        : "memory");
+}
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(

@@ -14,6 +14,7 @@ enum DeviceStatusBits : int {
     kStatusMmaWait = 2,      // the MMA issuer gave up waiting for a filled K chunk
     kStatusSoftmaxWait = 4,  // a softmax warp gave up waiting for the score tile
     kStatusEpilogueWait = 8, // the epilogue gave up waiting for the last PV
+    kStatusSmemLayout = 16,  // the dynamic shared memory did not start on a 1024-byte boundary (nothing was computed)
 };
 
 int launch_quantize_int8_rows(const void *x, int x_dtype, int64_t rows, int64_t x_row_stride, int8_t *q,

@@ -65,6 +65,13 @@ constexpr int kFmtInt8Wide = 2;
 // dims, values = the first 512).  The 64 RoPE dims of a tile sit in a fifth K chunk that shares its
 // shared memory with P^T: they are only read by QK^T, P^T is only written after QK^T has completed.
 constexpr int kFmtBf16Dense = 3;
+// Fifth value: the same, with the K tile fetched by TMA (a warp of its own issues 2-D boxes of R rows x 64
+// dims, R = min(page, 128)) into eight slabs of [128 rows][128 bytes] with the 128-byte swizzle, which the
+// tensor pipe reads K-major for QK^T and MN-major for PV.  (cp.async moves 16 bytes per thread and about one
+// such request per cycle and SM: measured 8-9k cycles for the 147 KB of a tile.)
+constexpr int kFmtBf16DenseTma = 4;
+__host__ __device__ constexpr bool is_dense(int fmt) { return fmt == kFmtBf16Dense || fmt == kFmtBf16DenseTma; }
+constexpr int kSlabBytes = 128 * 128;            // 128 rows x 64 dims of bf16 (swizzled K tile)
 constexpr int kDenseRowBytes = 1152;             // 576 bf16
 constexpr int kTileRows = 128;
 constexpr int kWorkerWarps = 16;                 // gather/dequant + softmax + epilogue
@@ -113,7 +120,8 @@ constexpr int kBarP = 9;       //     P^T of this tile is in shared memory (16 a
 constexpr int kBarO = 10;      //     the last PV of a segment has completed
 constexpr int kBarOFree = 11;  //     the segment's epilogue has read O^T (16 arrivals)
 constexpr int kBarQ = 12;      //     the segment's Q tile is in shared memory (TMA: 1 arrival + bytes; else 2 warps)
-static_assert(kBarQ + 1 <= 14, "mbarrier slots reserved in Smem");
+constexpr int kBarLand = 13;   // [4] dense, K by TMA: the boxes of K chunk c have landed (1 arrival + bytes)
+static_assert(kBarLand + 4 <= 18, "mbarrier slots reserved in Smem");
 constexpr int kQLoadWarps = 2;                   // warps 17 and 19 (cp.async fallback; with TMA warp 17 alone)
 
 struct StreamDev {
@@ -151,6 +159,8 @@ struct KernelArgs {
     // the first len - (dense_sq - 1 - i) rows.  lse[(b * H + h) * dense_sq + i], natural log, may be null.
     float *lse;
     int dense_sq, causal;
+    CUtensorMap k_map;    // kFmtBf16DenseTma: 3-D view {576 dims, page rows, pages} of the cache, box {64, k_box_rows, 1}
+    int k_box_rows;
 };
 
 template <int NPAD, bool DENSE = false>
@@ -169,7 +179,7 @@ struct Smem {
     static constexpr int kShift = kAlpha + NPAD * 4;     // m_old - m_new of the last reference move
     static constexpr int kThr = kShift + NPAD * 4;       // how far a score may exceed m before m moves (move_threshold)
     static constexpr int kBars = kThr + NPAD * 4;        // kNumBars mbarriers
-    static constexpr int kTmemPtr = kBars + 14 * 8;
+    static constexpr int kTmemPtr = kBars + 18 * 8;
     static constexpr int kAbort = kTmemPtr + 4;
     static constexpr int kSched = kAbort + 4 + 8;        // 160 ints: work distribution (scan scratch, iterator, segment ring)
     // Epilogue staging, 8 KB per column-slice group.  With 64 heads only 16 KB are left, so groups 0
@@ -369,7 +379,7 @@ __device__ __forceinline__ RowRef<FMT> make_row_ref(const KernelArgs &a, int ns,
     const uint8_t *blk = s.cache + static_cast<long long>(b) * s.block_stride;
     r.ok = true;
     r.vec = s.vec;
-    if constexpr (FMT == kFmtBf16Dense) {
+    if constexpr (is_dense(FMT)) {
         r.ptr = blk + static_cast<long long>(i) * s.pos_stride;
     } else if constexpr (FMT == SMLA_FP8_DS_MLA) {
         r.ptr = blk + static_cast<long long>(i) * 576;
@@ -393,7 +403,7 @@ __device__ __forceinline__ RowRef<FMT> make_row_ref(const KernelArgs &a, int ns,
 // instructions per lane and tile instead of 9 (int8 rows: see kFmtInt8Wide).  The count matters more than the bytes: while the tensor pipe
 // streams operands, every load instruction takes ~20 cycles of issue (measured: twice as many loads
 // for the same bytes cost 18 % of the kernel).
-template <int FMT> struct Steps { static constexpr int kCount = (FMT == kFmtBf16Dense) ? 1 : (FMT == SMLA_INT8_DS_MLA) ? 8 : 9; };
+template <int FMT> struct Steps { static constexpr int kCount = is_dense(FMT) ? 1 : (FMT == SMLA_INT8_DS_MLA) ? 8 : 9; };
 
 // The order is fixed per cache format at compile time (a run-time choice cost the int8 kernel 10 %):
 // fp8 rows use the wide order (their 576-byte pitch keeps them 32-byte aligned whenever the cache is;
@@ -410,7 +420,7 @@ template <int FMT>
 __device__ __forceinline__ void load_row_pieces(const RowRef<FMT> &r, int quarter, uint4 (&raw)[Steps<FMT>::kCount]) {
     constexpr int J = Steps<FMT>::kCount;
     // Invalid rows are zero rows; the choice is made per load (a select, no divergent branch).
-    if constexpr (FMT == kFmtBf16Dense) {
+    if constexpr (is_dense(FMT)) {
         // bf16 rows go to the K buffer with cp.async when the buffer is free (no registers could hold
         // 288 bytes per thread a tile ahead); a tile ahead they are only pulled into L2.
         raw[0] = make_uint4(0u, 0u, 0u, 0u);
@@ -872,7 +882,7 @@ __device__ __forceinline__ bool wait_published(const int *sched, int k, volatile
 // tensor pipe alone (M128 x N64 x K16 with both operands fetched from shared memory).  In this kernel the
 // one-lane form issued one MMA per ~75 cycles, so every PV chunk released its part of the K buffer late
 // and the conversion of the next tile, which follows those releases, was paced by MMA issue.
-template <int NPAD, bool DENSE>
+template <int NPAD, bool DENSE, bool KTMA>
 __device__ __forceinline__ void mma_role(uint8_t *smem, uint32_t tmem_base) {
     using L = Smem<NPAD, DENSE>;
     // Segment k is read from record k % 5 of the ring.  Warp 0 wrote it three segments earlier, before
@@ -891,6 +901,13 @@ __device__ __forceinline__ void mma_role(uint8_t *smem, uint32_t tmem_base) {
     const uint64_t qa = umma_desc(smem_u32(smem + L::kK), kCoreBytes, kRowGroupBytes);
     const uint64_t qb = umma_desc(smem_u32(smem + L::kQ), kCoreBytes, L::kQRowGroup);
     const uint64_t ra = umma_desc(smem_u32(smem + L::kP), kCoreBytes, 1024);      // dense: the tile's 64 RoPE dims
+    // K by TMA: slabs of [128 rows][128 B] with the 128-byte swizzle (layout type 2).  QK^T reads a slab
+    // K-major (eight rows are 1024 B apart, a K step of 16 dims is 32 B inside the row); PV reads the two
+    // slabs of a chunk MN-major (the next 64 dims are one slab on, the next eight rows 1024 B, a K step of 16 rows 2048 B).
+    constexpr uint64_t kSw128 = 2ull << 61;
+    const uint64_t qa_sw = umma_desc(smem_u32(smem + L::kK), 16, 1024) | kSw128;
+    const uint64_t ra_sw = umma_desc(smem_u32(smem + L::kP), 16, 1024) | kSw128;
+    const uint64_t pa_sw = umma_desc(smem_u32(smem + L::kK), kSlabBytes, 1024) | kSw128;
     const uint64_t pa = umma_desc(smem_u32(smem + L::kK), kRowGroupBytes, kCoreBytes);
     const uint64_t pb = umma_desc(smem_u32(smem + L::kP), kCoreBytes, 2048);
 
@@ -905,9 +922,13 @@ __device__ __forceinline__ void mma_role(uint8_t *smem, uint32_t tmem_base) {
                 if (lane == 0) give_up(abort_flag, kStatusMmaWait);
                 return;
             }
+            // K by TMA: a full tile needs nothing from the workers, so its chunks are taken as they land; only a
+            // last, partial tile waits for the workers, who wipe the rows past the sequence first.  (The workers
+            // arrive on the ready barriers for every tile, so both sets of barriers stay in step with `gt`.)
+            const bool from_tma = KTMA && (rec[4] + it + 1) * kTileRows <= rec[2];
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                if (!mbar_wait(bars + (kBarReady + c) * 8, gt & 1, abort_flag)) {
+                if (!mbar_wait(bars + ((from_tma ? kBarLand : kBarReady) + c) * 8, gt & 1, abort_flag)) {
                     if (lane == 0) give_up(abort_flag, kStatusMmaWait);
                     return;
                 }
@@ -915,7 +936,12 @@ __device__ __forceinline__ void mma_role(uint8_t *smem, uint32_t tmem_base) {
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {
                     const uint64_t off = static_cast<uint64_t>(((16 * c + 2 * k) * kCoreBytes) >> 4);
-                    umma_bf16_ss_pred(tmem_base, qa + off, qb + off, idesc_qk, (c | k) != 0 ? 1u : 0u, go);
+                    if constexpr (KTMA) {
+                        const uint64_t aoff = static_cast<uint64_t>(((2 * c + (k >> 2)) * kSlabBytes + (k & 3) * 32) >> 4);
+                        umma_bf16_ss_pred(tmem_base, qa_sw + aoff, qb + off, idesc_qk, (c | k) != 0 ? 1u : 0u, go);
+                    } else {
+                        umma_bf16_ss_pred(tmem_base, qa + off, qb + off, idesc_qk, (c | k) != 0 ? 1u : 0u, go);
+                    }
                 }
                 if constexpr (DENSE) {
                     if (c == 3) {
@@ -923,7 +949,8 @@ __device__ __forceinline__ void mma_role(uint8_t *smem, uint32_t tmem_base) {
                         for (int k = 0; k < 4; ++k) {
                             const uint64_t aoff = static_cast<uint64_t>((2 * k * kCoreBytes) >> 4);
                             const uint64_t boff = static_cast<uint64_t>(((64 + 2 * k) * kCoreBytes) >> 4);
-                            umma_bf16_ss_pred(tmem_base, ra + aoff, qb + boff, idesc_qk, 1u, go);
+                            if constexpr (KTMA) umma_bf16_ss_pred(tmem_base, ra_sw + static_cast<uint64_t>((k * 32) >> 4), qb + boff, idesc_qk, 1u, go);
+                            else umma_bf16_ss_pred(tmem_base, ra + aoff, qb + boff, idesc_qk, 1u, go);
                         }
                     }
                 }
@@ -949,7 +976,12 @@ __device__ __forceinline__ void mma_role(uint8_t *smem, uint32_t tmem_base) {
                 for (int k = 0; k < 8; ++k) {
                     const uint64_t aoff = static_cast<uint64_t>((c * 16 * kCoreBytes + 2 * k * kRowGroupBytes) >> 4);
                     const uint64_t boff = static_cast<uint64_t>((2 * k * kCoreBytes) >> 4);
-                    umma_bf16_ss_pred(tmem_base + kTmemOCol + c * NPAD, pa + aoff, pb + boff, idesc_pv, k > 0 ? 1u : acc0, go);
+                    if constexpr (KTMA) {
+                        const uint64_t soff = static_cast<uint64_t>((2 * c * kSlabBytes + k * 2048) >> 4);
+                        umma_bf16_ss_pred(tmem_base + kTmemOCol + c * NPAD, pa_sw + soff, pb + boff, idesc_pv, k > 0 ? 1u : acc0, go);
+                    } else {
+                        umma_bf16_ss_pred(tmem_base + kTmemOCol + c * NPAD, pa + aoff, pb + boff, idesc_pv, k > 0 ? 1u : acc0, go);
+                    }
                 }
                 umma_commit_pred(bars + (kBarFree + c) * 8, go);   // chunk c of the K buffer may be refilled
             }
@@ -1141,6 +1173,68 @@ __device__ __forceinline__ void qload_role(const KernelArgs &a, uint8_t *smem, i
     }
 }
 
+// ------------------------------------------------------------------ K loader warp (19; dense paged MLA with TMA)
+// Follows the segments; for every tile and K chunk c it waits until the previous tile's PV has released
+// the chunk, then fetches the chunk's two slabs (and with chunk 3 the RoPE slab, which shares its memory
+// with P^T) for every piece of R rows of the tile that holds rows of the sequence.  Lane p looks up the page
+// of piece p in the block table and issues that piece's boxes; completion is counted in bytes on the
+// chunk's "landed" barrier.  It is a producer of the tile chain (nothing advances without its boxes), so
+// waiting on the free barriers by phase is safe here.  The pieces of the tile after next are pulled into L2.
+template <int NPAD>
+__device__ __forceinline__ void kload_role(const KernelArgs &a, uint8_t *smem, int lane) {
+    using L = Smem<NPAD, true>;
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::kAbort);
+    const uint32_t bars = smem_u32(smem + L::kBars);
+    const volatile int *ring = reinterpret_cast<const volatile int *>(smem + L::kSched) + kSchedRec;
+    const int R = a.k_box_rows, pieces_per_tile = kTileRows / R;
+    const uint32_t k_addr = smem_u32(smem + L::kK), rope_addr = smem_u32(smem + L::kP);
+    const bool contiguous_rows = a.swa.pos_stride == kDenseRowBytes;
+    int gt = 0;
+    for (int so = 0;; ++so) {
+        const volatile int *rec = ring + 12 * (so % 5);
+        if (!wait_published(reinterpret_cast<const int *>(smem + L::kSched), so, abort_flag)) return;
+        if ((rec[7] & kSegValid) == 0) break;
+        const int t = rec[0], n = rec[2], tile0 = rec[4], ntl = rec[5];
+        const int b = a.dense_sq == 1 ? t : t / a.dense_sq;
+        const int *table = a.swa.indices + static_cast<long long>(b) * a.swa.idx_stride;
+        for (int it = 0; it < ntl; ++it, ++gt) {
+            const int g = (tile0 + it) * kTileRows + lane * R;          // first row of this lane's piece
+            const bool mine = lane < pieces_per_tile && g < n;
+            int page = 0, row_in_page = 0;
+            if (mine) {
+                const int page_i = a.swa.block_shift >= 0 ? (g >> a.swa.block_shift) : g / a.swa.block_size;
+                page = __ldg(table + page_i);
+                row_in_page = g - page_i * a.swa.block_size;
+            }
+            const uint32_t pieces = __popc(__ballot_sync(0xffffffffu, mine));
+            const uint32_t dst_row = static_cast<uint32_t>(lane * R) * 128u;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                if (gt > 0 && !warp_wait(bars + (kBarFree + c) * 8, (gt - 1) & 1, abort_flag, lane, kStatusGatherWait)) return;
+                const uint32_t bar = bars + (kBarLand + c) * 8;
+                if (lane == 0) mbar_arrive_expect_tx(bar, pieces * static_cast<uint32_t>(R) * 128u * (c == 3 ? 3u : 2u));
+                __syncwarp();
+                if (mine) {
+                    tma_load_3d(k_addr + (2 * c) * kSlabBytes + dst_row, &a.k_map, bar, 128 * c, row_in_page, page);
+                    tma_load_3d(k_addr + (2 * c + 1) * kSlabBytes + dst_row, &a.k_map, bar, 128 * c + 64, row_in_page, page);
+                    if (c == 3) tma_load_3d(rope_addr + dst_row, &a.k_map, bar, 512, row_in_page, page);
+                }
+            }
+            // the tile after next of this segment, into L2
+            const int g2 = g + 2 * kTileRows;
+            if (contiguous_rows && lane < pieces_per_tile && it + 2 < ntl && g2 < n) {
+                const int page_i = a.swa.block_shift >= 0 ? (g2 >> a.swa.block_shift) : g2 / a.swa.block_size;
+                const int pg = __ldg(table + page_i);
+                if (pg >= 0) {
+                    const uint8_t *src = a.swa.cache + static_cast<long long>(pg) * a.swa.block_stride +
+                                         static_cast<long long>(g2 - page_i * a.swa.block_size) * kDenseRowBytes;
+                    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(min(R, n - g2) * kDenseRowBytes) : "memory");
+                }
+            }
+        }
+    }
+}
+
 // ------------------------------------------------------------------ scheduler warp (18)
 // Publishes the segment records.  Records 1..4 at once, then record s + 3 when the first tile of
 // segment s has been scored: the ring slot it overwrites belonged to segment s - 2, whose last reader
@@ -1171,7 +1265,7 @@ __device__ __forceinline__ void scheduler_role(const KernelArgs &a, uint8_t *sme
 // The raw bytes of the next tile are always in flight, across segment boundaries too.
 template <int FMT, int NPAD>
 __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, uint32_t tmem_base, int warp, int lane) {
-    using L = Smem<NPAD, FMT == kFmtBf16Dense>;
+    using L = Smem<NPAD, is_dense(FMT)>;
     constexpr int J = Steps<FMT>::kCount;
     constexpr int CW = NPAD / 4;   // head columns per warp in the softmax job
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::kAbort);
@@ -1285,7 +1379,7 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
         }
         named_bar_sync(kAllWorkersBar, kWorkerThreads);
         if (direct) {
-            if constexpr (FMT == kFmtBf16Dense) {
+            if constexpr (is_dense(FMT)) {
                 // Dense paged MLA has no staging area (its longer Q rows take the room): a thread holds one dim
                 // of HR heads and stores it as it is; the 32 lanes of a warp hold 32 consecutive dims, so each
                 // 2-byte store instruction writes one 64-byte segment of a head's output row.
@@ -1405,9 +1499,13 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
     {   // raw bytes of the very first tile (segment 0 was published before the roles split)
         const int *r0 = sched + kSchedRec;
         g = r0[4] * kTileRows + my_row;
-        cur = make_row_ref<FMT>(a, r0[3], r0[2], g, FMT == kFmtBf16Dense ? load_dense_slot_id(a, r0[0], r0[2], g)
-                                                                          : load_slot_id(a, r0[0], r0[3], r0[2], g));
-        load_row_pieces<FMT>(cur, quarter, raw);
+        if constexpr (FMT == kFmtBf16DenseTma) {
+            cur = make_row_ref<FMT>(a, 0, 0, 0, -1);        // the loader warp fetches the rows
+        } else {
+            cur = make_row_ref<FMT>(a, r0[3], r0[2], g, is_dense(FMT) ? load_dense_slot_id(a, r0[0], r0[2], g)
+                                                                     : load_slot_id(a, r0[0], r0[3], r0[2], g));
+            load_row_pieces<FMT>(cur, quarter, raw);
+        }
     }
 
     for (int k = 0;; ++k) {      // segments
@@ -1434,10 +1532,40 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
             const bool more = in_seg || have_next;
             const int n_t = in_seg ? sg[0] : ng[0], n_ns = in_seg ? sg[3] : ng[3], n_n = in_seg ? sg[2] : ng[2];
             const int g_next = in_seg ? g + kTileRows : ng[4] * kTileRows + my_row;
-            const int id_next = !more ? -1 : FMT == kFmtBf16Dense ? load_dense_slot_id(a, n_t, n_n, g_next)
-                                                                  : load_slot_id(a, n_t, n_ns, n_n, g_next);
+            const int id_next = (!more || FMT == kFmtBf16DenseTma) ? -1
+                                : is_dense(FMT)                     ? load_dense_slot_id(a, n_t, n_n, g_next)
+                                                                    : load_slot_id(a, n_t, n_ns, n_n, g_next);
 
-            if constexpr (FMT == kFmtBf16Dense) {
+            if constexpr (FMT == kFmtBf16DenseTma) {
+                // ---- K by TMA: the loader warp fills the chunks; the workers only wait for a chunk to land,
+                // wipe the rows of a last, partial tile that lie past the sequence (whatever the boxes brought
+                // or left there must not reach the tensor pipe: 0 x NaN is NaN) and hand the chunk over.
+                const bool wipe = my_row >= rows_left;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    warp_wait(bars + (kBarLand + c) * 8, gt & 1, abort_flag, lane, kStatusGatherWait);
+                    if (rows_left < kTileRows) {
+                        if (wipe) {
+                            const uint32_t sw = static_cast<uint32_t>(my_row & 7);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const uint32_t piece = 4u * i + quarter;         // 16-byte piece of the chunk's 256 bytes
+                                const uint32_t addr = smem_u32(smem + L::kK) + (2 * c + (piece >> 3)) * kSlabBytes + my_row * 128 +
+                                                      (((piece & 7u) ^ sw) << 4);
+                                st_shared_v4(addr, 0u, 0u, 0u, 0u);
+                            }
+                            if (c == 3) {
+#pragma unroll
+                                for (int i = 0; i < 2; ++i)
+                                    st_shared_v4(smem_u32(smem + L::kP) + my_row * 128 + (((4u * i + quarter) ^ sw) << 4), 0u, 0u, 0u, 0u);
+                            }
+                        }
+                        fence_async_smem();
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bars + (kBarReady + c) * 8);
+                }
+            } else if constexpr (FMT == kFmtBf16Dense) {
                 // ---- bf16 rows: cp.async straight into the K chunks as the previous tile's PV releases them
                 // (this thread: four 16-byte pieces of its row per chunk), the RoPE dims with chunk 3 into the buffer
                 // they share with P^T, which PV has finished reading by then; handed over as they land.
@@ -1503,8 +1631,10 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
             // the chunks would put a memory latency on every hand-over.  They land while QK^T runs.
             // (Measured: sending half of them after the softmax instead made the tile 25 % slower: the
             // issue of a load blocks the warp while the SM's load queue is full.)
-            cur = make_row_ref<FMT>(a, n_ns, n_n, more ? g_next : n_n, id_next);
-            if (more) load_row_pieces<FMT>(cur, quarter, raw);
+            if constexpr (FMT != kFmtBf16DenseTma) {
+                cur = make_row_ref<FMT>(a, n_ns, n_n, more ? g_next : n_n, id_next);
+                if (more) load_row_pieces<FMT>(cur, quarter, raw);
+            }
             if constexpr (FMT == kFmtBf16Dense) {
                 // Dense rows come from HBM once (no reuse between query tokens as in the sparse workloads):
                 // measured, a row asked for one tile ahead arrives 7-8k cycles after its cp.async was issued,
@@ -1629,15 +1759,22 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
             break;
         }
     }
-    if (a.fused_merge == 2) merge_head_slices<NPAD, FMT == kFmtBf16Dense>(a, smem, tid, warp, lane);
+    if (a.fused_merge == 2) merge_head_slices<NPAD, is_dense(FMT)>(a, smem, tid, warp, lane);
 }
 
 // ------------------------------------------------------------------ the kernel
 template <int FMT, int NPAD>
 __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const __grid_constant__ KernelArgs a) {
-    extern __shared__ __align__(128) uint8_t smem[];
-    using L = Smem<NPAD, FMT == kFmtBf16Dense>;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    using L = Smem<NPAD, is_dense(FMT)>;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if constexpr (FMT == kFmtBf16DenseTma) {
+        // the swizzled K slabs (written by TMA, read by the tensor pipe) need a 1024-byte aligned base
+        if ((smem_u32(smem) & 1023u) != 0u) {
+            if (tid == 0) atomicOr(&g_device_status, kStatusSmemLayout);
+            return;
+        }
+    }
 
     // ---- this CTA's share of the work
     int *sched = reinterpret_cast<int *>(smem + L::kSched);
@@ -1666,6 +1803,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const __gri
         mbar_init(bars + kBarO * 8, 1);
         mbar_init(bars + kBarOFree * 8, kWorkerWarps);
         mbar_init(bars + kBarQ * 8, a.q_tma ? 1 : kQLoadWarps);
+        for (int c = 0; c < 4; ++c) mbar_init(bars + (kBarLand + c) * 8, 1);
         *reinterpret_cast<volatile int *>(smem + L::kAbort) = 0;
         sched[kSchedTiles] = 0;
         mbar_init_fence();
@@ -1701,15 +1839,18 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const __gri
     if (warp < kWorkerWarps) {
         worker_role<FMT, NPAD>(a, smem, tmem_base, warp, lane);
     } else if (warp == kMmaWarp) {
-        mma_role<NPAD, FMT == kFmtBf16Dense>(smem, tmem_base);
+        mma_role<NPAD, is_dense(FMT), FMT == kFmtBf16DenseTma>(smem, tmem_base);
     } else if (a.q_tma) {
         // one tensor copy per item needs one thread; the next warp publishes the schedule
-        if (warp == kMmaWarp + 1) qload_role<NPAD, FMT == kFmtBf16Dense>(a, smem, 0, lane);
-        if (warp == kMmaWarp + 2) scheduler_role<NPAD, FMT == kFmtBf16Dense>(a, smem, lane);
+        if (warp == kMmaWarp + 1) qload_role<NPAD, is_dense(FMT)>(a, smem, 0, lane);
+        if (warp == kMmaWarp + 2) scheduler_role<NPAD, is_dense(FMT)>(a, smem, lane);
+        if constexpr (FMT == kFmtBf16DenseTma) {
+            if (warp == kMmaWarp + 3) kload_role<NPAD>(a, smem, lane);
+        }
     } else {
         // cp.async fallback for Q: two loader warps, one scheduler warp
-        if (warp == kMmaWarp + 2) scheduler_role<NPAD, FMT == kFmtBf16Dense>(a, smem, lane);
-        else qload_role<NPAD, FMT == kFmtBf16Dense>(a, smem, warp == kMmaWarp + 1 ? 0 : 1, lane);
+        if (warp == kMmaWarp + 2) scheduler_role<NPAD, is_dense(FMT)>(a, smem, lane);
+        else qload_role<NPAD, is_dense(FMT)>(a, smem, warp == kMmaWarp + 1 ? 0 : 1, lane);
     }
 
     __syncthreads();
@@ -1783,7 +1924,7 @@ int fill_stream(const smla_stream_t &s, int fmt, StreamDev &d) {
 
 template <int FMT, int NPAD>
 int launch_fwd(const KernelArgs &a, unsigned grid, cudaStream_t stream) {
-    constexpr int smem_bytes = Smem<NPAD, FMT == kFmtBf16Dense>::kTotal;
+    constexpr int smem_bytes = Smem<NPAD, is_dense(FMT)>::kTotal;
     // The opt-in to 227 KB of dynamic shared memory is per device and per kernel instance; hosts that
     // run one thread per GPU come through here concurrently, hence atomics (setting it twice is harmless).
     static std::atomic<bool> attr_done[64];
@@ -1839,6 +1980,21 @@ bool make_q_tensor_map(const KernelArgs &a, int npad, int dim_groups, CUtensorMa
     const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
     const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<__nv_bfloat16 *>(a.q), dims, strides, box,
                            estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                           CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+// Dense paged MLA: the bf16 cache as a 3-D tensor {576 dims, rows of a page, pages}; a box {64 dims, R rows, 1 page}
+// with the 128-byte swizzle is R rows of one slab of the K tile.
+bool make_k_tensor_map(const KernelArgs &a, int num_blocks, int box_rows, CUtensorMap *map) {
+    EncodeTiledFn enc = tensor_map_encoder();
+    if (enc == nullptr || num_blocks <= 0) return false;
+    const cuuint64_t dims[3] = {576, static_cast<cuuint64_t>(a.swa.block_size), static_cast<cuuint64_t>(num_blocks)};
+    const cuuint64_t strides[2] = {static_cast<cuuint64_t>(a.swa.pos_stride), static_cast<cuuint64_t>(a.swa.block_stride)};
+    const cuuint32_t box[3] = {64, static_cast<cuuint32_t>(box_rows), 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<uint8_t *>(a.swa.cache), dims, strides, box,
+                           estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                            CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
 }
@@ -1906,10 +2062,12 @@ int schedule_and_launch(KernelArgs &a, int fmt, int num_splits, void *workspace,
         a.balanced = 0;
         ctas = std::min<long long>(items, sms);
     }
-    a.q_tma = make_q_tensor_map(a, npad, fmt == kFmtBf16Dense ? 72 : 64, &a.q_map) ? 1 : 0;
+    a.q_tma = make_q_tensor_map(a, npad, is_dense(fmt) ? 72 : 64, &a.q_map) ? 1 : 0;
+    if (fmt == kFmtBf16DenseTma && !a.q_tma) fmt = kFmtBf16Dense;      // the K loader is the warp the Q fallback needs
     const unsigned grid = static_cast<unsigned>(ctas);
     const bool int8_wide = fmt == SMLA_INT8_DS_MLA && a.swa.vec == 2 && (a.extra.cache == nullptr || a.extra.vec == 2);
-    rc = (fmt == kFmtBf16Dense)      ? launch_fwd_npad<kFmtBf16Dense>(npad, a, grid, stream)
+    rc = (fmt == kFmtBf16DenseTma)   ? launch_fwd_npad<kFmtBf16DenseTma>(npad, a, grid, stream)
+         : (fmt == kFmtBf16Dense)   ? launch_fwd_npad<kFmtBf16Dense>(npad, a, grid, stream)
          : (fmt == SMLA_FP8_DS_MLA) ? launch_fwd_npad<SMLA_FP8_DS_MLA>(npad, a, grid, stream)
          : int8_wide                ? launch_fwd_npad<kFmtInt8Wide>(npad, a, grid, stream)
                                     : launch_fwd_npad<SMLA_INT8_DS_MLA>(npad, a, grid, stream);
@@ -1998,7 +2156,17 @@ int launch_dense_mla_attention(const smla_dense_params_t &p, cudaStream_t stream
     a.swa.block_size = p.page_block_size;
     a.swa.block_shift = (p.page_block_size & (p.page_block_size - 1)) ? -1 : __builtin_ctz(static_cast<unsigned>(p.page_block_size));
     a.swa.vec = 1;
-    return schedule_and_launch(a, kFmtBf16Dense, p.num_splits, p.workspace, p.workspace_bytes, stream);
+    // K by TMA when a 128-row tile is a whole number of pages or a page a whole number of tiles
+    int fmt = kFmtBf16Dense;
+    const int page = p.page_block_size;
+    if (page % 8 == 0 && (page >= 128 ? page % 128 == 0 : 128 % page == 0)) {
+        const int box_rows = std::min(page, 128);
+        if (make_k_tensor_map(a, p.num_blocks, box_rows, &a.k_map)) {
+            a.k_box_rows = box_rows;
+            fmt = kFmtBf16DenseTma;
+        }
+    }
+    return schedule_and_launch(a, fmt, p.num_splits, p.workspace, p.workspace_bytes, stream);
 }
 
 int read_and_clear_device_status(int *status_out) {

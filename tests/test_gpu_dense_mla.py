@@ -93,6 +93,30 @@ def test_dense_every_schedule_and_merge(fm, b, mean_sk, block_size):
     check(out, lse, ref_out, ref_lse, f"b={b}", sequences=seqs)
 
 
+@pytest.mark.parametrize("block_size", [16, 32, 64, 128, 256])
+def test_dense_page_sizes(fm, block_size):
+    """Pages smaller than, equal to and larger than the 128-row tile (the K tile is fetched in boxes of
+    min(page, 128) rows), ragged lengths, two query positions with the causal mask."""
+    kw, _ = dense_decode_workload(b=5, s_q=2, mean_sk=900, h_q=64, varlen=True, block_size=block_size, seed=block_size)
+    out, lse = run_api(fm, kw, causal=True)
+    ref_out, ref_lse = oracle.dense_mla_decode(kw["q"], kw["k_cache"], kw["block_table"], kw["cache_seqlens"], causal=True)
+    check(out, lse, ref_out, ref_lse, f"page {block_size}")
+
+
+def test_dense_strided_cache_and_q(fm):
+    """A cache whose rows are wider than 576 elements (row stride 640) and a q that is a slice of a wider
+    tensor: strides are honoured, nothing is copied for the cache."""
+    kw, _ = dense_decode_workload(b=4, s_q=1, mean_sk=700, h_q=32, varlen=True, block_size=64, seed=21)
+    wide = torch.full((*kw["k_cache"].shape[:3], 640), float("nan"), device="cuda", dtype=torch.bfloat16)
+    wide[..., :576] = kw["k_cache"]
+    qwide = torch.randn(4, 1, 32, 600, device="cuda").to(torch.bfloat16)
+    qwide[..., :576] = kw["q"]
+    kw2 = dict(kw, k_cache=wide[..., :576], q=qwide[..., :576])
+    out, lse = run_api(fm, kw2, causal=False)
+    ref_out, ref_lse = oracle.dense_mla_decode(kw["q"], kw["k_cache"], kw["block_table"], kw["cache_seqlens"])
+    check(out, lse, ref_out, ref_lse, "strided")
+
+
 def test_dense_edges(fm):
     """Lengths at the edges: exactly s_q rows (the shortest the reference generates), exact multiples of the
     128-row tile and of the page, one row more, and 12 heads (not a multiple of 8: Q arrives by cp.async)."""
