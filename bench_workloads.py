@@ -183,12 +183,11 @@ def prefill_int8_workload(T: int = 4096, H: int = 64, swa_slots: int = 16384, sw
 
 
 def dense_decode_workload(b: int = 128, s_q: int = 1, mean_sk: int = 4096, h_q: int = 128, varlen: bool = False,
-                          block_size: int = 64, seed: int = 0, device="cuda", poison_tail: bool = True):
+                          block_size: int = 64, seed: int = 0, device="cuda", poison_tail: bool = True, d: int = 576):
     """The reference's dense test case (tests/test_flash_mla_sm80.py:43-63): ``b`` sequences of ``mean_sk`` rows
     (``varlen``: normal around it with sigma mean_sk / 2, at least s_q), q and the bf16 cache N(0, 1), pages in
     a scrambled order, rows past each length NaN so that any read of them shows in the result."""
     gen = _gen(device, seed)
-    d = 576
     lens = torch.full((b,), mean_sk, dtype=torch.int32)
     if varlen:
         cpu_gen = torch.Generator().manual_seed(seed + 1)
@@ -206,7 +205,7 @@ def dense_decode_workload(b: int = 128, s_q: int = 1, mean_sk: int = 4096, h_q: 
         k_cache[block_table[i].long()] = rows.view(pages_per_seq, block_size, 1, d)
     lens = lens.to(device)
     rows_total = int(lens.sum()) * s_q        # without the causal trim (at most s_q - 1 rows per query)
-    meta = {"flops": 2 * rows_total * h_q * (576 + 512),
-            "bytes": int(lens.sum()) * 1152 + b * s_q * h_q * (576 + 512) * 2 + b * pages_per_seq * 4,
+    meta = {"flops": 2 * rows_total * h_q * (d + 512),
+            "bytes": int(lens.sum()) * 2 * d + b * s_q * h_q * (d + 512) * 2 + b * pages_per_seq * 4,
             "rows_in_lens": rows_total}
     return {"q": q, "k_cache": k_cache, "block_table": block_table, "cache_seqlens": lens}, meta

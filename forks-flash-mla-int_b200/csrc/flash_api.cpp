@@ -323,9 +323,10 @@ void fwd_kvcache_mla(const Tensor &q_in, const Tensor &kcache, const std::option
     STD_TORCH_CHECK(q_in.dim() == 4, "q must have shape (batch_size, seqlen_q, num_heads, head_size)");
     STD_TORCH_CHECK(q_in.scalar_type() == ScalarType::BFloat16 && kcache.scalar_type() == ScalarType::BFloat16,
                     "query and key must be bfloat16");
-    STD_TORCH_CHECK(q_in.size(3) == 576 && head_size_v == 512, "only head_size 576 with head_size_v 512 is built");
-    STD_TORCH_CHECK(kcache.dim() == 4 && kcache.size(2) == 1 && kcache.size(3) == 576,
-                    "kcache must have shape (num_blocks, page_block_size, 1, 576)");
+    const int64_t D = q_in.size(3);
+    STD_TORCH_CHECK((D == 576 || D == 512) && head_size_v == 512, "head_size must be 576 or 512 with head_size_v 512");
+    STD_TORCH_CHECK(kcache.dim() == 4 && kcache.size(2) == 1 && kcache.size(3) == D,
+                    "kcache must have shape (num_blocks, page_block_size, 1, head_size)");
     STD_TORCH_CHECK(kcache.stride(3) == 1, "Input tensor must have contiguous last dimension");
     if (vcache.has_value())
         STD_TORCH_CHECK(vcache->data_ptr() == kcache.data_ptr(), "vcache must be a view of kcache (or None)");
@@ -339,7 +340,7 @@ void fwd_kvcache_mla(const Tensor &q_in, const Tensor &kcache, const std::option
     const int device = q_in.get_device_index();
     torch::stable::accelerator::DeviceGuard guard(device);
 
-    // Tokens are (sequence, query position) pairs: q is read as [B * SQ, H, 576].
+    // Tokens are (sequence, query position) pairs: q is read as [B * SQ, H, head_size].
     const bool q_ok = q_in.stride(3) == 1 && q_in.stride(0) == SQ * q_in.stride(1) && q_in.stride(1) % 8 == 0 &&
                       q_in.stride(2) % 8 == 0 && aligned16(q_in);
     const Tensor q = q_ok ? q_in : torch::stable::contiguous(q_in);
@@ -353,6 +354,7 @@ void fwd_kvcache_mla(const Tensor &q_in, const Tensor &kcache, const std::option
     p.seqlen_q = static_cast<int32_t>(SQ);
     p.num_heads = static_cast<int32_t>(H);
     p.causal = is_causal ? 1 : 0;
+    p.head_dim = static_cast<int32_t>(D);
     p.softmax_scale = static_cast<float>(softmax_scale);
     p.q = q.data_ptr();
     p.q_token_stride = q.stride(1);

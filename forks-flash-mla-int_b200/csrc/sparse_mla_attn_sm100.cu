@@ -159,6 +159,7 @@ struct KernelArgs {
     // the first len - (dense_sq - 1 - i) rows.  lse[(b * H + h) * dense_sq + i], natural log, may be null.
     float *lse;
     int dense_sq, causal;
+    int dense_dims;       // 576, or 512 (no RoPE dims: the fifth K chunk and the last eight Q groups are zero-filled)
     CUtensorMap k_map;    // kFmtBf16DenseTma: 3-D view {576 dims, page rows, pages} of the cache, box {64, k_box_rows, 1}
     int k_box_rows;
 };
@@ -417,7 +418,8 @@ __device__ __forceinline__ int piece16(int j, int quarter) {
 }
 
 template <int FMT>
-__device__ __forceinline__ void load_row_pieces(const RowRef<FMT> &r, int quarter, uint4 (&raw)[Steps<FMT>::kCount]) {
+__device__ __forceinline__ void load_row_pieces(const RowRef<FMT> &r, int quarter, uint4 (&raw)[Steps<FMT>::kCount],
+                                                int row_bytes = kDenseRowBytes) {
     constexpr int J = Steps<FMT>::kCount;
     // Invalid rows are zero rows; the choice is made per load (a select, no divergent branch).
     if constexpr (is_dense(FMT)) {
@@ -425,7 +427,7 @@ __device__ __forceinline__ void load_row_pieces(const RowRef<FMT> &r, int quarte
         // 288 bytes per thread a tile ahead); a tile ahead they are only pulled into L2.
         raw[0] = make_uint4(0u, 0u, 0u, 0u);
         if (r.ok && quarter == 0)      // one bulk prefetch per row (1152 bytes)
-            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(r.ptr), "r"(kDenseRowBytes) : "memory");
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(r.ptr), "r"(row_bytes) : "memory");
     } else if constexpr (FMT == kFmtInt8Wide) {
         // 512 data bytes from a 16-byte aligned address: an even row is 16 aligned 32-byte windows; an
         // odd row is fetched from 16 bytes earlier (the tail of the token before it, readable), so
@@ -1003,8 +1005,8 @@ __device__ __forceinline__ void issue_q_tile(const KernelArgs &a, uint8_t *smem,
     constexpr int kQuads = L::kQDimGroups / 4;      // groups of four 16-byte pieces per head row
     for (int idx = warp; idx < (NPAD / 8) * kQuads; idx += nwarps) {
         const int hg = idx / kQuads, dg = (idx - hg * kQuads) * 4 + (lane >> 3), h = hg * 8 + (lane & 7);
-        const bool ok = h < hvalid;
-        const __nv_bfloat16 *src = qt + static_cast<long long>(ok ? h : 0) * a.q_hs + dg * 8;
+        const bool ok = h < hvalid && (!DENSE || dg * 8 < a.dense_dims);
+        const __nv_bfloat16 *src = qt + static_cast<long long>(ok ? h : 0) * a.q_hs + (ok ? dg : 0) * 8;
         cp_async_16_zfill(q_addr + hg * L::kQRowGroup + dg * kCoreBytes + (lane & 7) * 16, src, ok ? 16u : 0u);
     }
 }
@@ -1188,7 +1190,8 @@ __device__ __forceinline__ void kload_role(const KernelArgs &a, uint8_t *smem, i
     const volatile int *ring = reinterpret_cast<const volatile int *>(smem + L::kSched) + kSchedRec;
     const int R = a.k_box_rows, pieces_per_tile = kTileRows / R;
     const uint32_t k_addr = smem_u32(smem + L::kK), rope_addr = smem_u32(smem + L::kP);
-    const bool contiguous_rows = a.swa.pos_stride == kDenseRowBytes;
+    const int row_bytes = a.dense_dims * 2;
+    const bool contiguous_rows = a.swa.pos_stride == row_bytes;
     int gt = 0;
     for (int so = 0;; ++so) {
         const volatile int *rec = ring + 12 * (so % 5);
@@ -1227,8 +1230,8 @@ __device__ __forceinline__ void kload_role(const KernelArgs &a, uint8_t *smem, i
                 const int pg = __ldg(table + page_i);
                 if (pg >= 0) {
                     const uint8_t *src = a.swa.cache + static_cast<long long>(pg) * a.swa.block_stride +
-                                         static_cast<long long>(g2 - page_i * a.swa.block_size) * kDenseRowBytes;
-                    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(min(R, n - g2) * kDenseRowBytes) : "memory");
+                                         static_cast<long long>(g2 - page_i * a.swa.block_size) * row_bytes;
+                    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(min(R, n - g2) * row_bytes) : "memory");
                 }
             }
         }
@@ -1504,7 +1507,7 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
         } else {
             cur = make_row_ref<FMT>(a, r0[3], r0[2], g, is_dense(FMT) ? load_dense_slot_id(a, r0[0], r0[2], g)
                                                                      : load_slot_id(a, r0[0], r0[3], r0[2], g));
-            load_row_pieces<FMT>(cur, quarter, raw);
+            load_row_pieces<FMT>(cur, quarter, raw, is_dense(FMT) ? a.dense_dims * 2 : 0);
         }
     }
 
@@ -1584,7 +1587,8 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
 #pragma unroll
                         for (int i = 0; i < 2; ++i) {
                             const int dg = 4 * i + quarter;
-                            cp_async_16_zfill(rope_row_addr + dg * kCoreBytes, src + 1024 + dg * 16, nbytes);
+                            cp_async_16_zfill(rope_row_addr + dg * kCoreBytes, src + (a.dense_dims > 512 ? 1024 + dg * 16 : 0),
+                                              a.dense_dims > 512 ? nbytes : 0u);
                         }
                     }
                     cp_async_commit();
@@ -1633,7 +1637,7 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
             // issue of a load blocks the warp while the SM's load queue is full.)
             if constexpr (FMT != kFmtBf16DenseTma) {
                 cur = make_row_ref<FMT>(a, n_ns, n_n, more ? g_next : n_n, id_next);
-                if (more) load_row_pieces<FMT>(cur, quarter, raw);
+                if (more) load_row_pieces<FMT>(cur, quarter, raw, is_dense(FMT) ? a.dense_dims * 2 : 0);
             }
             if constexpr (FMT == kFmtBf16Dense) {
                 // Dense rows come from HBM once (no reuse between query tokens as in the sparse workloads):
@@ -1642,7 +1646,7 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
                 if (left > 2) {
                     const int g2 = g_next + kTileRows;
                     const RowRef<FMT> ahead = make_row_ref<FMT>(a, sg[3], sg[2], g2, load_dense_slot_id(a, sg[0], sg[2], g2));
-                    load_row_pieces<FMT>(ahead, quarter, raw);
+                    load_row_pieces<FMT>(ahead, quarter, raw, a.dense_dims * 2);
                 }
             }
             g = g_next;
@@ -1969,14 +1973,14 @@ EncodeTiledFn tensor_map_encoder() {
 
 // 5-D view of q [T, H, 512] whose box {8, 8, 64, npad/8, 1} is the Q operand's shared-memory layout.
 // False (the kernel then uses cp.async) when H is not a multiple of 8 or the driver refuses the map.
-bool make_q_tensor_map(const KernelArgs &a, int npad, int dim_groups, CUtensorMap *map) {
+bool make_q_tensor_map(const KernelArgs &a, int npad, int dim_groups, int box_dim_groups, CUtensorMap *map) {
     if (a.H % 8 != 0) return false;
     EncodeTiledFn enc = tensor_map_encoder();
     if (enc == nullptr) return false;
     const cuuint64_t dims[5] = {8, 8, static_cast<cuuint64_t>(dim_groups), static_cast<cuuint64_t>(a.H / 8), static_cast<cuuint64_t>(a.T)};
     const cuuint64_t strides[4] = {static_cast<cuuint64_t>(a.q_hs) * 2, 16, static_cast<cuuint64_t>(a.q_hs) * 16,
                                    static_cast<cuuint64_t>(a.q_ts) * 2};
-    const cuuint32_t box[5] = {8, 8, static_cast<cuuint32_t>(dim_groups), static_cast<cuuint32_t>(npad / 8), 1};
+    const cuuint32_t box[5] = {8, 8, static_cast<cuuint32_t>(box_dim_groups), static_cast<cuuint32_t>(npad / 8), 1};
     const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
     const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<__nv_bfloat16 *>(a.q), dims, strides, box,
                            estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
@@ -1989,7 +1993,7 @@ bool make_q_tensor_map(const KernelArgs &a, int npad, int dim_groups, CUtensorMa
 bool make_k_tensor_map(const KernelArgs &a, int num_blocks, int box_rows, CUtensorMap *map) {
     EncodeTiledFn enc = tensor_map_encoder();
     if (enc == nullptr || num_blocks <= 0) return false;
-    const cuuint64_t dims[3] = {576, static_cast<cuuint64_t>(a.swa.block_size), static_cast<cuuint64_t>(num_blocks)};
+    const cuuint64_t dims[3] = {static_cast<cuuint64_t>(a.dense_dims), static_cast<cuuint64_t>(a.swa.block_size), static_cast<cuuint64_t>(num_blocks)};
     const cuuint64_t strides[2] = {static_cast<cuuint64_t>(a.swa.pos_stride), static_cast<cuuint64_t>(a.swa.block_stride)};
     const cuuint32_t box[3] = {64, static_cast<cuuint32_t>(box_rows), 1};
     const cuuint32_t estr[3] = {1, 1, 1};
@@ -2062,7 +2066,7 @@ int schedule_and_launch(KernelArgs &a, int fmt, int num_splits, void *workspace,
         a.balanced = 0;
         ctas = std::min<long long>(items, sms);
     }
-    a.q_tma = make_q_tensor_map(a, npad, is_dense(fmt) ? 72 : 64, &a.q_map) ? 1 : 0;
+    a.q_tma = make_q_tensor_map(a, npad, is_dense(fmt) ? a.dense_dims / 8 : 64, is_dense(fmt) ? 72 : 64, &a.q_map) ? 1 : 0;
     if (fmt == kFmtBf16DenseTma && !a.q_tma) fmt = kFmtBf16Dense;      // the K loader is the warp the Q fallback needs
     const unsigned grid = static_cast<unsigned>(ctas);
     const bool int8_wide = fmt == SMLA_INT8_DS_MLA && a.swa.vec == 2 && (a.extra.cache == nullptr || a.extra.vec == 2);
@@ -2127,8 +2131,9 @@ int launch_dense_mla_attention(const smla_dense_params_t &p, cudaStream_t stream
     if ((reinterpret_cast<uintptr_t>(p.q) & 15u) || (p.q_token_stride & 7) || (p.q_head_stride & 7) ||
         (reinterpret_cast<uintptr_t>(p.out) & 15u) || (p.out_token_stride & 7) || (p.out_head_stride & 7) ||
         (reinterpret_cast<uintptr_t>(p.k_cache) & 15u) || (p.k_block_stride & 15) || (p.k_row_stride & 15) ||
-        p.k_row_stride < kDenseRowBytes)
+        p.k_row_stride < (p.head_dim == 512 ? 1024 : kDenseRowBytes))
         return SMLA_EALIGN;
+    if (p.head_dim != 0 && p.head_dim != 576 && p.head_dim != 512) return SMLA_EINVAL;
     KernelArgs a = {};
     a.q = static_cast<const __nv_bfloat16 *>(p.q);
     a.q_ts = p.q_token_stride;
@@ -2142,6 +2147,7 @@ int launch_dense_mla_attention(const smla_dense_params_t &p, cudaStream_t stream
     a.scale_log2 = p.softmax_scale * kLog2e;
     a.lse = p.softmax_lse;
     a.dense_sq = p.seqlen_q;
+    a.dense_dims = p.head_dim == 512 ? 512 : 576;
     a.causal = (p.causal && p.seqlen_q > 1) ? 1 : 0;
     a.swa.cache = static_cast<const uint8_t *>(p.k_cache);
     a.swa.indices = p.block_table;

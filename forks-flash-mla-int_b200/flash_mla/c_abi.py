@@ -68,6 +68,7 @@ class SmlaDenseParams(C.Structure):
         ("seqlen_q", C.c_int32),
         ("num_heads", C.c_int32),
         ("causal", C.c_int32),
+        ("head_dim", C.c_int32),
         ("softmax_scale", C.c_float),
         ("q", C.c_void_p),
         ("q_token_stride", C.c_int64),
@@ -182,6 +183,7 @@ def dense_params(q, k_cache, block_table, cache_seqlens, out, lse=None, softmax_
     p = SmlaDenseParams()
     p.batch, p.seqlen_q, p.num_heads = q.shape[0], q.shape[1], q.shape[2]
     p.causal = 1 if causal else 0
+    p.head_dim = q.shape[3]
     p.softmax_scale = softmax_scale if softmax_scale is not None else q.shape[-1] ** -0.5
     p.q, p.q_token_stride, p.q_head_stride = q.data_ptr(), q.stride(1), q.stride(2)
     p.out, p.out_token_stride, p.out_head_stride = out.data_ptr(), out.stride(1), out.stride(2)

@@ -171,16 +171,17 @@ SMLA_API int smla_sparse_mla_prefill(const smla_attn_params_t *params, void *str
  * No scheduler metadata is needed: the persistent kernel cuts the work itself (get_mla_metadata of the
  * reference has no counterpart here; the binding returns placeholders of the reference's shapes). */
 typedef struct smla_dense_params {
-    int32_t batch, seqlen_q, num_heads;   /* q [batch, seqlen_q, num_heads, 576] bf16                            */
+    int32_t batch, seqlen_q, num_heads;   /* q [batch, seqlen_q, num_heads, head_dim] bf16                       */
     int32_t causal;                       /* query position i sees the first len - (seqlen_q - 1 - i) rows       */
+    int32_t head_dim;                     /* 576 (0 means 576), or 512: scores over 512 dims, no RoPE part       */
     float softmax_scale;
     const void *q;                        /* 16-byte aligned                                                     */
     int64_t q_token_stride, q_head_stride;       /* elements; token = batch index * seqlen_q + query position   */
     void *out;                            /* [batch, seqlen_q, num_heads, 512] bf16                              */
     int64_t out_token_stride, out_head_stride;   /* elements                                                    */
     float *softmax_lse;                   /* [batch, num_heads, seqlen_q] fp32, natural log; may be NULL         */
-    const void *k_cache;                  /* [num_blocks, page_block_size, 1, 576] bf16, 16-byte aligned         */
-    int64_t k_block_stride, k_row_stride; /* bytes, multiples of 16, k_row_stride >= 1152                        */
+    const void *k_cache;                  /* [num_blocks, page_block_size, 1, head_dim] bf16, 16-byte aligned    */
+    int64_t k_block_stride, k_row_stride; /* bytes, multiples of 16, k_row_stride >= 2 * head_dim                */
     int32_t num_blocks, page_block_size;
     const int32_t *block_table;           /* [batch, max_blocks_per_seq] page numbers (negative: zero rows)      */
     int64_t block_table_stride;           /* elements                                                            */

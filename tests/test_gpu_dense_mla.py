@@ -103,6 +103,16 @@ def test_dense_page_sizes(fm, block_size):
     check(out, lse, ref_out, ref_lse, f"page {block_size}")
 
 
+@pytest.mark.parametrize("b,seqlen,heads", [(2, 128, 4), (4, 256, 8), (6, 1100, 64)])
+def test_dense_head_dim_512(fm, b, seqlen, heads):
+    """head_size 512 = head_size_v (the reference's tests/test_flash_mla_dsv4_sm80.py:18-40 shapes and a larger
+    one): scores over 512 dims, no RoPE part."""
+    kw, _ = dense_decode_workload(b=b, s_q=1, mean_sk=seqlen, h_q=heads, varlen=False, block_size=32, seed=b, d=512)
+    out, lse = run_api(fm, kw, causal=True)
+    ref_out, ref_lse = oracle.dense_mla_decode(kw["q"], kw["k_cache"], kw["block_table"], kw["cache_seqlens"])
+    check(out, lse, ref_out, ref_lse, f"d=512 b={b} heads={heads}")
+
+
 def test_dense_strided_cache_and_q(fm):
     """A cache whose rows are wider than 576 elements (row stride 640) and a q that is a slice of a wider
     tensor: strides are honoured, nothing is copied for the cache."""
