@@ -23,6 +23,9 @@ With the default workload the line also carries, measured in the same process:
                  (int8 prefill, 4096 tokens) and config 5's shapes on one GPU: ms per step, tokens/s,
                  TFLOP/s, roofline, a sampled-token parity check against the CPU oracle and, where the
                  reference's own CUDA kernels were built (oracle/_ref), their time on the same inputs;
+  dense_configs  dense bf16 paged MLA decode (flash_mla_with_kvcache) on the reference's dense test shapes
+                 (batch 128, 4096 / 8192 rows per sequence, 16 / 64 / 128 heads): ms per step, tokens/s,
+                 TFLOP/s, roofline, parity of three sequences against the CPU oracle;
   config5        ONE seeded batch of 1024 tokens (128 heads, 16384-slot caches, top-k 2048 + 512, fp8
                  and int8) cut by token over the N ranks with flash_mla.sharding.shard_tokens, caches
                  replicated: strong scaling against the same batch on one GPU of the same run.
@@ -72,6 +75,11 @@ DEFAULT_WORKLOAD = "dsv4_fp8_decode_T128_H64"
 # measured next to the headline in the default run (BASELINE configs 3, 4 and 5 on one GPU)
 OTHER_CONFIGS = ([f"dsv4_int8_decode_T{t}_H{h}" for h in (64, 128) for t in (1, 8, 32, 128, 512)] +
                  ["int8_prefill_T4096_H64", "ctx16k_fp8_decode_T1024_H128", "ctx16k_int8_decode_T1024_H128"])
+
+
+# dense paged MLA decode (flash_mla_with_kvcache), measured next to the headline as well
+DENSE_CONFIGS = ["dense_bf16_decode_b128_s4096_h128", "dense_bf16_decode_b128_s4096_h16",
+                 "dense_bf16_decode_b128_s8192_h64_sq2_varlen"]
 
 
 def measured_peaks():
@@ -433,6 +441,7 @@ def run_reference(args_ns):
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from ncu captures of this command line
 NCU_DRAM_TRAFFIC_BYTES = {"dsv4_fp8_decode_T128_H64": 42.7e6, "dsv4_int8_decode_T128_H64": 39.7e6,
                           "dsv4_int8_decode_T128_H128": 57.3e6, "int8_prefill_T4096_H64": 537.5e6,
+                          "dense_bf16_decode_b128_s4096_h16": 657.9e6, "dense_bf16_decode_b128_s4096_h128": 1380.2e6,
                           # row kernels: captured on 2^18 rows, scaled by 4
                           "write_int8_cache_rows1M": 1543.6e6, "write_fp8_cache_rows1M": 1567.9e6,
                           "quantize_int8_rows1M": 1495.8e6,
@@ -664,6 +673,51 @@ def dense_oracle_sample(kw, causal, budget_s=12.0):
     out, lse = oracle.dense_mla_decode(cpu["q"], cpu["k_cache"], cpu["block_table"], cpu["cache_seqlens"], causal=causal,
                                        sequences=list(range(n)))
     return n, time.perf_counter() - t0, out, lse, torch.get_num_threads()
+
+
+def dense_config_record(name, dev, steps=6):
+    """One dense paged MLA workload next to the headline: timing, roofline, parity on three sequences."""
+    import numpy as np
+    import torch
+    import flash_mla
+    import bench_workloads
+    import oracle
+    kw_build = WORKLOADS[name][1]
+    kw, meta = bench_workloads.dense_decode_workload(device=dev, seed=0, **kw_build)
+    causal = kw_build["s_q"] > 1
+    md, ns = flash_mla.get_mla_metadata(kw["cache_seqlens"], kw_build["s_q"] * kw_build["h_q"], 1)
+
+    def step():
+        return flash_mla.flash_mla_with_kvcache(kw["q"], kw["k_cache"], kw["block_table"], kw["cache_seqlens"], 512, md, ns,
+                                                causal=causal)
+    for _ in range(3):
+        out, lse = step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    tokens = kw_build["b"] * kw_build["s_q"]
+    seqs = sorted({0, kw_build["b"] // 2, kw_build["b"] - 1})
+    cpu = {k: v.detach().cpu() for k, v in kw.items()}
+    ref_out, ref_lse = oracle.dense_mla_decode(cpu["q"], cpu["k_cache"], cpu["block_table"], cpu["cache_seqlens"], causal=causal,
+                                               sequences=seqs)
+    got, got_lse = out[seqs].float().cpu().numpy(), lse[seqs].cpu().numpy()
+    cd_out, cd_lse = oracle.cos_diff(got, ref_out[seqs]), oracle.cos_diff(got_lse, ref_lse[seqs])
+    rec = {"workload": name, **kw_build, "tokens": tokens, "ms_per_step": ms, "tokens_per_s": tokens / (ms / 1e3),
+           "tflops": meta["flops"] / (ms / 1e3) / 1e12, "steps": steps, "warmup": 3, "gpu_launches_per_step": 1,
+           "l2": f"{kw['k_cache'].numel() * 2 / 2**20:.0f} MiB cache read per step > 126 MiB L2",
+           "roofline": roofline_record(meta, ms / 1e3, name),
+           "parity": {"sequences": seqs, "cos_diff_out": cd_out, "cos_diff_lse": cd_lse,
+                      "max_abs_out": float(np.abs(got - ref_out[seqs]).max()),
+                      "within_gate": bool(cd_out < 8e-5 and cd_lse < 8e-5),
+                      "gate": "cos_diff < 8e-5 for out and lse (the reference's dense test)"}}
+    del kw, out, lse
+    torch.cuda.empty_cache()
+    return rec
 
 
 def run_dense_reference(a, kw_build):
@@ -1026,6 +1080,13 @@ def main():
                 except Exception as e:      # one broken configuration must not cost the whole line
                     others.append({"workload": name, "error": f"{type(e).__name__}: {e}"[:300]})
             line["other_configs"] = others
+            dense = []
+            for name in DENSE_CONFIGS:
+                try:
+                    dense.append(dense_config_record(name, dev))
+                except Exception as e:
+                    dense.append({"workload": name, "error": f"{type(e).__name__}: {e}"[:300]})
+            line["dense_configs"] = dense
         print(json.dumps(line))
     if world > 1:
         dist.barrier()
