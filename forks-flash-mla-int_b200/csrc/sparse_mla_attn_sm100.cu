@@ -151,6 +151,7 @@ struct KernelArgs {
                                   // slice of its heads at the end of its run
     StreamDev swa, extra;
     int T, H, head_blocks, balanced;
+    int hb_major;         // items are ordered head block first (item = hb * T + t) instead of token first: see schedule_and_launch
     float scale_log2;
     int q_tma;            // the Q tile is fetched with one TMA tensor copy through q_map (else cp.async)
     CUtensorMap q_map;    // 5-D view of q: {8 dims, 8 heads, 64 (dense: 72) dim groups, H/8 head groups, T}
@@ -510,7 +511,7 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatil
 
 // ------------------------------------------------------------------ work distribution
 // The grid is persistent: `gridDim.x` CTAs (at most one per SM) share the launch's work, which is the
-// list of items (token t, block of 64 heads hb), item = t * head_blocks + hb, each made of
+// list of items (token t, block of 64 heads hb), item = t * head_blocks + hb (or hb * T + t: `hb_major`), each made of
 // ceil(rows(t) / 128) tiles.  Two ways of sharing it:
 //   whole items (balanced == 0): CTA c takes items c, c + P, c + 2P, ...; every output is final.
 //   balanced tiles (balanced == 1): the tiles of all items, in item order, are cut into P equal
@@ -560,8 +561,13 @@ __device__ __forceinline__ bool iter_next(const KernelArgs &a, SegIter &it, Seg 
         bool &first = it.first;
         if (!a.balanced) {
             if (item >= a.T * a.head_blocks) return false;
-            s.t = item / a.head_blocks;
-            s.hb = item - s.t * a.head_blocks;
+            if (a.hb_major) {
+                s.hb = item / a.T;
+                s.t = item - s.hb * a.T;
+            } else {
+                s.t = item / a.head_blocks;
+                s.hb = item - s.t * a.head_blocks;
+            }
             token_rows(a, s.t, s.ns, s.n);
             s.tile0 = 0;
             s.ntl = (s.n + kTileRows - 1) / kTileRows;
@@ -590,7 +596,12 @@ __device__ __forceinline__ bool iter_next(const KernelArgs &a, SegIter &it, Seg 
         rem -= take;
         gpos += take;
         off = 0;
-        if (++hb == a.head_blocks) {
+        if (a.hb_major) {
+            if (++t == a.T) {
+                t = 0;
+                ++hb;
+            }
+        } else if (++hb == a.head_blocks) {
             hb = 0;
             ++t;
         }
@@ -628,7 +639,8 @@ __device__ bool make_schedule(const KernelArgs &a, int *scratch, SegIter &it, lo
         int ns = 0, n = 0;
         if (tid < a.T) token_rows(a, tid, ns, n);
         const int ntS = sched_tiles(n);
-        const long long v = tid < a.T ? static_cast<long long>(ntS) * a.head_blocks : 0;
+        const int per_token = a.hb_major ? 1 : a.head_blocks;      // items of a token that are neighbours in the order
+        const long long v = tid < a.T ? static_cast<long long>(ntS) * per_token : 0;
         long long incl = v;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
@@ -637,22 +649,25 @@ __device__ bool make_schedule(const KernelArgs &a, int *scratch, SegIter &it, lo
         }
         if (lane == 31) wsum[warp] = incl;
         __syncthreads();
-        long long before = 0, W = 0;
+        long long before = 0, W1 = 0;
         for (int w = 0; w < kNumWarps; ++w) {
             if (w < warp) before += wsum[w];
-            W += wsum[w];
+            W1 += wsum[w];
         }
+        const long long W = a.hb_major ? W1 * a.head_blocks : W1;
         const long long P = min(static_cast<long long>(gridDim.x), W);
         W_out = W;
         P_out = static_cast<int>(P);
         if (static_cast<long long>(blockIdx.x) >= P) return false;      // uniform
         const long long lo = range_begin(blockIdx.x, W, P), hi = range_begin(blockIdx.x + 1, W, P);
         const long long excl = before + incl - v;
-        if (tid < a.T && excl <= lo && lo < excl + v) {
-            const long long d = lo - excl;
+        const int hb_lo = a.hb_major ? static_cast<int>(lo / W1) : 0;   // head block first: W1 tiles per head block
+        const long long lo_in = lo - hb_lo * W1;
+        if (tid < a.T && excl <= lo_in && lo_in < excl + v) {
+            const long long d = lo_in - excl;
             found[0] = tid;
-            found[1] = static_cast<int>(d / ntS);                        // head block
-            found[2] = static_cast<int>(d - static_cast<long long>(found[1]) * ntS);   // first tile inside the item
+            found[1] = a.hb_major ? hb_lo : static_cast<int>(d / ntS);  // head block
+            found[2] = static_cast<int>(d - (a.hb_major ? 0ll : static_cast<long long>(found[1]) * ntS));   // first tile inside the item
         }
         __syncthreads();
         it.t = found[0];
@@ -683,6 +698,10 @@ __device__ bool make_schedule(const KernelArgs &a, int *scratch, SegIter &it, lo
     P_out = static_cast<int>(P);
     if (static_cast<long long>(blockIdx.x) >= P) return false;
     const long long lo = range_begin(blockIdx.x, W, P), hi = range_begin(blockIdx.x + 1, W, P);
+    const long long W1 = W / a.head_blocks;
+    const int hb_lo = a.hb_major ? static_cast<int>(lo / W1) : 0;
+    const long long lo_in = lo - hb_lo * W1;       // position inside the head block's run of tokens (head block first)
+    const int per_token = a.hb_major ? 1 : a.head_blocks;
 
     // pass 2: the token whose tiles contain global tile `lo`
     long long run = 0;
@@ -692,7 +711,7 @@ __device__ bool make_schedule(const KernelArgs &a, int *scratch, SegIter &it, lo
         if (t < a.T) {
             int ns, n;
             token_rows(a, t, ns, n);
-            v = static_cast<long long>(sched_tiles(n)) * a.head_blocks;
+            v = static_cast<long long>(sched_tiles(n)) * per_token;
         }
         long long incl = v;
 #pragma unroll
@@ -708,24 +727,24 @@ __device__ bool make_schedule(const KernelArgs &a, int *scratch, SegIter &it, lo
             total += wsum[w];
         }
         const long long excl = before + incl - v;
-        if (t < a.T && excl <= lo && lo < excl + v) {
+        if (t < a.T && excl <= lo_in && lo_in < excl + v) {
             found[0] = t;
             found[1] = static_cast<int>(excl & 0xFFFFFFFFll);
             found[2] = static_cast<int>(excl >> 32);
         }
         run += total;
         __syncthreads();
-        if (run > lo) break;     // uniform: every thread holds the same `run`
+        if (run > lo_in) break;     // uniform: every thread holds the same `run`
     }
     const int t0 = found[0];
     const long long excl0 = (static_cast<long long>(found[2]) << 32) | static_cast<unsigned int>(found[1]);
     int ns, n;
     token_rows(a, t0, ns, n);
     const int ntS = sched_tiles(n);
-    const long long d = lo - excl0;
+    const long long d = lo_in - excl0;
     it.t = t0;
-    it.hb = static_cast<int>(d / ntS);
-    it.off = static_cast<int>(d - static_cast<long long>(it.hb) * ntS);
+    it.hb = a.hb_major ? hb_lo : static_cast<int>(d / ntS);
+    it.off = static_cast<int>(d - (a.hb_major ? 0ll : static_cast<long long>(it.hb) * ntS));
     it.gpos = lo;
     it.rem = hi - lo;
     return true;
@@ -800,9 +819,11 @@ __device__ __forceinline__ void publish_segment(const KernelArgs &a, int *sched,
     }
     {   // warm the lens of the tokens the next calls will ask for (lane i: i + 1 items ahead)
         const long long ahead = a.balanced ? static_cast<long long>(it.t) + lane
+                                           : a.hb_major ? (static_cast<long long>(it.item) + static_cast<long long>(lane) * it.stride) % a.T
                                            : (static_cast<long long>(it.item) + static_cast<long long>(lane) * it.stride) / a.head_blocks;
         if (ahead < a.T) {
-            asm volatile("prefetch.global.L1 [%0];" ::"l"(a.swa.lens + ahead));
+            // dense paged MLA: lens are per sequence, a token is (sequence, query position)
+            asm volatile("prefetch.global.L1 [%0];" ::"l"(a.swa.lens + (a.dense_sq > 1 ? ahead / a.dense_sq : ahead)));
             if (a.extra.cache != nullptr) asm volatile("prefetch.global.L1 [%0];" ::"l"(a.extra.lens + ahead));
         }
     }
@@ -2037,6 +2058,11 @@ int schedule_and_launch(KernelArgs &a, int fmt, int num_splits, void *workspace,
     a.head_blocks = (a.H + 63) / 64;
     const long long items = static_cast<long long>(a.T) * a.head_blocks;
     if (items > 0x7FFFFFFFLL) return SMLA_ETOOBIG;
+    // Dense rows come from HBM (no reuse between tokens).  With several head blocks the items are ordered
+    // head block first: CTA c and CTA c + P / blocks then walk the same rows at the same time, one head block
+    // each, and the second reader finds them in L2 (token first, the blocks of a sequence ran one after
+    // the other in one CTA and read its rows from HBM once per block).
+    a.hb_major = (is_dense(fmt) && a.head_blocks > 1) ? 1 : 0;
     int sms = 0;
     int rc = sm_count_of_current_device(sms);
     if (rc != 0) return rc;
