@@ -543,8 +543,19 @@ __device__ __forceinline__ void token_rows(const KernelArgs &a, int t, int &ns, 
 }
 __device__ __forceinline__ int sched_tiles(int n) { return max(1, (n + kTileRows - 1) / kTileRows); }
 
+// Position u in the order the schedule walks the tokens -> token.  Identity, except for dense paged MLA with
+// several query positions per sequence: there the tokens are walked query position first (all sequences at
+// position 0, then at position 1, ...), so that the positions of one sequence, which read the same rows, are
+// handled by different CTAs at the same time and share the rows through L2 instead of reading them from HBM
+// one after the other.
+__device__ __forceinline__ int tok_of(const KernelArgs &a, int u) {
+    if (a.dense_sq <= 1) return u;
+    const int B = a.T / a.dense_sq, i = u / B;
+    return (u - i * B) * a.dense_sq + i;
+}
+
 struct SegIter {
-    int t, hb;          // next item
+    int t, hb;          // next item (t: position in the walking order, see tok_of)
     int off;            // first tile of that item still to do (balanced mode)
     long long gpos;     // global tile index of (t, hb, off) (balanced mode)
     long long rem;      // tiles left in this CTA's range (balanced mode)
@@ -563,10 +574,11 @@ __device__ __forceinline__ bool iter_next(const KernelArgs &a, SegIter &it, Seg 
             if (item >= a.T * a.head_blocks) return false;
             if (a.hb_major) {
                 s.hb = item / a.T;
-                s.t = item - s.hb * a.T;
+                s.t = tok_of(a, item - s.hb * a.T);
             } else {
-                s.t = item / a.head_blocks;
-                s.hb = item - s.t * a.head_blocks;
+                const int u = item / a.head_blocks;
+                s.hb = item - u * a.head_blocks;
+                s.t = tok_of(a, u);
             }
             token_rows(a, s.t, s.ns, s.n);
             s.tile0 = 0;
@@ -580,9 +592,9 @@ __device__ __forceinline__ bool iter_next(const KernelArgs &a, SegIter &it, Seg 
             return true;
         }
         if (rem <= 0) return false;
-        s.t = t;
+        s.t = tok_of(a, t);
         s.hb = hb;
-        token_rows(a, t, s.ns, s.n);
+        token_rows(a, s.t, s.ns, s.n);
         const int nt = (s.n + kTileRows - 1) / kTileRows;
         s.ntS = max(1, nt);
         const int take = static_cast<int>(min(static_cast<long long>(s.ntS - off), rem));
@@ -637,7 +649,7 @@ __device__ bool make_schedule(const KernelArgs &a, int *scratch, SegIter &it, lo
         // The usual case (the balanced schedule is chosen for few items): one token per thread, one
         // scan gives the total and every token's first global tile at once.
         int ns = 0, n = 0;
-        if (tid < a.T) token_rows(a, tid, ns, n);
+        if (tid < a.T) token_rows(a, tok_of(a, tid), ns, n);
         const int ntS = sched_tiles(n);
         const int per_token = a.hb_major ? 1 : a.head_blocks;      // items of a token that are neighbours in the order
         const long long v = tid < a.T ? static_cast<long long>(ntS) * per_token : 0;
@@ -710,7 +722,7 @@ __device__ bool make_schedule(const KernelArgs &a, int *scratch, SegIter &it, lo
         long long v = 0;
         if (t < a.T) {
             int ns, n;
-            token_rows(a, t, ns, n);
+            token_rows(a, tok_of(a, t), ns, n);
             v = static_cast<long long>(sched_tiles(n)) * per_token;
         }
         long long incl = v;
@@ -739,7 +751,7 @@ __device__ bool make_schedule(const KernelArgs &a, int *scratch, SegIter &it, lo
     const int t0 = found[0];
     const long long excl0 = (static_cast<long long>(found[2]) << 32) | static_cast<unsigned int>(found[1]);
     int ns, n;
-    token_rows(a, t0, ns, n);
+    token_rows(a, tok_of(a, t0), ns, n);
     const int ntS = sched_tiles(n);
     const long long d = lo_in - excl0;
     it.t = t0;
@@ -823,7 +835,7 @@ __device__ __forceinline__ void publish_segment(const KernelArgs &a, int *sched,
                                            : (static_cast<long long>(it.item) + static_cast<long long>(lane) * it.stride) / a.head_blocks;
         if (ahead < a.T) {
             // dense paged MLA: lens are per sequence, a token is (sequence, query position)
-            asm volatile("prefetch.global.L1 [%0];" ::"l"(a.swa.lens + (a.dense_sq > 1 ? ahead / a.dense_sq : ahead)));
+            asm volatile("prefetch.global.L1 [%0];" ::"l"(a.swa.lens + (a.dense_sq > 1 ? tok_of(a, static_cast<int>(ahead)) / a.dense_sq : ahead)));
             if (a.extra.cache != nullptr) asm volatile("prefetch.global.L1 [%0];" ::"l"(a.extra.lens + ahead));
         }
     }
