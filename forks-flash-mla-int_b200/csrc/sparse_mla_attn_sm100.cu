@@ -28,8 +28,15 @@
 // buffer chunk by chunk (128 dims), each chunk as soon as the previous tile's PV has released it;
 // (2) softmax -- warp w owns TMEM lanes 32*(w%4).. and head columns (N/4)*(w/4)..: S^T -> P^T with a
 // lazily moved reference max, running denominators, and the epilogue.  Warp 16
-// allocates TMEM and its lane 0 issues every tcgen05.mma; warp 17 fetches each item's Q tile (one TMA
-// tensor copy); warp 18 publishes the CTA's segments into a ring in shared memory.
+// allocates TMEM and issues every tcgen05.mma (warp-uniform code, one elected lane); warp 17 fetches
+// each item's Q tile (one TMA tensor copy); warp 18 publishes the CTA's segments into a ring in shared
+// memory.
+//
+// Dense paged MLA decode (the path behind flash_mla_with_kvcache: csrc/flash_api.cpp:159-322 of the
+// reference) is two more values of the format parameter: bf16 rows of 576 dims found through a block
+// table, scores over all 576 dims (the 64 RoPE dims of a tile in a fifth K piece that shares its memory
+// with P^T), values = the first 512, log-sum-exp output.  The rows are copied, not converted: by TMA from
+// warp 19 into 128-byte-swizzled slabs (kFmtBf16DenseTma), or with cp.async by the workers (kFmtBf16Dense).
 //
 // Every spin is time-bounded; a wait that runs out sets a bit in the device status word and the
 // CTA leaves through the normal teardown.
