@@ -1,4 +1,4 @@
-"""Token sharding for multi-GPU runs: every query token is independent (no cross-token reduction),
+"""Token (and, for dense calls, sequence) sharding for multi-GPU runs: every query token is independent (no cross-token reduction),
 so a batch splits into contiguous token ranges, one per rank, with the caches replicated (or
 batch-partitioned by the caller) and NO collective on the data path.  Outputs stay on the rank
 that owns the tokens; ``gather_outputs`` is a convenience for harnesses that want one tensor."""
@@ -32,6 +32,24 @@ def shard_tokens(kwargs: Dict[str, object], world_size: int, rank: int) -> Dict[
             if v.shape[0] != T:
                 raise ValueError(f"{k} has {v.shape[0]} rows, expected {T}")
             out[k] = v[a:b]
+    return out
+
+
+SEQUENCE_KEYS = ("q", "block_table", "cache_seqlens")
+
+
+def shard_sequences(kwargs: Dict[str, object], world_size: int, rank: int) -> Dict[str, object]:
+    """The same for a dense call (``flash_mla_with_kvcache``): q [b, s_q, h, d], block_table [b, pages] and
+    cache_seqlens [b] are cut to this rank's contiguous range of sequences; the paged cache is passed through
+    (replicated, or holding this rank's pages: the block table names them)."""
+    B = kwargs["q"].shape[0]
+    a, b = token_range(B, world_size, rank)
+    out = dict(kwargs)
+    for k in SEQUENCE_KEYS:
+        v = kwargs[k]
+        if v.shape[0] != B:
+            raise ValueError(f"{k} has {v.shape[0]} rows, expected {B}")
+        out[k] = v[a:b]
     return out
 
 

@@ -214,6 +214,19 @@ local = torch.from_numpy(oracle.sparse_mla_attention(mine["q"], K, mine["swa_ind
 allo = gather_outputs(local, T)
 assert allo.shape == (T, H, 512)
 assert np.array_equal(allo.numpy(), full), "sharded result differs from the unsharded one"
+# dense paged MLA: sequences shard the same way (block table and lengths with q, cache replicated)
+from flash_mla.sharding import shard_sequences
+g = torch.Generator().manual_seed(3)
+dkw = dict(q=torch.randn(5, 2, 4, 576, generator=g).to(torch.bfloat16),
+           k_cache=torch.randn(20, 16, 1, 576, generator=g).to(torch.bfloat16),
+           block_table=torch.randperm(20, generator=g).to(torch.int32).view(5, 4),
+           cache_seqlens=torch.tensor([3, 64, 17, 40, 2], dtype=torch.int32))
+dfull, dlse = oracle.dense_mla_decode(dkw["q"], dkw["k_cache"], dkw["block_table"], dkw["cache_seqlens"], causal=True)
+dm = shard_sequences(dkw, world, rank)
+da, db = token_range(5, world, rank)
+dloc, _ = oracle.dense_mla_decode(dm["q"], dm["k_cache"], dm["block_table"], dm["cache_seqlens"], causal=True)
+dall = gather_outputs(torch.from_numpy(dloc), 5)
+assert np.array_equal(dall.numpy(), dfull), "sharded dense result differs from the unsharded one"
 dist.barrier(); dist.destroy_process_group()
 print("rank", rank, "ok")
 '''
