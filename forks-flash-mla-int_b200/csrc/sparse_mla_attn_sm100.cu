@@ -158,7 +158,6 @@ struct KernelArgs {
                                   // slice of its heads at the end of its run
     StreamDev swa, extra;
     int T, H, head_blocks, balanced;
-    int hb_major;         // items are ordered head block first (item = hb * T + t) instead of token first: see schedule_and_launch
     float scale_log2;
     int q_tma;            // the Q tile is fetched with one TMA tensor copy through q_map (else cp.async)
     CUtensorMap q_map;    // 5-D view of q: {8 dims, 8 heads, 64 (dense: 72) dim groups, H/8 head groups, T}
@@ -170,6 +169,7 @@ struct KernelArgs {
     int dense_dims;       // 576, or 512 (no RoPE dims: the fifth K chunk and the last eight Q groups are zero-filled)
     CUtensorMap k_map;    // kFmtBf16DenseTma: 3-D view {576 dims, page rows, pages} of the cache, box {64, k_box_rows, 1}
     int k_box_rows;
+    int hb_major;         // items are ordered head block first (item = hb * T + t) instead of token first: see schedule_and_launch
 };
 
 template <int NPAD, bool DENSE = false>
@@ -538,15 +538,18 @@ struct Seg {
     int ntS;         // scheduled tiles of the item (max(1, tiles))
 };
 
+// DENSE is a template parameter throughout the scheduling code so that the sparse kernels carry none of the
+// dense bookkeeping (measured: as run-time branches it cost the sparse decode 1-2 %).
+template <bool DENSE>
 __device__ __forceinline__ void token_rows(const KernelArgs &a, int t, int &ns, int &n) {
-    if (a.dense_sq > 0) {     // dense paged MLA: all rows of the sequence, minus what the causal mask hides
+    if constexpr (DENSE) {     // dense paged MLA: all rows of the sequence, minus what the causal mask hides
         const int b = t / a.dense_sq, i = t - b * a.dense_sq;
         ns = n = max(__ldg(a.swa.lens + b) - (a.causal ? a.dense_sq - 1 - i : 0), 0);
-        return;
+    } else {
+        ns = min(max(__ldg(a.swa.lens + t), 0), a.swa.topk);
+        const int ne = (a.extra.cache != nullptr) ? min(max(__ldg(a.extra.lens + t), 0), a.extra.topk) : 0;
+        n = ns + ne;
     }
-    ns = min(max(__ldg(a.swa.lens + t), 0), a.swa.topk);
-    const int ne = (a.extra.cache != nullptr) ? min(max(__ldg(a.extra.lens + t), 0), a.extra.topk) : 0;
-    n = ns + ne;
 }
 __device__ __forceinline__ int sched_tiles(int n) { return max(1, (n + kTileRows - 1) / kTileRows); }
 
@@ -555,8 +558,9 @@ __device__ __forceinline__ int sched_tiles(int n) { return max(1, (n + kTileRows
 // position 0, then at position 1, ...), so that the positions of one sequence, which read the same rows, are
 // handled by different CTAs at the same time and share the rows through L2 instead of reading them from HBM
 // one after the other.
+template <bool DENSE>
 __device__ __forceinline__ int tok_of(const KernelArgs &a, int u) {
-    if (a.dense_sq <= 1) return u;
+    if (!DENSE || a.dense_sq <= 1) return u;
     const int B = a.T / a.dense_sq, i = u / B;
     return (u - i * B) * a.dense_sq + i;
 }
@@ -571,23 +575,25 @@ struct SegIter {
 
 };
 
+template <bool DENSE>
 __device__ __forceinline__ bool iter_next(const KernelArgs &a, SegIter &it, Seg &s) {
     {
+        const bool hb_major = DENSE && a.hb_major != 0;
         int &t = it.t, &hb = it.hb, &off = it.off, &item = it.item;
         const int stride = it.stride;
         long long &gpos = it.gpos, &rem = it.rem;
         bool &first = it.first;
         if (!a.balanced) {
             if (item >= a.T * a.head_blocks) return false;
-            if (a.hb_major) {
+            if (hb_major) {
                 s.hb = item / a.T;
-                s.t = tok_of(a, item - s.hb * a.T);
+                s.t = tok_of<DENSE>(a, item - s.hb * a.T);
             } else {
                 const int u = item / a.head_blocks;
                 s.hb = item - u * a.head_blocks;
-                s.t = tok_of(a, u);
+                s.t = tok_of<DENSE>(a, u);
             }
-            token_rows(a, s.t, s.ns, s.n);
+            token_rows<DENSE>(a, s.t, s.ns, s.n);
             s.tile0 = 0;
             s.ntl = (s.n + kTileRows - 1) / kTileRows;
             s.ntS = max(1, s.ntl);
@@ -599,9 +605,9 @@ __device__ __forceinline__ bool iter_next(const KernelArgs &a, SegIter &it, Seg 
             return true;
         }
         if (rem <= 0) return false;
-        s.t = tok_of(a, t);
+        s.t = tok_of<DENSE>(a, t);
         s.hb = hb;
-        token_rows(a, s.t, s.ns, s.n);
+        token_rows<DENSE>(a, s.t, s.ns, s.n);
         const int nt = (s.n + kTileRows - 1) / kTileRows;
         s.ntS = max(1, nt);
         const int take = static_cast<int>(min(static_cast<long long>(s.ntS - off), rem));
@@ -615,7 +621,7 @@ __device__ __forceinline__ bool iter_next(const KernelArgs &a, SegIter &it, Seg 
         rem -= take;
         gpos += take;
         off = 0;
-        if (a.hb_major) {
+        if (hb_major) {
             if (++t == a.T) {
                 t = 0;
                 ++hb;
@@ -637,8 +643,10 @@ __device__ __forceinline__ int cta_of_tile(long long x, long long W, long long P
 // Every thread of the CTA calls this; returns false when the CTA has nothing to do.  `scratch` is a
 // shared-memory array of at least 24 ints.  `W_out` / `P_out`: total scheduled tiles and the number
 // of CTAs that share them (needed later for the merge descriptors).
+template <bool DENSE>
 __device__ bool make_schedule(const KernelArgs &a, int *scratch, SegIter &it, long long &W_out, int &P_out) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const bool hb_major = DENSE && a.hb_major != 0;
     it.first = true;
     it.off = 0;
     it.gpos = 0;
@@ -656,9 +664,9 @@ __device__ bool make_schedule(const KernelArgs &a, int *scratch, SegIter &it, lo
         // The usual case (the balanced schedule is chosen for few items): one token per thread, one
         // scan gives the total and every token's first global tile at once.
         int ns = 0, n = 0;
-        if (tid < a.T) token_rows(a, tok_of(a, tid), ns, n);
+        if (tid < a.T) token_rows<DENSE>(a, tok_of<DENSE>(a, tid), ns, n);
         const int ntS = sched_tiles(n);
-        const int per_token = a.hb_major ? 1 : a.head_blocks;      // items of a token that are neighbours in the order
+        const int per_token = hb_major ? 1 : a.head_blocks;      // items of a token that are neighbours in the order
         const long long v = tid < a.T ? static_cast<long long>(ntS) * per_token : 0;
         long long incl = v;
 #pragma unroll
@@ -673,20 +681,20 @@ __device__ bool make_schedule(const KernelArgs &a, int *scratch, SegIter &it, lo
             if (w < warp) before += wsum[w];
             W1 += wsum[w];
         }
-        const long long W = a.hb_major ? W1 * a.head_blocks : W1;
+        const long long W = hb_major ? W1 * a.head_blocks : W1;
         const long long P = min(static_cast<long long>(gridDim.x), W);
         W_out = W;
         P_out = static_cast<int>(P);
         if (static_cast<long long>(blockIdx.x) >= P) return false;      // uniform
         const long long lo = range_begin(blockIdx.x, W, P), hi = range_begin(blockIdx.x + 1, W, P);
         const long long excl = before + incl - v;
-        const int hb_lo = a.hb_major ? static_cast<int>(lo / W1) : 0;   // head block first: W1 tiles per head block
+        const int hb_lo = hb_major ? static_cast<int>(lo / W1) : 0;   // head block first: W1 tiles per head block
         const long long lo_in = lo - hb_lo * W1;
         if (tid < a.T && excl <= lo_in && lo_in < excl + v) {
             const long long d = lo_in - excl;
             found[0] = tid;
-            found[1] = a.hb_major ? hb_lo : static_cast<int>(d / ntS);  // head block
-            found[2] = static_cast<int>(d - (a.hb_major ? 0ll : static_cast<long long>(found[1]) * ntS));   // first tile inside the item
+            found[1] = hb_major ? hb_lo : static_cast<int>(d / ntS);  // head block
+            found[2] = static_cast<int>(d - (hb_major ? 0ll : static_cast<long long>(found[1]) * ntS));   // first tile inside the item
         }
         __syncthreads();
         it.t = found[0];
@@ -701,7 +709,7 @@ __device__ bool make_schedule(const KernelArgs &a, int *scratch, SegIter &it, lo
     long long mine = 0;
     for (int t = tid; t < a.T; t += kThreads) {
         int ns, n;
-        token_rows(a, t, ns, n);
+        token_rows<DENSE>(a, t, ns, n);
         mine += sched_tiles(n);
     }
 #pragma unroll
@@ -718,9 +726,9 @@ __device__ bool make_schedule(const KernelArgs &a, int *scratch, SegIter &it, lo
     if (static_cast<long long>(blockIdx.x) >= P) return false;
     const long long lo = range_begin(blockIdx.x, W, P), hi = range_begin(blockIdx.x + 1, W, P);
     const long long W1 = W / a.head_blocks;
-    const int hb_lo = a.hb_major ? static_cast<int>(lo / W1) : 0;
+    const int hb_lo = hb_major ? static_cast<int>(lo / W1) : 0;
     const long long lo_in = lo - hb_lo * W1;       // position inside the head block's run of tokens (head block first)
-    const int per_token = a.hb_major ? 1 : a.head_blocks;
+    const int per_token = hb_major ? 1 : a.head_blocks;
 
     // pass 2: the token whose tiles contain global tile `lo`
     long long run = 0;
@@ -729,7 +737,7 @@ __device__ bool make_schedule(const KernelArgs &a, int *scratch, SegIter &it, lo
         long long v = 0;
         if (t < a.T) {
             int ns, n;
-            token_rows(a, tok_of(a, t), ns, n);
+            token_rows<DENSE>(a, tok_of<DENSE>(a, t), ns, n);
             v = static_cast<long long>(sched_tiles(n)) * per_token;
         }
         long long incl = v;
@@ -758,12 +766,12 @@ __device__ bool make_schedule(const KernelArgs &a, int *scratch, SegIter &it, lo
     const int t0 = found[0];
     const long long excl0 = (static_cast<long long>(found[2]) << 32) | static_cast<unsigned int>(found[1]);
     int ns, n;
-    token_rows(a, tok_of(a, t0), ns, n);
+    token_rows<DENSE>(a, tok_of<DENSE>(a, t0), ns, n);
     const int ntS = sched_tiles(n);
     const long long d = lo_in - excl0;
     it.t = t0;
-    it.hb = a.hb_major ? hb_lo : static_cast<int>(d / ntS);
-    it.off = static_cast<int>(d - (a.hb_major ? 0ll : static_cast<long long>(it.hb) * ntS));
+    it.hb = hb_major ? hb_lo : static_cast<int>(d / ntS);
+    it.off = static_cast<int>(d - (hb_major ? 0ll : static_cast<long long>(it.hb) * ntS));
     it.gpos = lo;
     it.rem = hi - lo;
     return true;
@@ -799,9 +807,10 @@ __device__ __forceinline__ void load_iter(const int *p, SegIter &it, long long &
 }
 
 // An item without rows: its output is zero (the reference's "no selected slot" case).
+template <bool DENSE>
 __device__ __forceinline__ void zero_item(const KernelArgs &a, const Seg &s, int tid, int nthreads) {
     const int h0 = s.hb * 64, hv = min(64, a.H - h0);
-    if (a.lse != nullptr)
+    if (DENSE && a.lse != nullptr)
         for (int h = tid; h < hv; h += nthreads) *lse_ptr(a, s.t, h0 + h) = -INFINITY;
     for (int i = tid; i < hv * (kD / 8); i += nthreads) {
         const int h = i / (kD / 8), d8 = i - h * (kD / 8);
@@ -812,21 +821,23 @@ __device__ __forceinline__ void zero_item(const KernelArgs &a, const Seg &s, int
 
 // One warp (all lanes, uniformly): continue the iterator to the next segment that has tiles, zeroing the
 // outputs of items without rows on the way, and publish it as segment `k` (records are published in order).
+template <bool DENSE>
 __device__ __forceinline__ void publish_segment(const KernelArgs &a, int *sched, int k, int lane) {
+    const bool hb_major = DENSE && a.hb_major != 0;
     SegIter it;
     long long W;
     load_iter(sched + kSchedIter, it, W);
     const int P = sched[kSchedP];
     Seg s = {};
     bool ok = false;
-    while (iter_next(a, it, s)) {
+    while (iter_next<DENSE>(a, it, s)) {
         if (s.ntl > 0) {
             ok = true;
             break;
         }
-        zero_item(a, s, lane, 32);
+        zero_item<DENSE>(a, s, lane, 32);
     }
-    if (ok && lane < 5 && a.dense_sq == 0) {
+    if (!DENSE && ok && lane < 5) {
         // Warm L2 (and the TLB) with the slot ids of the segment's first tile: nobody has touched that
         // token's index row yet, and the workers need the ids in the last tile of the segment before,
         // to issue the gather.  Records are published three segments ahead, so the lines have arrived by then.
@@ -838,11 +849,11 @@ __device__ __forceinline__ void publish_segment(const KernelArgs &a, int *sched,
     }
     {   // warm the lens of the tokens the next calls will ask for (lane i: i + 1 items ahead)
         const long long ahead = a.balanced ? static_cast<long long>(it.t) + lane
-                                           : a.hb_major ? (static_cast<long long>(it.item) + static_cast<long long>(lane) * it.stride) % a.T
+                                           : hb_major ? (static_cast<long long>(it.item) + static_cast<long long>(lane) * it.stride) % a.T
                                            : (static_cast<long long>(it.item) + static_cast<long long>(lane) * it.stride) / a.head_blocks;
         if (ahead < a.T) {
             // dense paged MLA: lens are per sequence, a token is (sequence, query position)
-            asm volatile("prefetch.global.L1 [%0];" ::"l"(a.swa.lens + (a.dense_sq > 1 ? tok_of(a, static_cast<int>(ahead)) / a.dense_sq : ahead)));
+            asm volatile("prefetch.global.L1 [%0];" ::"l"(a.swa.lens + (DENSE && a.dense_sq > 1 ? tok_of<DENSE>(a, static_cast<int>(ahead)) / a.dense_sq : ahead)));
             if (a.extra.cache != nullptr) asm volatile("prefetch.global.L1 [%0];" ::"l"(a.extra.lens + ahead));
         }
     }
@@ -1172,7 +1183,7 @@ __device__ __forceinline__ void merge_head_slices(const KernelArgs &a, uint8_t *
             const float sink_l2 = a.sink ? a.sink[h0 + hl] * kLog2e : -INFINITY;
             merge_head(a.part_o, a.part_ml, slot_of, S, NPAD, hl, sink_l2,
                        a.out + static_cast<long long>(t) * a.o_ts + static_cast<long long>(h0 + hl) * a.o_hs, lane,
-                       a.lse != nullptr ? lse_ptr(a, t, h0 + hl) : nullptr);
+                       (DENSE && a.lse != nullptr) ? lse_ptr(a, t, h0 + hl) : nullptr);
         }
     }
 }
@@ -1288,14 +1299,14 @@ __device__ __forceinline__ void scheduler_role(const KernelArgs &a, uint8_t *sme
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::kAbort);
     const uint32_t bars = smem_u32(smem + L::kBars);
     int *sched = reinterpret_cast<int *>(smem + L::kSched);
-    for (int k = 1; k < 5; ++k) publish_segment(a, sched, k, lane);
+    for (int k = 1; k < 5; ++k) publish_segment<DENSE>(a, sched, k, lane);
     int gt = 0;
     for (int s = 0;; ++s) {
         const volatile int *rec = sched + kSchedRec + 12 * (s % 5);
         if ((rec[7] & kSegValid) == 0) break;
         const int ntl = rec[5];
         if (!wait_tiles(sched, gt + 1, abort_flag, lane)) return;      // first tile of segment s scored
-        if (s >= 2) publish_segment(a, sched, s + 3, lane);
+        if (s >= 2) publish_segment<DENSE>(a, sched, s + 3, lane);
         gt += ntl;
     }
 }
@@ -1402,12 +1413,12 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
                     wk_s[k * NPAD + tid] = w;
                 }
                 const float inv = 1.0f / denom;
-                if (a.lse != nullptr && tid < hvalid) *lse_ptr(a, t, h0 + tid) = (M + log2f(denom)) * kLn2;
+                if (is_dense(FMT) && a.lse != nullptr && tid < hvalid) *lse_ptr(a, t, h0 + tid) = (M + log2f(denom)) * kLn2;
                 alpha_s[tid] = w_own * inv;
                 for (int k = 0; k < others; ++k) wk_s[k * NPAD + tid] *= inv;
             } else if (direct) {
                 if (a.sink != nullptr && tid < hvalid) l += fast_exp2(a.sink[h0 + tid] * kLog2e - m_s[tid]);
-                if (a.lse != nullptr && tid < hvalid) *lse_ptr(a, t, h0 + tid) = (m_s[tid] + log2f(l)) * kLn2;
+                if (is_dense(FMT) && a.lse != nullptr && tid < hvalid) *lse_ptr(a, t, h0 + tid) = (m_s[tid] + log2f(l)) * kLn2;
                 alpha_s[tid] = 1.0f / l;
             } else if (tid < hvalid) {
                 float *ml = a.part_ml + (static_cast<long long>(slot) * NPAD + tid) * 2;
@@ -1809,7 +1820,7 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
 // ------------------------------------------------------------------ the kernel
 template <int FMT, int NPAD>
 __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const __grid_constant__ KernelArgs a) {
-    extern __shared__ __align__(1024) uint8_t smem[];
+    extern __shared__ __align__(FMT == kFmtBf16DenseTma ? 1024 : 128) uint8_t smem[];
     using L = Smem<NPAD, is_dense(FMT)>;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if constexpr (FMT == kFmtBf16DenseTma) {
@@ -1829,7 +1840,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const __gri
         SegIter iter;
         long long W;
         int P;
-        if (!make_schedule(a, sched + kSchedScan, iter, W, P)) return;
+        if (!make_schedule<is_dense(FMT)>(a, sched + kSchedScan, iter, W, P)) return;
         if (tid == 0) {
             store_iter(sched + kSchedIter, iter, W);
             sched[kSchedP] = P;
@@ -1837,7 +1848,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const __gri
     }
     __syncthreads();
     // ---- set-up, three things side by side: first segment record, barriers, tensor memory
-    if (warp == 0) publish_segment(a, sched, 0, lane);      // sets the published count to 1
+    if (warp == 0) publish_segment<is_dense(FMT)>(a, sched, 0, lane);      // sets the published count to 1
     if (tid == 32) {
         const uint32_t bars = smem_u32(smem + L::kBars);
         for (int c = 0; c < 4; ++c) mbar_init(bars + (kBarReady + c) * 8, kWorkerWarps);
@@ -1847,7 +1858,9 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const __gri
         mbar_init(bars + kBarO * 8, 1);
         mbar_init(bars + kBarOFree * 8, kWorkerWarps);
         mbar_init(bars + kBarQ * 8, a.q_tma ? 1 : kQLoadWarps);
-        for (int c = 0; c < 4; ++c) mbar_init(bars + (kBarLand + c) * 8, 1);
+        if constexpr (FMT == kFmtBf16DenseTma) {
+            for (int c = 0; c < 4; ++c) mbar_init(bars + (kBarLand + c) * 8, 1);
+        }
         *reinterpret_cast<volatile int *>(smem + L::kAbort) = 0;
         sched[kSchedTiles] = 0;
         mbar_init_fence();
