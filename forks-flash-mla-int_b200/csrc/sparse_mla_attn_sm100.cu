@@ -1368,46 +1368,83 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
         const bool direct = (pg[7] & kSegComplete) != 0 || owner;
         const int others = owner ? pg[8] - static_cast<int>(blockIdx.x) : 0;
         float *wk_s = reinterpret_cast<float *>(smem + L::kK);     // [others][NPAD] weights (the K buffer is idle: last segment)
+        // What the merge needs from OTHER CTAs does not depend on this CTA's last PV, which is still running
+        // when the final epilogue starts: the flags are checked and the first loads are issued before the
+        // wait for the accumulators ({max, denominator} of up to four other segments, and the first other
+        // segment's rows of round 0), so that their latency overlaps that PV.
+        constexpr int kEarly = 4;
+        float pv[kFinal ? 4 : 1][HR];
+        float2 e_early[kFinal ? kEarly : 1];
+        auto load_pv = [&](int r) {
+            const float *src = a.part_o + (static_cast<long long>(2 * (blockIdx.x + 1)) * NPAD + col0 + r * HR) * kD + q * 32 + lane;
+#pragma unroll
+            for (int c = 0; c < (kFinal ? 4 : 1); ++c)
+#pragma unroll
+                for (int j = 0; j < HR; ++j) pv[c][j] = __ldcg(src + c * 128 + j * kD);
+        };
+        if constexpr (kFinal) {
+            if (owner) {
+                if (warp == 0) {
+                    // The others wrote their partials at the start of their runs (or, for an item spread over
+                    // three or more CTAs, finish about now): wait, time-bounded, for their flags.
+                    bool ok = true;
+                    for (int k = lane; k < others; k += 32) {
+                        const volatile unsigned long long *f = a.flags + 2 * (static_cast<int>(blockIdx.x) + 1 + k);
+                        if (*f != a.tag) {
+                            const uint64_t t0 = globaltimer_ns();
+                            while (*f != a.tag) {
+                                __nanosleep(200);
+                                if (*abort_flag != 0 || globaltimer_ns() - t0 > kWaitLimitNs) {
+                                    ok = false;
+                                    break;
+                                }
+                            }
+                        }
+                    }
+                    if (!__all_sync(0xffffffffu, ok) && lane == 0) give_up(abort_flag, kStatusEpilogueWait);
+                    __threadfence();
+                }
+                named_bar_sync(kAllWorkersBar, kWorkerThreads);
+                if (tid < NPAD) {
+#pragma unroll
+                    for (int k = 0; k < kEarly; ++k)
+                        if (k < others)
+                            e_early[k] = __ldcg(reinterpret_cast<const float2 *>(a.part_ml) +
+                                                static_cast<long long>(2 * (blockIdx.x + 1 + k)) * NPAD + tid);
+                }
+                if constexpr (!is_dense(FMT)) load_pv(0);
+            }
+        }
         warp_wait(bars + kBarO * 8, parity, abort_flag, lane, kStatusEpilogueWait);
         tc_fence_after_sync();
         store_col_partial<CW>(red + q * NPAD + col0, lacc, lane);
         lacc = 0.0f;
-        if (owner && warp == 0) {
-            // The others wrote their partials at the start of their runs (or, for an item spread over
-            // three or more CTAs, finish about now): wait, time-bounded, for their flags.
-            bool ok = true;
-            for (int k = lane; k < others; k += 32) {
-                const volatile unsigned long long *f = a.flags + 2 * (static_cast<int>(blockIdx.x) + 1 + k);
-                if (*f != a.tag) {
-                    const uint64_t t0 = globaltimer_ns();
-                    while (*f != a.tag) {
-                        __nanosleep(200);
-                        if (*abort_flag != 0 || globaltimer_ns() - t0 > kWaitLimitNs) {
-                            ok = false;
-                            break;
-                        }
-                    }
-                }
-            }
-            if (!__all_sync(0xffffffffu, ok) && lane == 0) give_up(abort_flag, kStatusEpilogueWait);
-            __threadfence();
-        }
         named_bar_sync(kAllWorkersBar, kWorkerThreads);
         if (tid < NPAD) {
             float l = (red[tid] + red[NPAD + tid]) + (red[2 * NPAD + tid] + red[3 * NPAD + tid]);
             if (owner) {
                 const float sink_l2 = (a.sink != nullptr && tid < hvalid) ? a.sink[h0 + tid] * kLog2e : -INFINITY;
                 float M = fmaxf(m_s[tid], sink_l2);
+                auto ml_of = [&](int k) {
+                    if constexpr (kFinal) {
+                        if (k < kEarly) {
+                            float2 e = e_early[0];
+#pragma unroll
+                            for (int u = 1; u < kEarly; ++u)
+                                if (k == u) e = e_early[u];
+                            return e;
+                        }
+                    }
+                    return __ldcg(reinterpret_cast<const float2 *>(a.part_ml) + static_cast<long long>(2 * (blockIdx.x + 1 + k)) * NPAD + tid);
+                };
                 for (int k = 0; k < others; ++k) {
-                    const float2 e = __ldcg(reinterpret_cast<const float2 *>(a.part_ml) +
-                                            static_cast<long long>(2 * (blockIdx.x + 1 + k)) * NPAD + tid);
+                    const float2 e = ml_of(k);
                     if (e.y > 0.0f) M = fmaxf(M, e.x);
                 }
                 const float w_own = fast_exp2(m_s[tid] - M);
                 float denom = w_own * l + fast_exp2(sink_l2 - M);
                 for (int k = 0; k < others; ++k) {
-                    const float2 e = __ldcg(reinterpret_cast<const float2 *>(a.part_ml) +
-                                            static_cast<long long>(2 * (blockIdx.x + 1 + k)) * NPAD + tid);
+                    const float2 e = ml_of(k);
                     const float w = e.y > 0.0f ? fast_exp2(e.x - M) : 0.0f;
                     denom += w * e.y;
                     wk_s[k * NPAD + tid] = w;
@@ -1468,19 +1505,9 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
                 __nv_bfloat16 *orow = a.out + static_cast<long long>(t) * a.o_ts + static_cast<long long>(h0 + col0) * a.o_hs;
     #pragma unroll 1
                 for (int r = 0; r < CW / HR; ++r) {
-                    // Owner: the first other segment's rows of this round are fetched for all four chunks at
-                    // once (this is the CTA's last epilogue: the gather registers are free), so that their
-                    // latency is paid once per round and not once per chunk.
-                    float pv[kFinal ? 4 : 1][HR];
-                    if constexpr (kFinal) {
-                        if (owner) {
-                            const float *src = a.part_o + (static_cast<long long>(2 * (blockIdx.x + 1)) * NPAD + col0 + r * HR) * kD + gtid;
-    #pragma unroll
-                            for (int c = 0; c < 4; ++c)
-    #pragma unroll
-                                for (int j = 0; j < HR; ++j) pv[c][j] = __ldcg(src + c * 128 + j * kD);
-                        }
-                    }
+                    // Owner: `pv` holds the first other segment's rows of this round for all four chunks (this is
+                    // the CTA's last epilogue: the gather registers are free), fetched a round ahead -- round 0
+                    // before the wait for the accumulators -- so that their latency is never waited for.
     #pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         uint32_t o[HR];
@@ -1506,6 +1533,9 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
                             const __nv_bfloat16 v = __float2bfloat16_rn(val[j]);
                             asm volatile("st.shared.u16 [%0], %1;" ::"r"(dst + j * 1024), "h"(*reinterpret_cast<const uint16_t *>(&v)) : "memory");
                         }
+                    }
+                    if constexpr (kFinal) {
+                        if (owner && r + 1 < CW / HR) load_pv(r + 1);
                     }
                     named_bar_sync(group_bar, 128);
     #pragma unroll
