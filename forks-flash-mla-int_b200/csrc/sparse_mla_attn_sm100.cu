@@ -329,10 +329,12 @@ __device__ __forceinline__ void store_col_partial(float *dst_cols, float v, int 
 template <int N> struct TmemIO;
 template <> struct TmemIO<4> {
     static __device__ __forceinline__ void ld(uint32_t a, uint32_t (&r)[4]) { tmem_ld_x4(a, r); }
+    static __device__ __forceinline__ void ld2(uint32_t a, uint32_t b, uint32_t (&r)[4], uint32_t (&t)[4]) { tmem_ld_x4_pair(a, b, r, t); }
     static __device__ __forceinline__ void st(uint32_t a, const uint32_t (&r)[4]) { tmem_st_x4(a, r); }
 };
 template <> struct TmemIO<8> {
     static __device__ __forceinline__ void ld(uint32_t a, uint32_t (&r)[8]) { tmem_ld_x8(a, r); }
+    static __device__ __forceinline__ void ld2(uint32_t a, uint32_t b, uint32_t (&r)[8], uint32_t (&t)[8]) { tmem_ld_x8_pair(a, b, r, t); }
     static __device__ __forceinline__ void st(uint32_t a, const uint32_t (&r)[8]) { tmem_st_x8(a, r); }
 };
 template <> struct TmemIO<16> {
@@ -1508,10 +1510,13 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
                     // Owner: `pv` holds the first other segment's rows of this round for all four chunks (this is
                     // the CTA's last epilogue: the gather registers are free), fetched a round ahead -- round 0
                     // before the wait for the accumulators -- so that their latency is never waited for.
+                    uint32_t o2[2][HR];      // two chunks per tensor-memory round trip
     #pragma unroll
                     for (int c = 0; c < 4; ++c) {
-                        uint32_t o[HR];
-                        TmemIO<HR>::ld(tmem_lane + kTmemOCol + c * NPAD + col0 + r * HR, o);
+                        if ((c & 1) == 0)
+                            TmemIO<HR>::ld2(tmem_lane + kTmemOCol + c * NPAD + col0 + r * HR,
+                                            tmem_lane + kTmemOCol + (c + 1) * NPAD + col0 + r * HR, o2[0], o2[1]);
+                        const uint32_t (&o)[HR] = o2[c & 1];
                         const uint32_t dst = stage + (c * 128 + gtid) * 2;
                         float val[HR];
     #pragma unroll
