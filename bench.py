@@ -62,6 +62,7 @@ WORKLOADS = {
     "dense_bf16_decode_b128_s4096_h128": ("dense", dict(b=128, s_q=1, mean_sk=4096, h_q=128, varlen=False)),
     "dense_bf16_decode_b128_s4096_h16": ("dense", dict(b=128, s_q=1, mean_sk=4096, h_q=16, varlen=False)),
     "dense_bf16_decode_b128_s8192_h64_sq2_varlen": ("dense", dict(b=128, s_q=2, mean_sk=8192, h_q=64, varlen=True)),
+    "dense_bf16_decode_b128_s4096_h16_sq2": ("dense", dict(b=128, s_q=2, mean_sk=4096, h_q=16, varlen=False)),
     # cache writers (the step before the attention calls): 2^20 new bf16 latent rows scattered into a paged cache
     "write_int8_cache_rows1M": ("write_int8", dict(rows=1 << 20, block_size=64)),
     "write_fp8_cache_rows1M": ("write_fp8", dict(rows=1 << 20, block_size=64)),
@@ -79,7 +80,7 @@ OTHER_CONFIGS = ([f"dsv4_int8_decode_T{t}_H{h}" for h in (64, 128) for t in (1, 
 
 # dense paged MLA decode (flash_mla_with_kvcache), measured next to the headline as well
 DENSE_CONFIGS = ["dense_bf16_decode_b128_s4096_h128", "dense_bf16_decode_b128_s4096_h16",
-                 "dense_bf16_decode_b128_s8192_h64_sq2_varlen"]
+                 "dense_bf16_decode_b128_s8192_h64_sq2_varlen", "dense_bf16_decode_b128_s4096_h16_sq2"]
 
 
 def measured_peaks():

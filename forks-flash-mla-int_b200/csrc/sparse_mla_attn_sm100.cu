@@ -169,6 +169,11 @@ struct KernelArgs {
     int dense_dims;       // 576, or 512 (no RoPE dims: the fifth K chunk and the last eight Q groups are zero-filled)
     CUtensorMap k_map;    // kFmtBf16DenseTma: 3-D view {576 dims, page rows, pages} of the cache, box {64, k_box_rows, 1}
     int k_box_rows;
+    // Dense paged MLA with several query positions and few heads (fold_sq * fold_h <= 64): the positions of a
+    // sequence are folded into the head dimension, column i * fold_h + h = (query position i, head h), so that
+    // one item reads the sequence's rows once for all positions.  T, H, q_ts, o_ts describe the folded problem
+    // (dense_sq == 1); with fold_causal the columns of position i see fold_sq - 1 - i rows less.
+    int fold_sq, fold_h, fold_causal;
     int hb_major;         // items are ordered head block first (item = hb * T + t) instead of token first: see schedule_and_launch
 };
 
@@ -203,6 +208,10 @@ struct Smem {
 constexpr float kLn2 = 0.6931471805599453f;
 // Where the log-sum-exp of (token t, head h) goes (dense paged MLA: [sequence, head, query position]).
 __device__ __forceinline__ float *lse_ptr(const KernelArgs &a, int t, int h) {
+    if (a.fold_sq > 1) {      // folded query positions: column h = position * fold_h + head, token t = sequence
+        const int i = h / a.fold_h;
+        return a.lse + (static_cast<long long>(t) * a.fold_h + (h - i * a.fold_h)) * a.fold_sq + i;
+    }
     const int b = t / a.dense_sq, i = t - b * a.dense_sq;
     return a.lse + (static_cast<long long>(b) * a.H + h) * a.dense_sq + i;
 }
@@ -1451,14 +1460,14 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
                     denom += w * e.y;
                     wk_s[k * NPAD + tid] = w;
                 }
-                const float inv = 1.0f / denom;
+                const float inv = (!is_dense(FMT) || denom > 0.0f) ? 1.0f / denom : 0.0f;
                 if (is_dense(FMT) && a.lse != nullptr && tid < hvalid) *lse_ptr(a, t, h0 + tid) = (M + log2f(denom)) * kLn2;
                 alpha_s[tid] = w_own * inv;
                 for (int k = 0; k < others; ++k) wk_s[k * NPAD + tid] *= inv;
             } else if (direct) {
                 if (a.sink != nullptr && tid < hvalid) l += fast_exp2(a.sink[h0 + tid] * kLog2e - m_s[tid]);
                 if (is_dense(FMT) && a.lse != nullptr && tid < hvalid) *lse_ptr(a, t, h0 + tid) = (m_s[tid] + log2f(l)) * kLn2;
-                alpha_s[tid] = 1.0f / l;
+                alpha_s[tid] = (!is_dense(FMT) || l > 0.0f) ? 1.0f / l : 0.0f;
             } else if (tid < hvalid) {
                 float *ml = a.part_ml + (static_cast<long long>(slot) * NPAD + tid) * 2;
                 ml[0] = m_s[tid];
@@ -1744,7 +1753,9 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
             warp_wait(bars + kBarS * 8, gt & 1, abort_flag, lane, kStatusSoftmaxWait);
             tc_fence_after_sync();
             // sm = S^T * scale - m, with m read once per tile (the same for all rows).
-            const bool row_valid = row < rows_left;
+            // (dense, folded query positions: the columns of this warp belong to one position, which the causal
+            // mask lets see fewer of the sequence's last rows)
+            const bool row_valid = row < rows_left - ((is_dense(FMT) && a.fold_causal) ? a.fold_sq - 1 - col0 / a.fold_h : 0);
             float sm[CW];
             bool need = first_tile;
             {
@@ -1783,7 +1794,8 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
                     // The first tile sets m outright (only the sink, if it counts here, holds it up);
                     // nothing has been accumulated yet, so there is nothing to rescale.
                     const bool sink_here = (sg[7] & kSegComplete) != 0 && a.sink != nullptr;
-                    const bool up = first_tile ? (!sink_here || tm > m_old) : tm > m_old + thr_s[col];
+                    bool up = first_tile ? (!sink_here || tm > m_old) : tm > m_old + thr_s[col];
+                    if (is_dense(FMT) && tm == -INFINITY) up = false;     // folded positions: no row of this tile is visible to the column
                     const float m_new = up ? tm + kRefHeadroom : m_old;
                     alpha_s[col] = (up && !first_tile) ? fast_exp2(m_old - m_new) : 1.0f;
                     shift_s[col] = m_old - m_new;
@@ -1962,7 +1974,7 @@ __global__ void __launch_bounds__(128) sparse_mla_combine_kernel(const float *__
                                                                  const float *__restrict__ sink,
                                                                  __nv_bfloat16 *__restrict__ out, long long o_ts,
                                                                  long long o_hs, int head_blocks, int npad,
-                                                                 float *__restrict__ lse, int num_heads, int dense_sq) {
+                                                                 float *__restrict__ lse, int num_heads, int dense_sq, int fold_sq, int fold_h) {
     const int lane = threadIdx.x & 31;
     const int c = blockIdx.x;
     const int4 d = desc[c];
@@ -1971,9 +1983,14 @@ __global__ void __launch_bounds__(128) sparse_mla_combine_kernel(const float *__
     const int t = d.x / head_blocks, h = (d.x - t * head_blocks) * 64 + hl;
     auto slot_of = [&](int k) { return k == 0 ? d.z : 2 * (c + k); };
     float *lse_dst = nullptr;
-    if (lse != nullptr) {
-        const int b = t / dense_sq, i = t - b * dense_sq;
-        lse_dst = lse + (static_cast<long long>(b) * num_heads + h) * dense_sq + i;
+    if (lse != nullptr) {      // as lse_ptr()
+        if (fold_sq > 1) {
+            const int i = h / fold_h;
+            lse_dst = lse + (static_cast<long long>(t) * fold_h + (h - i * fold_h)) * fold_sq + i;
+        } else {
+            const int b = t / dense_sq, i = t - b * dense_sq;
+            lse_dst = lse + (static_cast<long long>(b) * num_heads + h) * dense_sq + i;
+        }
     }
     merge_head(part_o, part_ml, slot_of, d.y, npad, hl, sink ? sink[h] * kLog2e : -INFINITY,
                out + static_cast<long long>(t) * o_ts + static_cast<long long>(h) * o_hs, lane, lse_dst);
@@ -2172,7 +2189,7 @@ int schedule_and_launch(KernelArgs &a, int fmt, int num_splits, void *workspace,
     if (a.balanced && !a.fused_merge) {
         sparse_mla_combine_kernel<<<dim3(grid, static_cast<unsigned>((npad + 3) / 4)), 128, 0, stream>>>(
             a.part_o, a.part_ml, reinterpret_cast<const int4 *>(a.desc), a.sink, a.out, a.o_ts, a.o_hs, a.head_blocks,
-            npad, a.lse, a.H, a.dense_sq);
+            npad, a.lse, a.H, a.dense_sq, a.fold_sq, a.fold_h);
         rc = static_cast<int>(cudaGetLastError());
     }
     return rc;
@@ -2255,6 +2272,20 @@ int launch_dense_mla_attention(const smla_dense_params_t &p, cudaStream_t stream
     a.swa.block_size = p.page_block_size;
     a.swa.block_shift = (p.page_block_size & (p.page_block_size - 1)) ? -1 : __builtin_ctz(static_cast<unsigned>(p.page_block_size));
     a.swa.vec = 1;
+    // Few heads and several query positions: fold the positions into the head dimension (one pass over the rows)
+    const long long folded_heads = static_cast<long long>(p.seqlen_q) * p.num_heads;
+    if (p.seqlen_q > 1 && folded_heads <= 64 && p.num_heads % (head_pad(static_cast<int>(folded_heads)) / 4) == 0 &&
+        p.q_token_stride == p.num_heads * p.q_head_stride && p.out_token_stride == p.num_heads * p.out_head_stride) {
+        a.T = p.batch;
+        a.H = static_cast<int>(folded_heads);
+        a.q_ts = p.q_token_stride * p.seqlen_q;
+        a.o_ts = p.out_token_stride * p.seqlen_q;
+        a.fold_sq = p.seqlen_q;
+        a.fold_h = p.num_heads;
+        a.fold_causal = a.causal;
+        a.dense_sq = 1;
+        a.causal = 0;
+    }
     // K by TMA when a 128-row tile is a whole number of pages or a page a whole number of tiles
     int fmt = kFmtBf16Dense;
     const int page = p.page_block_size;

@@ -143,6 +143,26 @@ def test_dense_edges(fm):
         check(out, lse, ref_out, ref_lse, f"edges causal={causal}")
 
 
+@pytest.mark.parametrize("h_q,s_q", [(16, 2), (16, 4), (32, 2), (8, 3)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_dense_folded_query_positions(fm, h_q, s_q, causal):
+    """Few heads and several query positions: the positions are folded into the head dimension (one pass over
+    the rows).  Lengths shorter than s_q leave early positions without any visible row under the causal mask
+    (output zero, lse -inf, as the oracle), lengths around tile and page ends shift the mask across tiles."""
+    kw, _ = dense_decode_workload(b=9, s_q=s_q, mean_sk=700, h_q=h_q, varlen=True, block_size=64, seed=h_q * s_q,
+                                  poison_tail=False)          # poisoned below, past the lengths set here
+    lens = kw["cache_seqlens"].clone()
+    lens[:6] = torch.tensor([1, 2, 3, 129, 128, 257], dtype=torch.int32, device="cuda")
+    kw["cache_seqlens"] = lens
+    for i, n in enumerate(lens.tolist()):
+        rows = kw["k_cache"][kw["block_table"][i].long()].view(-1, 1, 576)
+        rows[n:] = float("nan")
+        kw["k_cache"][kw["block_table"][i].long()] = rows.view(-1, 64, 1, 576)
+    out, lse = run_api(fm, kw, causal)
+    ref_out, ref_lse = oracle.dense_mla_decode(kw["q"], kw["k_cache"], kw["block_table"], kw["cache_seqlens"], causal=causal)
+    check(out, lse, ref_out, ref_lse, f"folded h={h_q} s_q={s_q} causal={causal}")
+
+
 def test_dense_full_size_sample(fm):
     """The reference test's own size (b=128, s_k=4096, h_q=128, s_q=2, ragged, causal), checked on a sample
     of the sequences."""
