@@ -145,7 +145,8 @@ int smla_dense_mla_decode(const smla_dense_params_t *p, void *stream) {
     int rc = device_info(d);
     if (rc != SMLA_OK) return rc;
     if (d.major != 10) return SMLA_EARCH;
-    if (p->batch <= 0 || p->seqlen_q <= 0 || p->num_heads <= 0 || p->page_block_size <= 0 || p->block_table_stride < 0)
+    if (p->batch <= 0 || p->seqlen_q <= 0 || p->num_heads <= 0 || p->page_block_size <= 0 || p->block_table_stride < 0 ||
+        p->max_blocks_per_seq < 0 || p->max_blocks_per_seq > p->block_table_stride)
         return SMLA_EINVAL;
     const long long tokens_ll = static_cast<long long>(p->batch) * p->seqlen_q;
     if (tokens_ll > 0x7FFFFFFFLL) return SMLA_ETOOBIG;
@@ -154,7 +155,7 @@ int smla_dense_mla_decode(const smla_dense_params_t *p, void *stream) {
     if (q.num_splits < 0) return SMLA_EINVAL;
     if (q.num_splits == 0) {
         // The sequences' lengths live on the device: the policy sees the longest a block table row allows.
-        const long long width = std::min<long long>(p->block_table_stride * p->page_block_size, 0x7FFFFFFFLL);
+        const long long width = std::min<long long>(static_cast<long long>(p->max_blocks_per_seq) * p->page_block_size, 0x7FFFFFFFLL);
         q.num_splits = smla_choose_num_splits(d.sm_count, tokens, p->num_heads, static_cast<int>(width));
         if (q.num_splits > 1 && (!p->workspace || p->workspace_bytes < smla_attn_workspace_bytes(tokens, p->num_heads, q.num_splits)))
             q.num_splits = 1;

@@ -370,6 +370,7 @@ void fwd_kvcache_mla(const Tensor &q_in, const Tensor &kcache, const std::option
     p.page_block_size = static_cast<int32_t>(kcache.size(1));
     p.block_table = static_cast<const int32_t *>(block_table.data_ptr());
     p.block_table_stride = block_table.stride(0);
+    p.max_blocks_per_seq = static_cast<int32_t>(std::min<int64_t>(block_table.size(1), 0x7FFFFFFF));
     p.cache_seqlens = static_cast<const int32_t *>(lens.data_ptr());
 
     const int64_t width = std::min<int64_t>(block_table.size(1) * kcache.size(1), 0x7FFFFFFF);

@@ -555,7 +555,8 @@ template <bool DENSE>
 __device__ __forceinline__ void token_rows(const KernelArgs &a, int t, int &ns, int &n) {
     if constexpr (DENSE) {     // dense paged MLA: all rows of the sequence, minus what the causal mask hides
         const int b = t / a.dense_sq, i = t - b * a.dense_sq;
-        ns = n = max(__ldg(a.swa.lens + b) - (a.causal ? a.dense_sq - 1 - i : 0), 0);
+        // lengths are clamped to what the block table row can name (swa.topk rows), as the sparse lens are to topk
+        ns = n = max(min(__ldg(a.swa.lens + b), a.swa.topk) - (a.causal ? a.dense_sq - 1 - i : 0), 0);
     } else {
         ns = min(max(__ldg(a.swa.lens + t), 0), a.swa.topk);
         const int ne = (a.extra.cache != nullptr) ? min(max(__ldg(a.extra.lens + t), 0), a.extra.topk) : 0;
@@ -2265,7 +2266,7 @@ int launch_dense_mla_attention(const smla_dense_params_t &p, cudaStream_t stream
     a.swa.idx_stride = p.block_table_stride;
     a.swa.block_stride = p.k_block_stride;
     a.swa.pos_stride = p.k_row_stride;
-    a.swa.topk = 0x7FFFFFFF;
+    a.swa.topk = static_cast<int>(std::min<long long>(static_cast<long long>(p.max_blocks_per_seq) * p.page_block_size, 0x7FFFFFFFLL));
     const long long slots = static_cast<long long>(p.num_blocks) * p.page_block_size;
     if (slots > 0x7FFFFFFFLL) return SMLA_ETOOBIG;
     a.swa.num_slots = static_cast<int>(slots);

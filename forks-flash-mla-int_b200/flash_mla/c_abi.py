@@ -82,6 +82,7 @@ class SmlaDenseParams(C.Structure):
         ("k_row_stride", C.c_int64),
         ("num_blocks", C.c_int32),
         ("page_block_size", C.c_int32),
+        ("max_blocks_per_seq", C.c_int32),
         ("block_table", C.c_void_p),
         ("block_table_stride", C.c_int64),
         ("cache_seqlens", C.c_void_p),
@@ -192,6 +193,7 @@ def dense_params(q, k_cache, block_table, cache_seqlens, out, lse=None, softmax_
     p.k_block_stride, p.k_row_stride = k_cache.stride(0) * 2, k_cache.stride(1) * 2
     p.num_blocks, p.page_block_size = k_cache.shape[0], k_cache.shape[1]
     p.block_table, p.block_table_stride = block_table.data_ptr(), block_table.stride(0)
+    p.max_blocks_per_seq = block_table.shape[1]
     p.cache_seqlens = cache_seqlens.data_ptr()
     p.num_splits = num_splits
     if workspace is not None:

@@ -183,6 +183,7 @@ typedef struct smla_dense_params {
     const void *k_cache;                  /* [num_blocks, page_block_size, 1, head_dim] bf16, 16-byte aligned    */
     int64_t k_block_stride, k_row_stride; /* bytes, multiples of 16, k_row_stride >= 2 * head_dim                */
     int32_t num_blocks, page_block_size;
+    int32_t max_blocks_per_seq;           /* columns of block_table: lengths are clamped to this many pages      */
     const int32_t *block_table;           /* [batch, max_blocks_per_seq] page numbers (negative: zero rows)      */
     int64_t block_table_stride;           /* elements                                                            */
     const int32_t *cache_seqlens;         /* [batch] rows of each sequence                                       */

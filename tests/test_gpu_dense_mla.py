@@ -163,6 +163,18 @@ def test_dense_folded_query_positions(fm, h_q, s_q, causal):
     check(out, lse, ref_out, ref_lse, f"folded h={h_q} s_q={s_q} causal={causal}")
 
 
+def test_dense_length_beyond_block_table_is_clamped(fm):
+    """A length larger than the block table row can name must not make the kernel read past the table: it is
+    clamped to max_blocks_per_seq * page rows (the sparse ops clamp lens to topk the same way)."""
+    kw, _ = dense_decode_workload(b=3, s_q=1, mean_sk=512, h_q=64, varlen=False, block_size=64, seed=2, poison_tail=False)
+    cap = kw["block_table"].shape[1] * 64
+    kw["cache_seqlens"] = torch.tensor([cap + 1000, 300, 2 ** 30], dtype=torch.int32, device="cuda")
+    out, lse = run_api(fm, kw, causal=False)
+    clamped = torch.tensor([cap, 300, cap], dtype=torch.int32)
+    ref_out, ref_lse = oracle.dense_mla_decode(kw["q"], kw["k_cache"], kw["block_table"], clamped)
+    check(out, lse, ref_out, ref_lse, "clamped lengths")
+
+
 def test_dense_full_size_sample(fm):
     """The reference test's own size (b=128, s_k=4096, h_q=128, s_q=2, ragged, causal), checked on a sample
     of the sequences."""
