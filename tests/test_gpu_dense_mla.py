@@ -175,6 +175,37 @@ def test_dense_length_beyond_block_table_is_clamped(fm):
     check(out, lse, ref_out, ref_lse, "clamped lengths")
 
 
+@pytest.mark.parametrize("b", [2, 40])
+def test_dense_replays_from_a_cuda_graph(fm, b):
+    """Captured once, replayed with new q, new lengths and a new block table in the same buffers (b = 2: a
+    sequence spread over many CTAs; b = 40: merges in the owning CTA's epilogue): every replay must match the
+    oracle, i.e. nothing the kernels use to hand partial results between CTAs may depend on the launch."""
+    kw, _ = dense_decode_workload(b=b, s_q=1, mean_sk=1800, h_q=64, varlen=True, block_size=64, seed=100 + b, poison_tail=False)
+    q, bt, sl, kc = kw["q"], kw["block_table"], kw["cache_seqlens"], kw["k_cache"]
+    cap = bt.shape[1] * 64
+    md, ns = fm.get_mla_metadata(sl, 64, 1)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            fm.flash_mla_with_kvcache(q, kc, bt, sl, 512, md, ns)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out, lse = fm.flash_mla_with_kvcache(q, kc, bt, sl, 512, md, ns)
+    gen = torch.Generator(device="cuda").manual_seed(b)
+    for rep in range(3):
+        q.copy_(torch.randn(q.shape, device="cuda", generator=gen).to(torch.bfloat16))
+        sl.copy_(torch.randint(1, cap + 1, (b,), device="cuda", generator=gen, dtype=torch.int32))
+        bt.copy_(bt.flatten()[torch.randperm(bt.numel(), device="cuda", generator=gen)].view_as(bt))
+        graph.replay()
+        torch.cuda.synchronize()
+        seqs = list(range(min(b, 6)))
+        ref_out, ref_lse = oracle.dense_mla_decode(q, kc, bt, sl, sequences=seqs)
+        check(out, lse, ref_out, ref_lse, f"graph replay {rep}, b={b}", sequences=seqs)
+
+
 def test_dense_full_size_sample(fm):
     """The reference test's own size (b=128, s_k=4096, h_q=128, s_q=2, ragged, causal), checked on a sample
     of the sequences."""
