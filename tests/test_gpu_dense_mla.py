@@ -206,6 +206,33 @@ def test_dense_replays_from_a_cuda_graph(fm, b):
         check(out, lse, ref_out, ref_lse, f"graph replay {rep}, b={b}", sequences=seqs)
 
 
+@pytest.mark.parametrize("case", range(16))
+def test_dense_random_problems(fm, case):
+    """Random small problems: batch, query positions, heads (any count, not only multiples of 8), page size,
+    ragged lengths from 1 to several tiles, head_dim 576 or 512, with and without the causal mask."""
+    rng = np.random.default_rng(9000 + case)
+    b = int(rng.integers(1, 12))
+    s_q = int(rng.choice([1, 1, 2, 3, 4]))
+    h_q = int(rng.choice([1, 4, 8, 12, 16, 24, 32, 40, 64, 72, 128]))
+    page = int(rng.choice([16, 32, 64, 128, 256]))
+    d = int(rng.choice([576, 576, 512]))
+    causal = bool(rng.integers(0, 2))
+    kw, _ = dense_decode_workload(b=b, s_q=s_q, mean_sk=int(rng.integers(64, 1400)), h_q=h_q, varlen=True,
+                                  block_size=page, seed=case, poison_tail=False, d=d)
+    cap = kw["block_table"].shape[1] * page
+    lens = torch.from_numpy(rng.integers(1, cap + 1, b).astype(np.int32)).cuda()
+    if case % 4 == 0:
+        lens[0] = int(rng.choice([1, 127, 128, 129, 255, 256]))
+    kw["cache_seqlens"] = lens
+    for i, n in enumerate(lens.tolist()):
+        rows = kw["k_cache"][kw["block_table"][i].long()].view(-1, 1, d)
+        rows[n:] = float("nan")
+        kw["k_cache"][kw["block_table"][i].long()] = rows.view(-1, page, 1, d)
+    out, lse = run_api(fm, kw, causal)
+    ref_out, ref_lse = oracle.dense_mla_decode(kw["q"], kw["k_cache"], kw["block_table"], lens, causal=causal)
+    check(out, lse, ref_out, ref_lse, f"case {case}: b={b} s_q={s_q} h_q={h_q} page={page} d={d} causal={causal}")
+
+
 def test_dense_full_size_sample(fm):
     """The reference test's own size (b=128, s_k=4096, h_q=128, s_q=2, ragged, causal), checked on a sample
     of the sequences."""
