@@ -1383,7 +1383,7 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
         // What the merge needs from OTHER CTAs does not depend on this CTA's last PV, which is still running
         // when the final epilogue starts: the flags are checked and the first loads are issued before the
         // wait for the accumulators ({max, denominator} of up to four other segments, and the first other
-        // segment's rows of round 0), so that their latency overlaps that PV.
+        // segment's rows for the first group of heads), so that their latency overlaps that PV.
         constexpr int kEarly = 4;
         float pv[kFinal ? 4 : 1][HR];
         float2 e_early[kFinal ? kEarly : 1];
@@ -1518,7 +1518,7 @@ __device__ __forceinline__ void worker_role(const KernelArgs &a, uint8_t *smem, 
     #pragma unroll 1
                 for (int r = 0; r < CW / HR; ++r) {
                     // Owner: `pv` holds the first other segment's rows of this round for all four chunks (this is
-                    // the CTA's last epilogue: the gather registers are free), fetched a round ahead -- round 0
+                    // the CTA's last epilogue: the gather registers are free), fetched one group of heads ahead -- the first
                     // before the wait for the accumulators -- so that their latency is never waited for.
                     uint32_t o2[2][HR];      // two chunks per tensor-memory round trip
     #pragma unroll
