@@ -442,7 +442,7 @@ def run_reference(args_ns):
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from ncu captures of this command line
 NCU_DRAM_TRAFFIC_BYTES = {"dsv4_fp8_decode_T128_H64": 43.6e6, "dsv4_int8_decode_T128_H64": 39.8e6,
                           "dsv4_int8_decode_T128_H128": 57.3e6, "int8_prefill_T4096_H64": 537.5e6,
-                          "dense_bf16_decode_b128_s4096_h16": 657.9e6, "dense_bf16_decode_b128_s4096_h128": 684.4e6,
+                          "dense_bf16_decode_b128_s4096_h16": 618.8e6, "dense_bf16_decode_b128_s4096_h128": 680.1e6,
                           # row kernels: captured on 2^18 rows, scaled by 4
                           "write_int8_cache_rows1M": 1543.6e6, "write_fp8_cache_rows1M": 1567.9e6,
                           "quantize_int8_rows1M": 1495.8e6,
