@@ -1101,10 +1101,14 @@ __device__ __forceinline__ float initial_ref(const KernelArgs &a, bool complete,
 // ------------------------------------------------------------------ merging one head (one warp)
 // out = sum_s 2^(m_s - M) O_s / (sum_s 2^(m_s - M) l_s + 2^(sink - M)),  M = max(m_s, sink), over the S
 // partial segments whose slots `slot_of(k)` names.  Four segments in flight per lane; partials are read
-// past L1 (another SM wrote them).
+// past L1 (another SM wrote them).  With `scratch`, the warp is one of `nsub` that share the head: it sums
+// segments sub, sub + nsub, ... and leaves its un-normalised sum, M and the denominator in its scratch row
+// (kMergeRow floats) for merge_finish.
+constexpr int kMergeRow = kD + 4;
 template <typename SlotOf>
 __device__ __forceinline__ void merge_head(const float *part_o, const float *part_ml, SlotOf slot_of, int S, int npad,
-                                           int hl, float sink_l2, __nv_bfloat16 *dst, int lane, float *lse_dst = nullptr) {
+                                           int hl, float sink_l2, __nv_bfloat16 *dst, int lane, float *lse_dst = nullptr,
+                                           int sub = 0, int nsub = 1, float *scratch = nullptr) {
     auto ml_of = [&](int k) {
         return __ldcg(reinterpret_cast<const float2 *>(part_ml) + static_cast<long long>(slot_of(k)) * npad + hl);
     };
@@ -1129,15 +1133,15 @@ __device__ __forceinline__ void merge_head(const float *part_o, const float *par
     float acc[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) acc[i] = 0.0f;
-    for (int k0 = 0; k0 < S; k0 += 4) {
+    for (int k0 = sub; k0 < S; k0 += 4 * nsub) {
         float4 x[4][4];
         float w[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-            const int k = min(k0 + u, S - 1);
+            const int k = min(k0 + u * nsub, S - 1);
             const float2 e = ml_of(k);      // the same address in every lane: one broadcast load
             // empty segments (l == 0) get weight 0; their rows are loaded but never multiplied in
-            w[u] = (k0 + u < S && e.y > 0.0f && M > -INFINITY) ? fast_exp2(e.x - M) : 0.0f;
+            w[u] = (k0 + u * nsub < S && e.y > 0.0f && M > -INFINITY) ? fast_exp2(e.x - M) : 0.0f;
             const float4 *src = reinterpret_cast<const float4 *>(part_o) +
                                 (static_cast<long long>(slot_of(k)) * npad + hl) * (kD / 4);
 #pragma unroll
@@ -1156,12 +1160,46 @@ __device__ __forceinline__ void merge_head(const float *part_o, const float *par
             }
         }
     }
+    if (scratch != nullptr) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v)
+            reinterpret_cast<float4 *>(scratch)[v * 32 + lane] = make_float4(acc[4 * v], acc[4 * v + 1], acc[4 * v + 2], acc[4 * v + 3]);
+        if (lane == 0) {
+            scratch[kD] = M;
+            scratch[kD + 1] = denom;
+        }
+        return;
+    }
     const float inv = denom > 0.0f ? 1.0f / denom : 0.0f;
     if (lse_dst != nullptr && lane == 0) *lse_dst = denom > 0.0f ? (M + log2f(denom)) * kLn2 : -INFINITY;
 #pragma unroll
     for (int v = 0; v < 4; ++v) {
         const uint2 pk = make_uint2(pack_bf16x2(acc[4 * v] * inv, acc[4 * v + 1] * inv),
                                     pack_bf16x2(acc[4 * v + 2] * inv, acc[4 * v + 3] * inv));
+        *reinterpret_cast<uint2 *>(dst + (v * 32 + lane) * 4) = pk;
+    }
+}
+// Sum of the `nsub` scratch rows that merge_head left for one head (shared memory) -> output row and lse.
+__device__ __forceinline__ void merge_finish(const float *scratch, int nsub, __nv_bfloat16 *dst, int lane, float *lse_dst) {
+    const float M = scratch[kD], denom = scratch[kD + 1];
+    float4 acc[4];
+#pragma unroll
+    for (int v = 0; v < 4; ++v) acc[v] = reinterpret_cast<const float4 *>(scratch)[v * 32 + lane];
+    for (int i = 1; i < nsub; ++i) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+            const float4 x = reinterpret_cast<const float4 *>(scratch + i * kMergeRow)[v * 32 + lane];
+            acc[v].x += x.x;
+            acc[v].y += x.y;
+            acc[v].z += x.z;
+            acc[v].w += x.w;
+        }
+    }
+    const float inv = denom > 0.0f ? 1.0f / denom : 0.0f;
+    if (lse_dst != nullptr && lane == 0) *lse_dst = denom > 0.0f ? (M + log2f(denom)) * kLn2 : -INFINITY;
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+        const uint2 pk = make_uint2(pack_bf16x2(acc[v].x * inv, acc[v].y * inv), pack_bf16x2(acc[v].z * inv, acc[v].w * inv));
         *reinterpret_cast<uint2 *>(dst + (v * 32 + lane) * 4) = pk;
     }
 }
@@ -1206,7 +1244,25 @@ __device__ __forceinline__ void merge_head_slices(const KernelArgs &a, uint8_t *
         const int t = item / a.head_blocks, h0 = (item - t * a.head_blocks) * 64;
         const int hvalid = min(NPAD, a.H - h0);
         const int j = static_cast<int>(blockIdx.x) - c0;
-        const int hbeg = j * hvalid / S, hend = (j + 1) * hvalid / S;
+        const int hbeg = j * hvalid / S, hend = (j + 1) * hvalid / S, nh = hend - hbeg;
+        // A long item cut into many segments leaves a CTA one head or none, and one warp would walk all S
+        // partials four at a time (74 segments: ~25 us).  The idle warps then share the head's segments and
+        // the sums meet in the K buffer, which nobody uses any more (16 rows per partial item of this CTA).
+        // (Dense launches only: the sparse formats select at most 20 tiles per token, where one warp per head is as fast.)
+        const int nsub = (DENSE && nh > 0 && 2 * nh <= kWorkerWarps && S >= 8) ? min(kWorkerWarps / nh, (S + 3) / 4) : 1;
+        if (DENSE && nsub > 1) {
+            float *scratch = reinterpret_cast<float *>(smem + L::kK) + (e * kWorkerWarps + warp) * kMergeRow;
+            const int g = warp / nsub, hl = hbeg + g;
+            if (g < nh) {
+                const float sink_l2 = a.sink ? a.sink[h0 + hl] * kLog2e : -INFINITY;
+                merge_head(a.part_o, a.part_ml, slot_of, S, NPAD, hl, sink_l2, nullptr, lane, nullptr, warp - g * nsub, nsub, scratch);
+            }
+            named_bar_sync(kAllWorkersBar, kWorkerThreads);
+            if (g < nh && warp == g * nsub)
+                merge_finish(scratch, nsub, a.out + static_cast<long long>(t) * a.o_ts + static_cast<long long>(h0 + hl) * a.o_hs, lane,
+                             (DENSE && a.lse != nullptr) ? lse_ptr(a, t, h0 + hl) : nullptr);
+            continue;
+        }
         for (int hl = hbeg + warp; hl < hend; hl += kWorkerWarps) {
             const float sink_l2 = a.sink ? a.sink[h0 + hl] * kLog2e : -INFINITY;
             merge_head(a.part_o, a.part_ml, slot_of, S, NPAD, hl, sink_l2,

@@ -93,6 +93,16 @@ def test_dense_every_schedule_and_merge(fm, b, mean_sk, block_size):
     check(out, lse, ref_out, ref_lse, f"b={b}", sequences=seqs)
 
 
+@pytest.mark.parametrize("b,mean_sk,h_q", [(1, 20000, 128), (1, 9000, 16), (3, 6000, 8)])
+def test_dense_long_sequences_cut_into_many_segments(fm, b, mean_sk, h_q):
+    """A sequence cut across 40-70 CTAs leaves every CTA at most one head of the slice merge; the CTA's warps
+    then share that head's segments and add their sums in shared memory."""
+    kw, _ = dense_decode_workload(b=b, s_q=1, mean_sk=mean_sk, h_q=h_q, varlen=True, seed=7 * b + h_q)
+    out, lse = run_api(fm, kw, causal=False)
+    ref_out, ref_lse = oracle.dense_mla_decode(kw["q"], kw["k_cache"], kw["block_table"], kw["cache_seqlens"])
+    check(out, lse, ref_out, ref_lse, f"b={b} s_k~{mean_sk} h_q={h_q}")
+
+
 @pytest.mark.parametrize("block_size", [16, 32, 64, 128, 256])
 def test_dense_page_sizes(fm, block_size):
     """Pages smaller than, equal to and larger than the 128-row tile (the K tile is fetched in boxes of
