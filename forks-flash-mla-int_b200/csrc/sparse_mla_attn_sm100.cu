@@ -977,6 +977,8 @@ __device__ __forceinline__ void mma_role(uint8_t *smem, uint32_t tmem_base) {
     // slabs of a chunk MN-major (the next 64 dims are one slab on, the next eight rows 1024 B, a K step of 16 rows 2048 B).
     constexpr uint64_t kSw128 = 2ull << 61;
     const uint64_t qa_sw = umma_desc(smem_u32(smem + L::kK), 16, 1024) | kSw128;
+    // ... and so is Q there: nine slabs of [NPAD heads][128 B], fetched by nine 3-D boxes (qload_role)
+    const uint64_t qb_sw = umma_desc(smem_u32(smem + L::kQ), 16, 1024) | kSw128;
     const uint64_t ra_sw = umma_desc(smem_u32(smem + L::kP), 16, 1024) | kSw128;
     const uint64_t pa_sw = umma_desc(smem_u32(smem + L::kK), kSlabBytes, 1024) | kSw128;
     const uint64_t pa = umma_desc(smem_u32(smem + L::kK), kRowGroupBytes, kCoreBytes);
@@ -1016,7 +1018,8 @@ __device__ __forceinline__ void mma_role(uint8_t *smem, uint32_t tmem_base) {
                     const uint64_t off = static_cast<uint64_t>(((16 * c + 2 * k) * kCoreBytes) >> 4);
                     if constexpr (KTMA) {
                         const uint64_t aoff = static_cast<uint64_t>(((2 * c + (k >> 2)) * kSlabBytes + (k & 3) * 32) >> 4);
-                        umma_bf16_ss_pred(tmem_base, qa_sw + aoff + (c == 0 ? c0_off : 0ull), qb + off, idesc_qk, (c | k) != 0 ? 1u : 0u, go);
+                        const uint64_t qoff = static_cast<uint64_t>(((2 * c + (k >> 2)) * (NPAD * 128) + (k & 3) * 32) >> 4);
+                        umma_bf16_ss_pred(tmem_base, qa_sw + aoff + (c == 0 ? c0_off : 0ull), qb_sw + qoff, idesc_qk, (c | k) != 0 ? 1u : 0u, go);
                     } else {
                         umma_bf16_ss_pred(tmem_base, qa + off, qb + off, idesc_qk, (c | k) != 0 ? 1u : 0u, go);
                     }
@@ -1027,7 +1030,8 @@ __device__ __forceinline__ void mma_role(uint8_t *smem, uint32_t tmem_base) {
                         for (int k = 0; k < 4; ++k) {
                             const uint64_t aoff = static_cast<uint64_t>((2 * k * kCoreBytes) >> 4);
                             const uint64_t boff = static_cast<uint64_t>(((64 + 2 * k) * kCoreBytes) >> 4);
-                            if constexpr (KTMA) umma_bf16_ss_pred(tmem_base, ra_sw + static_cast<uint64_t>((k * 32) >> 4), qb + boff, idesc_qk, 1u, go);
+                            if constexpr (KTMA) umma_bf16_ss_pred(tmem_base, ra_sw + static_cast<uint64_t>((k * 32) >> 4),
+                                                                  qb_sw + static_cast<uint64_t>((8 * (NPAD * 128) + k * 32) >> 4), idesc_qk, 1u, go);
                             else umma_bf16_ss_pred(tmem_base, ra + aoff, qb + boff, idesc_qk, 1u, go);
                         }
                     }
@@ -1278,7 +1282,7 @@ __device__ __forceinline__ void merge_head_slices(const KernelArgs &a, uint8_t *
 // the segments in the ring, wait for every tile's S^T barrier so that they know when the last QK^T of
 // a segment has completed (the Q buffer is then free), fetch the next item's Q tile with cp.async
 // and hand it to the MMA thread through the Q barrier.
-template <int NPAD, bool DENSE>
+template <int NPAD, bool DENSE, bool QSW = false>
 __device__ __forceinline__ void qload_role(const KernelArgs &a, uint8_t *smem, int qwarp, int lane) {
     using L = Smem<NPAD, DENSE>;
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::kAbort);
@@ -1294,9 +1298,19 @@ __device__ __forceinline__ void qload_role(const KernelArgs &a, uint8_t *smem, i
             // One tensor copy: box {8, 8, 64, NPAD/8, 1} of the 5-D view lands as [head group][dim group]
             // [head % 8][8 dims], which is the K-major core-matrix layout of the Q operand; head groups
             // beyond H are zero-filled.  The innermost coordinate is 0 (TMA needs it 16-byte aligned).
+            // (That copy moves 16 bytes per element: 7-13k cycles per tile, which the first QK^T of every segment
+            // waits for.  Dense, K by TMA: the tensor map is 3-D {dims, heads, tokens} instead and nine boxes
+            // {64 dims, NPAD heads, 1 token} land as slabs of [head][128 B] with the 128-byte swizzle, the layout
+            // the K slabs have; heads beyond H and, with head_dim 512, the ninth slab are zero-filled.)
             if (qwarp == 0 && lane == 0) {
                 mbar_arrive_expect_tx(bars + kBarQ * 8, L::kQBytes);
-                tma_load_5d(smem_u32(smem + L::kQ), &a.q_map, bars + kBarQ * 8, 0, 0, 0, h0 / 8, rec[0]);
+                if constexpr (QSW) {
+#pragma unroll
+                    for (int sl = 0; sl < 9; ++sl)
+                        tma_load_3d(smem_u32(smem + L::kQ) + sl * (NPAD * 128), &a.q_map, bars + kBarQ * 8, sl * 64, h0, rec[0]);
+                } else {
+                    tma_load_5d(smem_u32(smem + L::kQ), &a.q_map, bars + kBarQ * 8, 0, 0, 0, h0 / 8, rec[0]);
+                }
             }
         } else {
             issue_q_tile<NPAD, DENSE>(a, smem, rec[0], h0, min(NPAD, a.H - h0), qwarp, lane, kQLoadWarps);
@@ -2034,7 +2048,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const __gri
         mma_role<NPAD, is_dense(FMT), FMT == kFmtBf16DenseTma>(smem, tmem_base);
     } else if (a.q_tma) {
         // one tensor copy per item needs one thread; the next warp publishes the schedule
-        if (warp == kMmaWarp + 1) qload_role<NPAD, is_dense(FMT)>(a, smem, 0, lane);
+        if (warp == kMmaWarp + 1) qload_role<NPAD, is_dense(FMT), FMT == kFmtBf16DenseTma>(a, smem, 0, lane);
         if (warp == kMmaWarp + 2) scheduler_role<NPAD, is_dense(FMT)>(a, smem, lane);
         if constexpr (FMT == kFmtBf16DenseTma) {
             if (warp == kMmaWarp + 3) kload_role<NPAD>(a, smem, lane);
@@ -2181,6 +2195,21 @@ bool make_q_tensor_map(const KernelArgs &a, int npad, int dim_groups, int box_di
     return r == CUDA_SUCCESS;
 }
 
+// Dense paged MLA with K by TMA: q [T, H, 576] as a 3-D tensor {dims, heads, tokens}.  A box {64 dims, npad heads,
+// 1 token} with the 128-byte swizzle is one slab of the Q operand's shared-memory layout in that format.
+bool make_q_tensor_map_slabs(const KernelArgs &a, int npad, CUtensorMap *map) {
+    EncodeTiledFn enc = tensor_map_encoder();
+    if (enc == nullptr) return false;
+    const cuuint64_t dims[3] = {static_cast<cuuint64_t>(a.dense_dims), static_cast<cuuint64_t>(a.H), static_cast<cuuint64_t>(a.T)};
+    const cuuint64_t strides[2] = {static_cast<cuuint64_t>(a.q_hs) * 2, static_cast<cuuint64_t>(a.q_ts) * 2};
+    const cuuint32_t box[3] = {64, static_cast<cuuint32_t>(npad), 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<__nv_bfloat16 *>(a.q), dims, strides, box,
+                           estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                           CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
 // Dense paged MLA: the bf16 cache as a 3-D tensor {576 dims, rows of a page, pages}; a box {64 dims, R rows, 1 page}
 // with the 128-byte swizzle is R rows of one slab of the K tile.
 bool make_k_tensor_map(const KernelArgs &a, int num_blocks, int box_rows, CUtensorMap *map) {
@@ -2264,8 +2293,12 @@ int schedule_and_launch(KernelArgs &a, int fmt, int num_splits, void *workspace,
         a.balanced = 0;
         ctas = std::min<long long>(items, sms);
     }
-    a.q_tma = make_q_tensor_map(a, npad, is_dense(fmt) ? a.dense_dims / 8 : 64, is_dense(fmt) ? 72 : 64, &a.q_map) ? 1 : 0;
-    if (fmt == kFmtBf16DenseTma && !a.q_tma) fmt = kFmtBf16Dense;      // the K loader is the warp the Q fallback needs
+    if (fmt == kFmtBf16DenseTma) {
+        a.q_tma = make_q_tensor_map_slabs(a, npad, &a.q_map) ? 1 : 0;
+        if (!a.q_tma) fmt = kFmtBf16Dense;      // the K loader is the warp the Q fallback needs
+    }
+    if (fmt != kFmtBf16DenseTma)
+        a.q_tma = make_q_tensor_map(a, npad, is_dense(fmt) ? a.dense_dims / 8 : 64, is_dense(fmt) ? 72 : 64, &a.q_map) ? 1 : 0;
     const unsigned grid = static_cast<unsigned>(ctas);
     const bool int8_wide = fmt == SMLA_INT8_DS_MLA && a.swa.vec == 2 && (a.extra.cache == nullptr || a.extra.vec == 2);
     rc = (fmt == kFmtBf16DenseTma)   ? launch_fwd_npad<kFmtBf16DenseTma>(npad, a, grid, stream)
