@@ -161,7 +161,7 @@ struct KernelArgs {
     int T, H, head_blocks, balanced;
     float scale_log2;
     int q_tma;            // the Q tile is fetched with one TMA tensor copy through q_map (else cp.async)
-    CUtensorMap q_map;    // 5-D view of q: {8 dims, 8 heads, 64 (dense: 72) dim groups, H/8 head groups, T}
+    CUtensorMap q_map;    // 5-D view of q: {8 dims, 8 heads, 64 (dense: 72) dim groups, H/8 head groups, T}; dense with K by TMA: 3-D {dims, heads, T}
     // dense paged MLA only (dense_sq > 0): token t is query position t % dense_sq of sequence t / dense_sq;
     // swa.indices is the block table, swa.lens the sequences' lengths; with `causal` query position i sees
     // the first len - (dense_sq - 1 - i) rows.  lse[(b * H + h) * dense_sq + i], natural log, may be null.
