@@ -243,6 +243,28 @@ def test_dense_random_problems(fm, case):
     check(out, lse, ref_out, ref_lse, f"case {case}: b={b} s_q={s_q} h_q={h_q} page={page} d={d} causal={causal}")
 
 
+@pytest.mark.parametrize("page,h_q,s_q", [(48, 64, 1), (48, 16, 2), (96, 128, 1), (24, 8, 3)])
+def test_dense_page_sizes_the_boxes_cannot_serve(fm, page, h_q, s_q):
+    """A 128-row tile is neither a whole number of these pages nor a page a whole number of tiles: the rows are
+    copied by the worker threads with cp.async instead of by TMA boxes.  Ragged lengths, NaN behind every sequence."""
+    rng = np.random.default_rng(page * 1000 + h_q)
+    b = 5
+    kw, _ = dense_decode_workload(b=b, s_q=s_q, mean_sk=768, h_q=h_q, varlen=False, block_size=page, seed=page + h_q,
+                                  poison_tail=False)
+    cap = kw["block_table"].shape[1] * page
+    lens = torch.from_numpy(rng.integers(1, cap + 1, b).astype(np.int32)).cuda()
+    lens[0] = cap
+    lens[1] = 129
+    kw["cache_seqlens"] = lens
+    for i, n in enumerate(lens.tolist()):
+        rows = kw["k_cache"][kw["block_table"][i].long()].view(-1, 1, 576)
+        rows[n:] = float("nan")
+        kw["k_cache"][kw["block_table"][i].long()] = rows.view(-1, page, 1, 576)
+    out, lse = run_api(fm, kw, causal=s_q > 1)
+    ref_out, ref_lse = oracle.dense_mla_decode(kw["q"], kw["k_cache"], kw["block_table"], lens, causal=s_q > 1)
+    check(out, lse, ref_out, ref_lse, f"page {page} h_q={h_q} s_q={s_q}")
+
+
 def test_dense_full_size_sample(fm):
     """The reference test's own size (b=128, s_k=4096, h_q=128, s_q=2, ragged, causal), checked on a sample
     of the sequences."""
